@@ -1,0 +1,208 @@
+/*
+ * aeon_b200 — C ABI of the B200-native routed-expert MoE FFN path.
+ *
+ * The reference project (marcoLapiello/project-aeon) has no C ABI for this path:
+ * its kernels are header-only HIP templates included straight into the engine
+ * (src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:50-61). Each entry
+ * point below therefore cites the reference *source-level* interface it stands
+ * in for; the C++ shim in project-aeon_b200/host/ restores the reference class
+ * and function names on top of these calls.
+ *
+ * Conventions
+ *  - Every function returns an aeon_b200_status; 0 is success. The message for
+ *    the last failure on the calling thread is aeon_b200_last_error().
+ *  - Pointers are DEVICE pointers unless the parameter name ends in `_host`.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ *  - Strides are in elements of the pointed-to type.
+ *  - 16-bit tensors (activations, gate matrix, shared-expert weights) are raw
+ *    IEEE fp16 or bfloat16 bit patterns, selected by aeon_b200_moe_config.act_dtype.
+ *  - There is no CPU fallback anywhere: a call on a machine without a usable
+ *    sm_100 device returns AEON_B200_ERR_CUDA.
+ */
+#ifndef AEON_B200_H
+#define AEON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum aeon_b200_status {
+    AEON_B200_OK = 0,
+    AEON_B200_ERR_INVALID_ARGUMENT = 1, /* shape / argument violation (std::invalid_argument in the reference) */
+    AEON_B200_ERR_LOGIC = 2,            /* protocol violation (std::logic_error) */
+    AEON_B200_ERR_CUDA = 3,             /* device error (std::runtime_error from CHECK_HIP, src/infrastructure/hip_check.hpp:20-27) */
+    AEON_B200_ERR_OUT_OF_RANGE = 4,     /* id out of range (std::out_of_range) */
+    AEON_B200_ERR_TIMEOUT = 5,          /* a bounded device-side wait ran out */
+    AEON_B200_ERR_UNSUPPORTED = 6
+} aeon_b200_status;
+
+enum { AEON_B200_F16 = 0, AEON_B200_BF16 = 1 };
+enum { AEON_B200_SCORE_SQRT_SOFTPLUS = 0, AEON_B200_SCORE_SIGMOID = 1 };
+
+/*
+ * Shape and model choices of one MoE layer. Replaces the constants the
+ * reference hard-codes: V4RoutedExpertScratch::kExperts/kHidden/kIntermediate
+ * (src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:96-101), the router
+ * scalars (src/architecture/deepseek_v4/spec/config.hpp:54-62) and the swizzle
+ * configurations kCfgW13 / kCfgW2
+ * (src/backend/swizzled_w4a16/kernels/aeon_w4a16_swizzle.hpp:14-15).
+ */
+typedef struct aeon_b200_moe_config {
+    int32_t hidden;         /* H: model width; K of W1/W3, N of W2 */
+    int32_t intermediate;   /* I: expert width; N of W1/W3, K of W2 */
+    int32_t experts;        /* routed experts per layer */
+    int32_t top_k;          /* routed experts per token */
+    int32_t group_size;     /* columns sharing one fp16 scale: 32 or 128 */
+    int32_t act_dtype;      /* AEON_B200_F16 / AEON_B200_BF16 */
+    int32_t score_fn;       /* AEON_B200_SCORE_* */
+    int32_t renormalize;    /* divide the selected scores by their sum */
+    float routed_scaling;   /* multiplies the (renormalised) weights */
+    float swiglu_limit;     /* clamp of the SwiGLU: gate <= L, |up| <= L */
+    int32_t w13_rpw, w13_lpr; /* swizzle rows-per-wave / lanes-per-row of W1 and W3 */
+    int32_t w2_rpw, w2_lpr;   /* same for W2 */
+} aeon_b200_moe_config;
+
+/* Byte geometry of one expert payload: W1 packed, W1 scales, W2 packed, W2
+ * scales, W3 packed, W3 scales, each region on a 4 KiB boundary. Replaces the
+ * constants of src/backend/swizzled_w4a16/core/swizzled_expert_format.hpp:11-30. */
+typedef struct aeon_b200_expert_layout {
+    uint64_t payload_bytes;
+    uint64_t w1_packed_offset, w1_scale_offset;
+    uint64_t w2_packed_offset, w2_scale_offset;
+    uint64_t w3_packed_offset, w3_scale_offset;
+    uint64_t w13_packed_bytes, w13_scale_bytes;
+    uint64_t w2_packed_bytes, w2_scale_bytes;
+} aeon_b200_expert_layout;
+
+typedef struct aeon_b200_ctx aeon_b200_ctx;
+
+const char* aeon_b200_last_error(void);
+const char* aeon_b200_version(void);
+
+/* Named presets: "ref_dsv4" (the reference model's shapes: H 4096, I 2048, 256
+ * experts, top-6, group 32, fp16, sqrt-softplus x1.5) and "baseline" (H 7168,
+ * I 2048, 256 experts, top-8, group 128, bf16, sigmoid renormalised to 1). */
+int aeon_b200_config_preset(const char* name, aeon_b200_moe_config* out_host);
+int aeon_b200_config_validate(const aeon_b200_moe_config* cfg_host);
+int aeon_b200_expert_layout_of(const aeon_b200_moe_config* cfg_host,
+                               aeon_b200_expert_layout* out_host);
+
+/* Host re-layout between checkpoint order (row-major [N, K/8] words of eight
+ * nibbles, scales [N, K/group]) and the swizzled order the kernels read.
+ * Replaces swizzle_w4a16 / unswizzle_w4a16
+ * (src/backend/swizzled_w4a16/kernels/aeon_w4a16_swizzle.hpp:46-129). */
+int aeon_b200_swizzle_w4a16(const uint32_t* src_packed_host, const uint16_t* src_scale_host,
+                            uint32_t* dst_packed_host, uint16_t* dst_scale_host,
+                            int N, int K, int rpw, int lpr, int group);
+int aeon_b200_unswizzle_w4a16(const uint32_t* src_packed_host, const uint16_t* src_scale_host,
+                              uint32_t* dst_packed_host, uint16_t* dst_scale_host,
+                              int N, int K, int rpw, int lpr, int group);
+
+/* A context owns the device scratch of the path for up to `max_tokens` tokens
+ * per call. Replaces V4RoutedExpertScratch
+ * (src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:95-173). */
+int aeon_b200_ctx_create(const aeon_b200_moe_config* cfg_host, int device, int max_tokens,
+                         aeon_b200_ctx** out_host);
+int aeon_b200_ctx_destroy(aeon_b200_ctx* ctx);
+uint64_t aeon_b200_ctx_scratch_bytes(const aeon_b200_ctx* ctx);
+/* Synchronises `stream` and reports a device-side error flag (a bounded wait
+ * that ran out, an id out of range) as a status. */
+int aeon_b200_ctx_check(aeon_b200_ctx* ctx, void* stream);
+/* Kernel launches issued by this context since creation (the benchmark's count). */
+uint64_t aeon_b200_ctx_launches(const aeon_b200_ctx* ctx);
+
+/* Expert payload pool: one device slab of slots x payload_bytes, a slot being a
+ * byte-identical expert payload. Replaces ExpertPayloadPool
+ * (src/infrastructure/expert/storage/expert_payload_pool.hpp:16-131). */
+int aeon_b200_pool_create(uint64_t payload_bytes, uint32_t slots, int device, void** out_base_host);
+int aeon_b200_pool_destroy(void* base, int device);
+int aeon_b200_pool_upload(void* base, uint64_t payload_bytes, uint32_t slot,
+                          const void* payload_host, void* stream);
+
+/* Router: gate projection + score + top-k + renormalise + scale, one call.
+ * Replaces dispatch_router
+ * (src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:124-159), i.e.
+ * gemv_fp16_vec8_kernel + v4_half_to_float_n_kernel + moe_router_kernel
+ * (src/architecture/deepseek_v4/kernels/moe_router.hpp:104-189).
+ * x[tokens, x_stride] and gate[experts, hidden] are 16-bit (act_dtype);
+ * bias[experts] fp32 may be NULL. hash_table[vocab, top_k] (int64) + token_ids
+ * select the table-lookup branch when both are non-NULL. Outputs: ids in
+ * descending selection order, ties to the lower index; logits_out[tokens,
+ * experts] fp32 is optional. */
+int aeon_b200_router_topk(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const void* gate,
+                          const float* bias, const int64_t* hash_table, const int32_t* token_ids,
+                          int tokens, float* topk_weights, int32_t* topk_ids, float* logits_out,
+                          void* stream);
+
+/* Counting sort of the (token, slot) draws by expert. Replaces
+ * dispatch_expert_permutation (src/platform/ops/expert_permutation.hpp:44-175):
+ * expert_offsets[experts+1], token_indices[draws], draw_indices[draws] and,
+ * when `weights` is non-NULL, weights_by_position[draws]. Ascending expert
+ * order, ascending draw order inside an expert; ids outside [0, experts) are
+ * dropped. */
+int aeon_b200_expert_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens,
+                                 int slots, int experts, int32_t* expert_offsets,
+                                 int32_t* token_indices, int32_t* draw_indices,
+                                 const float* weights, float* weights_by_position, void* stream);
+
+/* Shared expert: dense 16-bit FFN with the same clamped SwiGLU, WRITTEN into
+ * moe_accum (fp32) as the accumulator's initial value. Replaces
+ * run_layer_body_moe_shared_expert[_batch]
+ * (src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:216-256,
+ *  src/architecture/deepseek_v4/layer/v4_layer_body_batch.hpp:863-917).
+ * w1, w3: [I, H]; w2: [H, I]; row-major, act_dtype. */
+int aeon_b200_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
+                            const void* x, int64_t x_stride, int tokens, float* moe_accum,
+                            int64_t accum_stride, void* stream);
+
+/* Decode path: for every token, moe_accum[t,:] += sum over its top_k slots, in
+ * slot order, of weight * W2_e * clamped_swiglu(W1_e x, W3_e x); fp32 in and out.
+ * Replaces V4TieredExpertExecutor::accumulate_routed / accumulate_routed_batch
+ * (src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:298-370,379-461), i.e.
+ * aeon_moe_fused_gate_up_kernel, aeon_moe_fused_w2_contrib_kernel and
+ * moe_accumulate_fixed_order_kernel. `pool_base` is the expert pool slab;
+ * slot_of_expert[experts] maps a routed expert id to its slot (-1: absent, which
+ * raises the context's error flag). Each distinct expert's weights are read once
+ * per call. tokens <= the context's max_tokens. */
+int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
+                         const void* x, int64_t x_stride, const int32_t* topk_ids,
+                         const float* topk_weights, int tokens, float* moe_accum,
+                         int64_t accum_stride, void* stream);
+
+/* Statistics of the last decode/prefill call of this context (host values read
+ * back after a synchronise): distinct experts touched and work-list entries. */
+int aeon_b200_ctx_last_stats(aeon_b200_ctx* ctx, void* stream, int32_t* distinct_experts_host,
+                             int32_t* entries_host);
+
+/* Per-kernel device timing. When enabled, the decode path brackets its two streaming
+ * kernels with CUDA events on the caller's stream; aeon_b200_ctx_kernel_times synchronises
+ * the stream, adds up the elapsed times since the last call and returns, for kernel
+ * 0 (W1/W3 + SwiGLU) and 1 (W2 + accumulate), the total milliseconds and launch counts.
+ * No counterpart in the reference, which times regions with its PhaseProfiler
+ * (src/infrastructure/profiling/phase_profiler.hpp:41-110). */
+int aeon_b200_ctx_set_timing(aeon_b200_ctx* ctx, int enabled);
+int aeon_b200_ctx_kernel_times(aeon_b200_ctx* ctx, void* stream, double* total_ms_host2,
+                               int64_t* launches_host2);
+
+/* Counter-based synthetic tensors, bit-identical to the CPU test oracle's
+ * generators, so benchmark pools are filled on the device. Expert payloads:
+ * nibbles uniform in 0..15 (q = nibble - 8), scales drawn from `scale_table`
+ * (fp16 bit patterns, table_n a power of two). Dense tensors: magnitude from
+ * the table, sign from the draw. These have no counterpart in the reference,
+ * whose tests build payloads on the host
+ * (tests/test_w2_shard_equivalence.cpp:80-87). */
+int aeon_b200_synth_fill_experts(const aeon_b200_moe_config* cfg_host, void* pool_base,
+                                 uint32_t first_slot, uint32_t count, uint64_t seed,
+                                 uint32_t layer, uint32_t first_expert,
+                                 const uint16_t* scale_table, uint32_t table_n, void* stream);
+int aeon_b200_synth_fill_dense16(void* out, uint64_t count, uint64_t seed, uint32_t layer,
+                                 uint32_t stream_id, const uint16_t* magnitude_table,
+                                 uint32_t table_n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AEON_B200_H */

@@ -337,4 +337,23 @@ int ao_compare(const double* want, const double* got, uint64_t n, double rel_flo
     });
 }
 
+// FNV-1a over a byte range (fixture checksums).
+uint64_t ao_fnv1a(const uint8_t* data, uint64_t bytes) {
+    uint64_t h = 0xCBF29CE484222325ull;
+    for (uint64_t i = 0; i < bytes; ++i) { h ^= data[i]; h *= 0x100000001B3ull; }
+    return h;
+}
+
+// dense_ffn on fp64 weights (row-major [I,H], [I,H], [H,I]).
+int ao_dense_ffn_f64(const double* w1, const double* w3, const double* w2, int intermediate,
+                     int hidden, const double* x, double limit, double* out) {
+    return guarded([&] {
+        const size_t H = static_cast<size_t>(hidden), I = static_cast<size_t>(intermediate);
+        const std::vector<double> y = dense_ffn(
+            I, H, std::vector<double>(x, x + H), std::vector<double>(w1, w1 + I * H),
+            std::vector<double>(w3, w3 + I * H), std::vector<double>(w2, w2 + H * I), limit);
+        std::memcpy(out, y.data(), H * sizeof(double));
+    });
+}
+
 }  // extern "C"

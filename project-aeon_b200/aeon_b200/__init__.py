@@ -1,0 +1,277 @@
+"""ctypes binding of libaeon_b200.so (the C ABI declared in include/aeon_b200.h).
+
+PyTorch is used only as the owner of device memory and streams: every call takes
+``tensor.data_ptr()`` values and the current CUDA stream handle. There is no CPU
+fallback: importing works anywhere (so the symbols can be checked), but any
+compute call needs an sm_100 device and raises ``AeonError`` otherwise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import (POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint16, c_uint32,
+                    c_uint64, c_void_p)
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libaeon_b200.so")
+
+F16, BF16 = 0, 1
+SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID = 0, 1
+
+STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "LOGIC", 3: "CUDA", 4: "OUT_OF_RANGE",
+                5: "TIMEOUT", 6: "UNSUPPORTED"}
+
+# Every symbol include/aeon_b200.h declares (checked by the CPU test-suite).
+EXPORTED_SYMBOLS = [
+    "aeon_b200_last_error", "aeon_b200_version", "aeon_b200_config_preset",
+    "aeon_b200_config_validate", "aeon_b200_expert_layout_of", "aeon_b200_swizzle_w4a16",
+    "aeon_b200_unswizzle_w4a16", "aeon_b200_ctx_create", "aeon_b200_ctx_destroy",
+    "aeon_b200_ctx_scratch_bytes", "aeon_b200_ctx_check", "aeon_b200_ctx_launches",
+    "aeon_b200_pool_create", "aeon_b200_pool_destroy", "aeon_b200_pool_upload",
+    "aeon_b200_router_topk", "aeon_b200_expert_permutation", "aeon_b200_shared_expert",
+    "aeon_b200_moe_decode", "aeon_b200_ctx_last_stats", "aeon_b200_synth_fill_experts",
+    "aeon_b200_synth_fill_dense16", "aeon_b200_ctx_set_timing", "aeon_b200_ctx_kernel_times",
+]
+
+
+class AeonError(RuntimeError):
+    """Mirrors the reference's exception kinds through the status code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[{STATUS_NAMES.get(status, status)}] {message}")
+        self.status = status
+
+
+class MoeConfig(ctypes.Structure):
+    _fields_ = [("hidden", c_int32), ("intermediate", c_int32), ("experts", c_int32),
+                ("top_k", c_int32), ("group_size", c_int32), ("act_dtype", c_int32),
+                ("score_fn", c_int32), ("renormalize", c_int32), ("routed_scaling", c_float),
+                ("swiglu_limit", c_float), ("w13_rpw", c_int32), ("w13_lpr", c_int32),
+                ("w2_rpw", c_int32), ("w2_lpr", c_int32)]
+
+    def copy(self, **changes) -> "MoeConfig":
+        out = MoeConfig.from_buffer_copy(bytes(self))
+        for key, value in changes.items():
+            setattr(out, key, value)
+        return out
+
+
+class ExpertLayout(ctypes.Structure):
+    _fields_ = [(name, c_uint64) for name in (
+        "payload_bytes", "w1_packed_offset", "w1_scale_offset", "w2_packed_offset",
+        "w2_scale_offset", "w3_packed_offset", "w3_scale_offset", "w13_packed_bytes",
+        "w13_scale_bytes", "w2_packed_bytes", "w2_scale_bytes")]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the shared library; a missing build is an error, never a fallback."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise AeonError(3, f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; "
+                           "g.build()'` (or make -C project-aeon_b200/csrc) first")
+    L = ctypes.CDLL(LIB_PATH)
+    L.aeon_b200_last_error.restype = c_char_p
+    L.aeon_b200_version.restype = c_char_p
+    L.aeon_b200_ctx_scratch_bytes.restype = c_uint64
+    L.aeon_b200_ctx_scratch_bytes.argtypes = [c_void_p]
+    L.aeon_b200_ctx_launches.restype = c_uint64
+    L.aeon_b200_ctx_launches.argtypes = [c_void_p]
+    L.aeon_b200_config_preset.argtypes = [c_char_p, POINTER(MoeConfig)]
+    L.aeon_b200_config_validate.argtypes = [POINTER(MoeConfig)]
+    L.aeon_b200_expert_layout_of.argtypes = [POINTER(MoeConfig), POINTER(ExpertLayout)]
+    swz = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
+    L.aeon_b200_swizzle_w4a16.argtypes = swz
+    L.aeon_b200_unswizzle_w4a16.argtypes = swz
+    L.aeon_b200_ctx_create.argtypes = [POINTER(MoeConfig), c_int, c_int, POINTER(c_void_p)]
+    L.aeon_b200_ctx_destroy.argtypes = [c_void_p]
+    L.aeon_b200_ctx_check.argtypes = [c_void_p, c_void_p]
+    L.aeon_b200_ctx_last_stats.argtypes = [c_void_p, c_void_p, POINTER(c_int32), POINTER(c_int32)]
+    L.aeon_b200_ctx_set_timing.argtypes = [c_void_p, c_int]
+    L.aeon_b200_ctx_kernel_times.argtypes = [c_void_p, c_void_p, POINTER(ctypes.c_double),
+                                             POINTER(c_int64)]
+    L.aeon_b200_pool_create.argtypes = [c_uint64, c_uint32, c_int, POINTER(c_void_p)]
+    L.aeon_b200_pool_destroy.argtypes = [c_void_p, c_int]
+    L.aeon_b200_pool_upload.argtypes = [c_void_p, c_uint64, c_uint32, c_void_p, c_void_p]
+    L.aeon_b200_router_topk.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    L.aeon_b200_expert_permutation.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+    L.aeon_b200_shared_expert.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                          c_int, c_void_p, c_int64, c_void_p]
+    L.aeon_b200_moe_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                       c_void_p, c_int, c_void_p, c_int64, c_void_p]
+    L.aeon_b200_synth_fill_experts.argtypes = [POINTER(MoeConfig), c_void_p, c_uint32, c_uint32,
+                                               c_uint64, c_uint32, c_uint32, c_void_p, c_uint32,
+                                               c_void_p]
+    L.aeon_b200_synth_fill_dense16.argtypes = [c_void_p, c_uint64, c_uint64, c_uint32, c_uint32,
+                                               c_void_p, c_uint32, c_void_p]
+    _lib = L
+    return L
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise AeonError(status, lib().aeon_b200_last_error().decode())
+
+
+def preset(name: str) -> MoeConfig:
+    cfg = MoeConfig()
+    check(lib().aeon_b200_config_preset(name.encode(), ctypes.byref(cfg)))
+    return cfg
+
+
+def expert_layout(cfg: MoeConfig) -> ExpertLayout:
+    out = ExpertLayout()
+    check(lib().aeon_b200_expert_layout_of(ctypes.byref(cfg), ctypes.byref(out)))
+    return out
+
+
+def swizzle_w4a16(src_packed, src_scale, N, K, rpw, lpr, group, inverse=False):
+    """Host re-layout of one matrix; numpy uint32 [N, K/8] and uint16 [N, K/group] in and out."""
+    import numpy as np
+    src_packed = np.ascontiguousarray(src_packed, dtype=np.uint32)
+    src_scale = np.ascontiguousarray(src_scale, dtype=np.uint16)
+    dst_packed = np.empty_like(src_packed)
+    dst_scale = np.empty_like(src_scale)
+    fn = lib().aeon_b200_unswizzle_w4a16 if inverse else lib().aeon_b200_swizzle_w4a16
+    check(fn(src_packed.ctypes.data, src_scale.ctypes.data, dst_packed.ctypes.data,
+             dst_scale.ctypes.data, N, K, rpw, lpr, group))
+    return dst_packed, dst_scale
+
+
+def _ptr(t):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class ExpertPool:
+    """One device slab of `slots` expert payloads (the reference's UnifiedVRAMExpertPool)."""
+
+    def __init__(self, cfg: MoeConfig, slots: int, device: int = 0):
+        import torch
+        self.cfg = cfg
+        self.layout = expert_layout(cfg)
+        self.slots = slots
+        self.device = device
+        self.payload_bytes = int(self.layout.payload_bytes)
+        # torch owns the slab so its caching allocator sees the memory.
+        self.slab = torch.empty(self.payload_bytes * slots, dtype=torch.uint8,
+                                device=f"cuda:{device}")
+
+    @property
+    def base(self) -> int:
+        return self.slab.data_ptr()
+
+    def upload(self, slot: int, payload) -> None:
+        import torch
+        if not 0 <= slot < self.slots:
+            raise AeonError(4, f"slot {slot} outside the pool's {self.slots} slots")
+        t = torch.as_tensor(payload).view(torch.uint8)
+        if t.numel() != self.payload_bytes:
+            raise AeonError(1, "payload size does not match the pool's payload_bytes")
+        self.slab[slot * self.payload_bytes:(slot + 1) * self.payload_bytes].copy_(t)
+
+    def fill_synthetic(self, first_slot: int, count: int, seed: int, layer: int,
+                       first_expert: int, scale_table) -> None:
+        check(lib().aeon_b200_synth_fill_experts(
+            ctypes.byref(self.cfg), c_void_p(self.base), first_slot, count, seed, layer,
+            first_expert, _ptr(scale_table), scale_table.numel(), _stream()))
+
+
+def synth_fill_dense16(out, seed: int, layer: int, stream_id: int, table) -> None:
+    check(lib().aeon_b200_synth_fill_dense16(_ptr(out), out.numel(), seed, layer, stream_id,
+                                             _ptr(table), table.numel(), _stream()))
+
+
+class Context:
+    """Device scratch + the kernel entry points for one layer shape."""
+
+    def __init__(self, cfg: MoeConfig, device: int = 0, max_tokens: int = 128):
+        self.cfg = cfg
+        self.device = device
+        self.max_tokens = max_tokens
+        handle = c_void_p()
+        check(lib().aeon_b200_ctx_create(ctypes.byref(cfg), device, max_tokens, ctypes.byref(handle)))
+        self._h = handle
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().aeon_b200_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def scratch_bytes(self) -> int:
+        return int(lib().aeon_b200_ctx_scratch_bytes(self._h))
+
+    @property
+    def launches(self) -> int:
+        return int(lib().aeon_b200_ctx_launches(self._h))
+
+    def check(self) -> None:
+        check(lib().aeon_b200_ctx_check(self._h, _stream()))
+
+    def last_stats(self):
+        distinct, entries = c_int32(), c_int32()
+        check(lib().aeon_b200_ctx_last_stats(self._h, _stream(), ctypes.byref(distinct),
+                                             ctypes.byref(entries)))
+        return distinct.value, entries.value
+
+    def set_timing(self, enabled: bool) -> None:
+        check(lib().aeon_b200_ctx_set_timing(self._h, int(enabled)))
+
+    def kernel_times(self):
+        """((ms_w13, launches), (ms_w2, launches)) since the last call."""
+        ms = (ctypes.c_double * 2)()
+        n = (c_int64 * 2)()
+        check(lib().aeon_b200_ctx_kernel_times(self._h, _stream(), ms, n))
+        return (ms[0], n[0]), (ms[1], n[1])
+
+    def router_topk(self, x, gate, bias=None, hash_table=None, token_ids=None, logits_out=None):
+        import torch
+        tokens = x.shape[0]
+        k = self.cfg.top_k
+        weights = torch.empty(tokens, k, dtype=torch.float32, device=x.device)
+        ids = torch.empty(tokens, k, dtype=torch.int32, device=x.device)
+        check(lib().aeon_b200_router_topk(self._h, _ptr(x), x.stride(0), _ptr(gate), _ptr(bias),
+                                          _ptr(hash_table), _ptr(token_ids), tokens, _ptr(weights),
+                                          _ptr(ids), _ptr(logits_out), _stream()))
+        return weights, ids
+
+    def expert_permutation(self, ids, experts=None, weights=None):
+        import torch
+        tokens, slots = ids.shape
+        experts = experts or self.cfg.experts
+        dev = ids.device
+        offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+        token_idx = torch.full((tokens * slots,), -1, dtype=torch.int32, device=dev)
+        draw_idx = torch.full((tokens * slots,), -1, dtype=torch.int32, device=dev)
+        wpos = torch.zeros(tokens * slots, dtype=torch.float32, device=dev) if weights is not None else None
+        check(lib().aeon_b200_expert_permutation(self._h, _ptr(ids), tokens, slots, experts,
+                                                 _ptr(offsets), _ptr(token_idx), _ptr(draw_idx),
+                                                 _ptr(weights), _ptr(wpos), _stream()))
+        return offsets, token_idx, draw_idx, wpos
+
+    def shared_expert(self, w1, w3, w2, x, moe_accum):
+        check(lib().aeon_b200_shared_expert(self._h, _ptr(w1), _ptr(w3), _ptr(w2), _ptr(x),
+                                            x.stride(0), x.shape[0], _ptr(moe_accum),
+                                            moe_accum.stride(0), _stream()))
+
+    def moe_decode(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum):
+        check(lib().aeon_b200_moe_decode(self._h, c_void_p(pool_base), _ptr(slot_of_expert), _ptr(x),
+                                         x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
+                                         _ptr(moe_accum), moe_accum.stride(0), _stream()))

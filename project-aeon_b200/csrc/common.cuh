@@ -1,0 +1,155 @@
+// Internal declarations shared by the translation units of libaeon_b200.so.
+#pragma once
+
+#include "aeon_b200.h"
+
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace aeon_b200 {
+
+// ---------------------------------------------------------------------------
+// Error plumbing: C++ exceptions inside, status codes at the ABI.
+// ---------------------------------------------------------------------------
+struct StatusError : std::runtime_error {
+    int status;
+    StatusError(int s, const std::string& what) : std::runtime_error(what), status(s) {}
+};
+
+void set_last_error(const std::string& message);
+
+#define AEON_CUDA_CHECK(expr)                                                              \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess) {                                                           \
+            throw ::aeon_b200::StatusError(                                                \
+                AEON_B200_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e) +  \
+                                        " (" __FILE__ ":" + std::to_string(__LINE__) + ")"); \
+        }                                                                                  \
+    } while (0)
+
+inline void require(bool ok, const char* message) {
+    if (!ok) throw StatusError(AEON_B200_ERR_INVALID_ARGUMENT, message);
+}
+
+template <class F>
+int guarded(F&& f) noexcept {
+    try {
+        f();
+        return AEON_B200_OK;
+    } catch (const StatusError& e) {
+        set_last_error(e.what());
+        return e.status;
+    } catch (const std::exception& e) {
+        set_last_error(e.what());
+        return AEON_B200_ERR_CUDA;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Geometry of one swizzled matrix (device-visible POD).
+// ---------------------------------------------------------------------------
+struct MatrixGeom {
+    uint64_t packed_offset;   // bytes from payload start
+    uint64_t scale_offset;
+    int rows, cols, rpw, lpr;
+    int iters;                // (cols / 32) / lpr
+    int block_bytes;          // packed bytes of one row-block: iters * 512
+    int block_scale_bytes;    // scale bytes of one row-block: iters * 32 / (group/32) * 2
+};
+
+struct ExpertGeom {
+    MatrixGeom w1, w2, w3;
+    uint64_t payload_bytes;
+    int group;
+};
+
+ExpertGeom make_geom(const aeon_b200_moe_config& cfg);
+void validate_config(const aeon_b200_moe_config& cfg);
+
+// Device error flag values (ctx->d_error).
+enum : int {
+    kErrNone = 0,
+    kErrWaitTimeout = 1,      // an mbarrier wait ran out of iterations
+    kErrExpertAbsent = 2,     // slot_of_expert[e] < 0 for a routed expert
+    kErrIdOutOfRange = 3
+};
+
+// One entry of the decode work list: the tokens [pos0, pos0+ntok) of the
+// expert-sorted draw order all belong to `expert`, whose payload is pool slot `slot`.
+struct WorkEntry {
+    int expert, pos0, ntok, slot;
+};
+
+}  // namespace aeon_b200
+
+struct aeon_b200_ctx {
+    aeon_b200_moe_config cfg;
+    aeon_b200::ExpertGeom geom;
+    int device;
+    int sm_count;
+    int max_tokens;
+    uint64_t scratch_bytes;
+    uint64_t launches;
+
+    // --- device scratch ---
+    __half* d_xperm;        // [max_tokens, H] fp16 activations in the kernels' K order
+    float* d_logits;        // [max_tokens, E]
+    int32_t* d_offsets;     // [E + 1]
+    int32_t* d_token_idx;   // [max_tokens * k]
+    int32_t* d_draw_idx;    // [max_tokens * k]
+    float* d_wpos;          // [max_tokens * k]
+    aeon_b200::WorkEntry* d_entries;  // [E + max_tokens * k / 8 + 1]
+    int32_t* d_counts;      // [0] = entries, [1] = distinct experts, [2] = draws placed
+    __half* d_hidden_hi;    // [max_tokens * k, I]
+    __half* d_hidden_lo;    // [max_tokens * k, I]
+    float* d_contrib;       // [max_tokens * k, H]
+    int32_t* d_tile_done;   // per output row tile arrival counters
+    int32_t* d_error;       // device error flag
+    // optional per-kernel timing (events recorded on the caller's stream)
+    int timing_enabled;
+    std::vector<cudaEvent_t>* timing_events;   // triples: before A, between A and B, after B
+    size_t timing_used;
+    double timing_ms[2];
+    int64_t timing_launches[2];
+
+    // shared expert scratch
+    __half* d_sh_hi;        // [max_tokens, I] (hi/mid/lo split of the fp32 hidden)
+    __half* d_sh_mid;
+    __half* d_sh_lo;
+};
+
+namespace aeon_b200 {
+
+// Launchers (one per translation unit).
+void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const void* gate,
+                   const float* bias, const int64_t* hash_table, const int32_t* token_ids,
+                   int tokens, float* topk_weights, int32_t* topk_ids, float* logits_out,
+                   cudaStream_t stream);
+void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens, int slots,
+                        int experts, int32_t* expert_offsets, int32_t* token_indices,
+                        int32_t* draw_indices, const float* weights, float* weights_by_position,
+                        const int32_t* slot_of_expert, WorkEntry* entries, int32_t* counts,
+                        cudaStream_t stream);
+void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
+                       const void* x, int64_t x_stride, const int32_t* topk_ids,
+                       const float* topk_weights, int tokens, float* moe_accum,
+                       int64_t accum_stride, cudaStream_t stream);
+void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
+                          const void* x, int64_t x_stride, int tokens, float* moe_accum,
+                          int64_t accum_stride, cudaStream_t stream);
+void launch_synth_experts(const aeon_b200_moe_config& cfg, void* pool_base, uint32_t first_slot,
+                          uint32_t count, uint64_t seed, uint32_t layer, uint32_t first_expert,
+                          const uint16_t* scale_table, uint32_t table_n, cudaStream_t stream);
+void launch_synth_dense16(void* out, uint64_t count, uint64_t seed, uint32_t layer,
+                          uint32_t stream_id, const uint16_t* table, uint32_t table_n,
+                          cudaStream_t stream);
+
+}  // namespace aeon_b200

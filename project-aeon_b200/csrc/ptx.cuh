@@ -1,0 +1,174 @@
+// Thin inline-PTX wrappers used by the sm_100a kernels: shared-memory barriers
+// (mbarrier), bulk asynchronous copies (the TMA engine's untiled form), the
+// warp-level 16x8x16 MMA, and the int4 -> fp16 register unpack.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cstdint>
+
+namespace aeon_b200 {
+namespace ptx {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false when the iteration budget ran out, or at once when
+// `error_flag` is already set: after the first failure every later wait of the launch falls
+// through, so the kernel keeps its barrier structure (nobody is left alone at a bar.sync)
+// and ends quickly. The caller records the failure in the flag.
+constexpr uint32_t kWaitBudget = 1u << 21;
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          const volatile int32_t* error_flag) {
+    for (uint32_t i = 0; i < kWaitBudget; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *error_flag != 0) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+// Untiled bulk copy global -> shared, completion counted in bytes on `bar`.
+// Both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float lds_half_as_float(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return __half2float(__ushort_as_half(v));
+}
+
+// D += A(16x16, row) * B(16x8, col), fp16 operands, fp32 accumulate.
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int kLut>
+__device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(r) : "r"(a), "r"(b), "r"(c), "n"(kLut));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
+// One swizzled 32-bit word holds eight consecutive columns of a row, nibble
+// position p = column 2p (p < 4) or column 2(p-4)+1 (p >= 4), so the 16-bit
+// halves of (word >> 4p) & 0x000F000F are the column pair (2p, 2p+1). OR-ing
+// 0x6400 into a half gives the fp16 number 1024 + nibble (or 1024 + 16*nibble
+// for the nibble one position up), from which the signed value nibble - 8 is
+// one exact half2 operation away. Output: pairs[p] = fp16x2 (q(2p), q(2p+1)).
+__device__ __forceinline__ void unpack_word(uint32_t w, uint32_t (&pairs)[4]) {
+    constexpr uint32_t kMagic = 0x64006400u;      // 1024.0 | 1024.0
+    constexpr uint32_t k1032 = 0x64086408u;       // 1032.0
+    constexpr uint32_t kSixteenth = 0x2C002C00u;  // 1/16
+    constexpr uint32_t kMinus72 = 0xD480D480u;    // -72.0
+    constexpr int kAndOr = (0xF0 & 0xCC) | 0xAA;  // (a & b) | c
+    const uint32_t w8 = w >> 8;
+    const uint32_t p0 = lop3<kAndOr>(w, 0x000F000Fu, kMagic);
+    const uint32_t p1 = lop3<kAndOr>(w, 0x00F000F0u, kMagic);
+    const uint32_t p2 = lop3<kAndOr>(w8, 0x000F000Fu, kMagic);
+    const uint32_t p3 = lop3<kAndOr>(w8, 0x00F000F0u, kMagic);
+    pairs[0] = hsub2_u32(p0, k1032);
+    pairs[1] = hfma2_u32(p1, kSixteenth, kMinus72);
+    pairs[2] = hsub2_u32(p2, k1032);
+    pairs[3] = hfma2_u32(p3, kSixteenth, kMinus72);
+}
+
+}  // namespace ptx
+}  // namespace aeon_b200

@@ -1,0 +1,191 @@
+// Router: gate projection, score, top-k, renormalise, scale.
+//
+// Stands in for dispatch_router (src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:124-159)
+// = gemv_fp16_vec8_kernel (src/platform/ops/gemv.hpp:72-110) + v4_half_to_float_n_kernel +
+// moe_router_kernel (src/architecture/deepseek_v4/kernels/moe_router.hpp:104-189).
+//
+// The logits are fp32 with a *defined* summation order so a CPU can reproduce them bit for
+// bit and the selected ids can be checked exactly rather than up to near-ties: 32 partial
+// sums, partial l taking in ascending k the elements whose 8-wide vector index (k / 8) is
+// congruent to l modulo 32 (one fused multiply-add each; products of two 16-bit floats are
+// exact in fp32), then a butterfly over lane distances 16, 8, 4, 2, 1. The reference rounds
+// its logits to fp16 between the projection and the selection; that rounding is dropped.
+//
+// Selection: descending key, ties to the lower index (moe_router.hpp:154-169). With a bias
+// the key is score + bias, as in the reference; without one the key is the logit itself,
+// which orders identically (both score functions are strictly increasing) and does not
+// depend on the device's exp/log rounding. Stored weights are the unbiased scores of the
+// selected experts, divided by their sum when renormalising, then scaled.
+#include "common.cuh"
+
+namespace aeon_b200 {
+
+namespace {
+
+constexpr int kLogitWarps = 8;      // experts per CTA
+constexpr int kLogitTokens = 4;     // tokens per CTA
+
+template <bool kBf16>
+__device__ __forceinline__ void widen8(const uint4& v, float (&out)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if constexpr (kBf16) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+            out[2 * i] = __low2float(h);
+            out[2 * i + 1] = __high2float(h);
+        }
+    }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kLogitWarps * 32)
+router_logits_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
+                     const uint16_t* __restrict__ gate, int tokens, int experts, int hidden,
+                     float* __restrict__ logits) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int e = blockIdx.x * kLogitWarps + warp;
+    const int t0 = blockIdx.y * kLogitTokens;
+    if (e >= experts) return;
+    const int nt = min(kLogitTokens, tokens - t0);
+
+    float acc[kLogitTokens];
+#pragma unroll
+    for (int j = 0; j < kLogitTokens; ++j) acc[j] = 0.f;
+
+    const uint4* grow = reinterpret_cast<const uint4*>(gate + static_cast<size_t>(e) * hidden);
+    const int vectors = hidden / 8;
+    for (int v = lane; v < vectors; v += 32) {
+        float gv[8];
+        widen8<kBf16>(__ldg(grow + v), gv);
+#pragma unroll
+        for (int j = 0; j < kLogitTokens; ++j) {
+            if (j < nt) {
+                float xv[8];
+                widen8<kBf16>(__ldg(reinterpret_cast<const uint4*>(
+                                        x + static_cast<size_t>(t0 + j) * x_stride) + v), xv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[j] = fmaf(gv[i], xv[i], acc[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kLogitTokens; ++j) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xFFFFFFFFu, acc[j], off);
+        if (lane == 0 && j < nt) logits[static_cast<size_t>(t0 + j) * experts + e] = acc[j];
+    }
+}
+
+__device__ __forceinline__ float score_of(float logit, int score_fn) {
+    if (score_fn == AEON_B200_SCORE_SIGMOID) return 1.0f / (1.0f + expf(-logit));
+    // sqrt(softplus), softplus with the threshold of 20 the reference model uses.
+    return logit > 20.0f ? sqrtf(logit) : sqrtf(log1pf(expf(logit)));
+}
+
+constexpr int kSelectWarps = 4;
+
+__global__ void __launch_bounds__(kSelectWarps * 32)
+router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                     const int64_t* __restrict__ hash_table, const int32_t* __restrict__ token_ids,
+                     int tokens, int experts, int top_k, int score_fn, int renormalize,
+                     float scaling, float* __restrict__ out_weights, int32_t* __restrict__ out_ids) {
+    extern __shared__ float keys[];   // [kSelectWarps][experts]
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int token = blockIdx.x * kSelectWarps + warp;
+    if (token >= tokens) return;
+    const float* row = logits + static_cast<size_t>(token) * experts;
+    float* key = keys + warp * experts;
+    float* w_out = out_weights + static_cast<size_t>(token) * top_k;
+    int32_t* id_out = out_ids + static_cast<size_t>(token) * top_k;
+
+    float my_weight = 0.f;   // lane k keeps the k-th selected score
+    int my_id = -1;
+
+    if (hash_table != nullptr && token_ids != nullptr) {
+        if (lane < top_k) {
+            my_id = static_cast<int32_t>(hash_table[static_cast<size_t>(token_ids[token]) * top_k + lane]);
+            my_weight = score_of(row[my_id], score_fn);
+        }
+    } else {
+        for (int e = lane; e < experts; e += 32)
+            key[e] = (bias != nullptr) ? score_of(row[e], score_fn) + bias[e] : row[e];
+        __syncwarp();
+        for (int k = 0; k < top_k; ++k) {
+            float best = -INFINITY;
+            int best_e = 0x7FFFFFFF;
+            for (int e = lane; e < experts; e += 32) {
+                const float v = key[e];
+                if (v > best) { best = v; best_e = e; }   // ascending e: first maximum wins
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+                const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, off);
+                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+            }
+            if (best_e == 0x7FFFFFFF) best_e = 0;   // every key was NaN or -inf
+            if (lane == k) {
+                my_id = best_e;
+                my_weight = score_of(row[best_e], score_fn);
+            }
+            if (lane == (best_e & 31)) key[best_e] = -INFINITY;
+            __syncwarp();
+            // a key of -inf can be re-selected only when fewer than top_k finite keys exist
+        }
+    }
+
+    float sum = (lane < top_k) ? my_weight : 0.f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+    if (lane < top_k) {
+        float w = my_weight;
+        if (renormalize) w = w / sum;
+        w *= scaling;
+        w_out[lane] = w;
+        id_out[lane] = my_id;
+    }
+}
+
+}  // namespace
+
+void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const void* gate,
+                   const float* bias, const int64_t* hash_table, const int32_t* token_ids,
+                   int tokens, float* topk_weights, int32_t* topk_ids, float* logits_out,
+                   cudaStream_t stream) {
+    const aeon_b200_moe_config& cfg = ctx->cfg;
+    require(x && gate && topk_weights && topk_ids, "aeon_b200_router_topk: null pointer argument");
+    require(tokens > 0, "aeon_b200_router_topk: tokens must be positive");
+    require(logits_out != nullptr || tokens <= ctx->max_tokens,
+            "aeon_b200_router_topk: tokens exceed the context's max_tokens and no logits buffer was given");
+    require(x_stride >= cfg.hidden && x_stride % 8 == 0,
+            "aeon_b200_router_topk: x_stride must be >= hidden and a multiple of 8");
+    require(cfg.top_k <= 32, "aeon_b200_router_topk: top_k above 32 is not supported");
+    float* logits = logits_out != nullptr ? logits_out : ctx->d_logits;
+
+    const dim3 grid((cfg.experts + kLogitWarps - 1) / kLogitWarps,
+                    (tokens + kLogitTokens - 1) / kLogitTokens);
+    if (cfg.act_dtype == AEON_B200_BF16) {
+        router_logits_kernel<true><<<grid, kLogitWarps * 32, 0, stream>>>(
+            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
+            cfg.experts, cfg.hidden, logits);
+    } else {
+        router_logits_kernel<false><<<grid, kLogitWarps * 32, 0, stream>>>(
+            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
+            cfg.experts, cfg.hidden, logits);
+    }
+    AEON_CUDA_CHECK(cudaGetLastError());
+    const size_t smem = static_cast<size_t>(kSelectWarps) * cfg.experts * sizeof(float);
+    router_select_kernel<<<(tokens + kSelectWarps - 1) / kSelectWarps, kSelectWarps * 32, smem, stream>>>(
+        logits, bias, hash_table, token_ids, tokens, cfg.experts, cfg.top_k, cfg.score_fn,
+        cfg.renormalize, cfg.routed_scaling, topk_weights, topk_ids);
+    AEON_CUDA_CHECK(cudaGetLastError());
+    ctx->launches += 2;
+}
+
+}  // namespace aeon_b200
