@@ -1,0 +1,333 @@
+#!/usr/bin/env python
+"""Benchmark of the routed-expert MoE decode path (benchmark configuration 3's stack: 8 MoE
+layers of the configuration-0 shape, decode batch 128; at one GPU every layer's 256 experts
+are resident, which is configuration 1's layer at batch 128 repeated over 8 layers).
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torchrun)
+    python bench.py --impl reference ...                   (the CPU oracle, timed on host cores)
+
+A step = one pass of the stack: per layer, router top-k -> shared expert -> routed experts
+(dual W4A16 product + SwiGLU, W2, slot-order accumulate). Inputs are synthetic and seeded
+(int4 uniform, fp16 scales |N(0,0.02)|+1e-4, bf16 N(0,1) activations, bf16 N(0,0.01) gate).
+`value` is measured with inputs resident in HBM; `e2e` through the same calls with pinned
+host buffers and the copies inside the timed region. One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "project-aeon_b200"))
+
+LAYERS = 8
+BATCH = 128
+SEED = 0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/8/32/128 sweep")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ----------------------------------------------------------------------------------------
+# Clock sampling during the timed region
+# ----------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.proc = None
+        self.device_index = device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.device_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------
+# CPU oracle leg (reported baseline and the --impl reference arm)
+# ----------------------------------------------------------------------------------------
+def cpu_oracle_tokens_per_s(layers: int, repeats: int = 1):
+    """Times the CPU oracle on one token through one layer (router + 8 routed experts +
+    shared expert + combine) with every host thread it can use, and scales to the stack."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import numpy as np
+    import aeon_b200
+    from aeon_b200 import synth
+    import oracle_py as oracle
+
+    cfg = aeon_b200.preset("baseline")
+    la = oracle.layout_args(cfg)
+    scale_table = synth.half_normal_table(0.02, 1e-4, 4096, dtype=aeon_b200.F16)
+    dense_table = synth.half_normal_table(0.02, 0.0, 4096, dtype=cfg.act_dtype)
+    rng = np.random.default_rng([SEED, 0, 0x6A7E])
+    gate_bits = synth.normal_bits(rng, (cfg.experts, cfg.hidden), 0.01, cfg.act_dtype)
+    x_bits = synth.normal_bits(np.random.default_rng([SEED, 0xAC7]), (1, cfg.hidden), 1.0, cfg.act_dtype)
+    n = cfg.hidden * cfg.intermediate
+    shared = [oracle.synth_dense16(n, SEED, 0, s, dense_table) for s in range(3)]
+    w1 = shared[0].reshape(cfg.intermediate, cfg.hidden)
+    w3 = shared[1].reshape(cfg.intermediate, cfg.hidden)
+    w2 = shared[2].reshape(cfg.hidden, cfg.intermediate)
+    x = synth.from_bits16(x_bits, cfg.act_dtype)[0]
+    # payload generation is input preparation, not the path: done before the clock starts
+    logits0 = oracle.router_logits_f64(gate_bits, cfg.act_dtype, x_bits, cfg.act_dtype)
+    ids0, _, _ = oracle.router_topk(logits0, None, cfg.top_k, cfg.routed_scaling, cfg.score_fn)
+    payloads = {int(e): oracle.synth_expert_payload(la, SEED, 0, int(e), scale_table) for e in ids0[0]}
+
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        logits = oracle.router_logits_f64(gate_bits, cfg.act_dtype, x_bits, cfg.act_dtype)
+        ids, w, _ = oracle.router_topk(logits, None, cfg.top_k, cfg.routed_scaling, cfg.score_fn)
+        outs = np.stack([oracle.expert_ffn(la, payloads[int(e)], x, cfg.swiglu_limit) for e in ids[0]])
+        sh = oracle.dense_ffn(w1, w3, w2, cfg.act_dtype, x, cfg.swiglu_limit)
+        oracle.moe_combine(outs, w[0], sh)
+        best = min(best, time.perf_counter() - t0)
+    seconds_per_layer_token = best
+    return 1.0 / (seconds_per_layer_token * layers), seconds_per_layer_token, oracle.threads()
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_oracle_tokens_per_s(args.layers, 1)
+    tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, max(1, min(args.steps, 3)))
+    sample = (f"1 token through 1 layer (router + 8 routed experts + shared expert + combine) "
+              f"= {sec:.3f} s on {cores} threads, scaled x{args.layers} layers; fp64 oracle")
+    line = {
+        "impl": "reference", "metric": "moe_decode_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * args.layers * args.batch * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, n_gpus):
+    return {
+        "workload": (f"cfg3 stack: {args.layers} MoE layers x decode batch {args.batch}, hidden 7168, "
+                     "intermediate 2048, 256 routed experts top-8 + 1 shared expert, W4A16 group 128, "
+                     "bf16 activations, sigmoid router (cfg1 layer at batch 128 per layer)"),
+        "layers": args.layers, "batch": args.batch,
+        "parallelism": "single GPU, all experts resident" if n_gpus == 1 else f"expert-parallel ep{n_gpus}",
+        "l2_policy": "inputs larger than L2: every layer streams >= 5.7 GB of distinct expert weights",
+    }
+
+
+# ----------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import numpy as np
+    import torch
+    import aeon_b200
+    from aeon_b200 import synth, stack
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    cfg = aeon_b200.preset("baseline")
+    model = stack.MoeStack(cfg, layers=args.layers, max_tokens=args.batch, seed=SEED,
+                           device=local_rank, rank=rank, world=world, dist=dist)
+    T, H = args.batch, cfg.hidden
+    if T % world:
+        raise SystemExit("--batch must divide by the number of GPUs")
+    TL = T // world          # tokens owned by this rank
+    x_bits = synth.normal_bits(np.random.default_rng([SEED, 0xAC7]), (args.layers, T, H), 1.0, cfg.act_dtype)
+    x_bits = np.ascontiguousarray(x_bits[:, rank * TL:(rank + 1) * TL])
+    x_host = torch.from_numpy(x_bits.view(np.int16)).view(torch.bfloat16).pin_memory()
+    x_dev = x_host.cuda(non_blocking=True)
+    out_dev = torch.empty(args.layers, TL, H, dtype=torch.float32, device="cuda")
+    out_host = torch.empty(args.layers, TL, H, dtype=torch.float32).pin_memory()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        model.forward(x_dev, out_dev)
+
+    def step_e2e():
+        x_dev.copy_(x_host, non_blocking=True)
+        model.forward(x_dev, out_dev)
+        out_host.copy_(out_dev, non_blocking=True)
+
+    def timed(fn, steps, warmup, sample_clocks=False):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        if sampler:
+            sampler.start()
+            time.sleep(0.15)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        barrier()
+        ms = start.elapsed_time(end)
+        clocks = sampler.stop() if sampler else None
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, clocks
+
+    warmup = max(args.warmup, 3)
+    model.forward(x_dev, out_dev, collect_stats=True)     # untimed: routing statistics
+    model.ctx.check()
+    launches_before = model.launches
+    model.set_timing(True)
+    ms, clocks = timed(step_resident, args.steps, warmup, sample_clocks=True)
+    kernel_times = model.kernel_times()
+    model.set_timing(False)
+    launches_per_step = (model.launches - launches_before) / (args.steps + warmup)
+    ms_step = ms / args.steps
+    tokens_per_s = T / (ms_step * 1e-3)
+
+    ms_e2e, _ = timed(step_e2e, args.steps, 3)
+    e2e_tokens_per_s = T / (ms_e2e / args.steps * 1e-3)
+
+    # ---- roofline of the dominant kernel (W1/W3 dual product + SwiGLU) -------------------
+    stats = model.routing_stats()             # per layer: distinct experts (this rank)
+    lay = aeon_b200.expert_layout(cfg)
+    w13_bytes_per_expert = 2 * (lay.w13_packed_bytes + lay.w13_scale_bytes)
+    w2_bytes_per_expert = lay.w2_packed_bytes + lay.w2_scale_bytes
+    mean_distinct = float(np.mean([s["distinct"] for s in stats]))
+    mean_draws = float(np.mean([s["draws"] for s in stats]))
+    mean_tokens = float(np.mean([s["tokens"] for s in stats]))
+    bytes_a = mean_distinct * w13_bytes_per_expert + mean_tokens * H * 2 + mean_draws * cfg.intermediate * 4
+    bytes_b = mean_distinct * w2_bytes_per_expert + mean_draws * cfg.intermediate * 4 + mean_draws * H * 4
+    (ms_a, n_a), (ms_b, n_b) = kernel_times
+    peaks = {}
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            peaks = json.load(f)
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    avg_a_ms = ms_a / max(n_a, 1)
+    avg_b_ms = ms_b / max(n_b, 1)
+    achieved_a = bytes_a / (avg_a_ms * 1e-3) / 1e9 if n_a else None
+    achieved_b = bytes_b / (avg_b_ms * 1e-3) / 1e9 if n_b else None
+    step_bytes = args.layers * (bytes_a + bytes_b + cfg.experts * H * 2 + 3 * H * cfg.intermediate * 2)
+
+    line = {
+        "metric": "moe_decode_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights x fp16 scales, f16 MMA operands, f32 accumulate (W4A16)",
+        "data": "synthetic", "config": workload_config(args, world), "clocks": clocks,
+        "e2e": {"value": e2e_tokens_per_s, "unit": "tokens/s",
+                "h2d_bytes_per_step": int(x_host.numel() * 2 * world),
+                "d2h_bytes_per_step": int(out_host.numel() * 4 * world)},
+        "gpu_launches": int(round(launches_per_step * args.steps)),
+        "gpu_launches_per_step": launches_per_step,
+        "roofline": {
+            "bound": "hbm", "kernel": "moe_w13_swiglu_kernel", "achieved": achieved_a, "peak": peak_gbs,
+            "unit": "GB/s", "frac": (achieved_a / peak_gbs) if achieved_a else None,
+            "peak_source": peak_kind, "traffic": None,
+            "algorithmic_bytes_per_launch": bytes_a, "avg_launch_ms": avg_a_ms, "launches_timed": n_a,
+            "second_kernel": {"kernel": "moe_w2_accum_kernel", "achieved": achieved_b,
+                              "frac": (achieved_b / peak_gbs) if achieved_b else None,
+                              "algorithmic_bytes_per_launch": bytes_b, "avg_launch_ms": avg_b_ms},
+            "whole_step": {"algorithmic_bytes": step_bytes,
+                           "achieved": step_bytes / (ms_step * 1e-3) / 1e9,
+                           "frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak_gbs},
+            "frac_of_nominal_8TBs": (achieved_a / 8000.0) if achieved_a else None,
+            "mean_distinct_experts_per_layer": mean_distinct,
+        },
+    }
+
+    if world == 1 and not args.no_sweep:
+        line["decode_sweep"] = model.batch_sweep([1, 8, 32, 128], x_dev, out_dev, peak_gbs,
+                                                 iters=max(10, args.steps))
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, 1)
+        line["cpu_baseline"] = {
+            "value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": (f"1 token through 1 layer (router + 8 routed experts + shared expert + combine) "
+                       f"= {sec:.3f} s on {cores} threads, scaled x{args.layers} layers; fp64 oracle")}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

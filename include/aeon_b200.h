@@ -165,12 +165,25 @@ int aeon_b200_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, 
  * aeon_moe_fused_gate_up_kernel, aeon_moe_fused_w2_contrib_kernel and
  * moe_accumulate_fixed_order_kernel. `pool_base` is the expert pool slab;
  * slot_of_expert[experts] maps a routed expert id to its slot (-1: absent, which
- * raises the context's error flag). Each distinct expert's weights are read once
- * per call. tokens <= the context's max_tokens. */
+ * raises the context's error flag, unless AEON_B200_DECODE_SKIP_ABSENT is set in `flags`:
+ * then draws of absent experts contribute nothing, which is the expert-parallel case
+ * where this GPU holds a slice of the experts and moe_accum is a partial sum). Each
+ * distinct expert's weights are read once per call. tokens <= the context's max_tokens. */
+enum { AEON_B200_DECODE_SKIP_ABSENT = 1 };
 int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                          const void* x, int64_t x_stride, const int32_t* topk_ids,
                          const float* topk_weights, int tokens, float* moe_accum,
-                         int64_t accum_stride, void* stream);
+                         int64_t accum_stride, uint32_t flags, void* stream);
+
+/* Expert-parallel combine: out[t, :] += sum over r = 0..ranks-1, in rank order, of
+ * partials[r, t, :] (fp32; partials is [ranks, tokens, hidden] dense, as an equal-split
+ * all-to-all delivers it). The fixed order makes the result independent of arrival order.
+ * The reference has no expert parallelism (it is deferred:
+ * plans-and-docs/specs-and-requirements/multi-gpu/MULTI_GPU_REQUIREMENTS.md:103); the
+ * order rule follows its fixed-slot-order accumulate
+ * (src/platform/ops/moe_accumulate.hpp:73-92). */
+int aeon_b200_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks,
+                         int tokens, int hidden, void* stream);
 
 /* Statistics of the last decode/prefill call of this context (host values read
  * back after a synchronise): distinct experts touched and work-list entries. */

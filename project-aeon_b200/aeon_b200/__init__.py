@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libaeon_b200.so")
 
 F16, BF16 = 0, 1
 SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID = 0, 1
+DECODE_SKIP_ABSENT = 1
 
 STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "LOGIC", 3: "CUDA", 4: "OUT_OF_RANGE",
                 5: "TIMEOUT", 6: "UNSUPPORTED"}
@@ -31,6 +32,7 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_router_topk", "aeon_b200_expert_permutation", "aeon_b200_shared_expert",
     "aeon_b200_moe_decode", "aeon_b200_ctx_last_stats", "aeon_b200_synth_fill_experts",
     "aeon_b200_synth_fill_dense16", "aeon_b200_ctx_set_timing", "aeon_b200_ctx_kernel_times",
+    "aeon_b200_ep_combine",
 ]
 
 
@@ -104,7 +106,8 @@ def lib() -> ctypes.CDLL:
     L.aeon_b200_shared_expert.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                           c_int, c_void_p, c_int64, c_void_p]
     L.aeon_b200_moe_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
-                                       c_void_p, c_int, c_void_p, c_int64, c_void_p]
+                                       c_void_p, c_int, c_void_p, c_int64, c_uint32, c_void_p]
+    L.aeon_b200_ep_combine.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]
     L.aeon_b200_synth_fill_experts.argtypes = [POINTER(MoeConfig), c_void_p, c_uint32, c_uint32,
                                                c_uint64, c_uint32, c_uint32, c_void_p, c_uint32,
                                                c_void_p]
@@ -271,7 +274,16 @@ class Context:
                                             x.stride(0), x.shape[0], _ptr(moe_accum),
                                             moe_accum.stride(0), _stream()))
 
-    def moe_decode(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum):
+    def moe_decode(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum,
+                   skip_absent: bool = False):
         check(lib().aeon_b200_moe_decode(self._h, c_void_p(pool_base), _ptr(slot_of_expert), _ptr(x),
                                          x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
-                                         _ptr(moe_accum), moe_accum.stride(0), _stream()))
+                                         _ptr(moe_accum), moe_accum.stride(0),
+                                         DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
+
+
+def ep_combine(out, partials) -> None:
+    """out[t, :] += sum_r partials[r, t, :] in rank order (fp32)."""
+    ranks, tokens, hidden = partials.shape
+    check(lib().aeon_b200_ep_combine(_ptr(out), out.stride(0), _ptr(partials), ranks, tokens, hidden,
+                                     _stream()))

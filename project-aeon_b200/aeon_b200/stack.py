@@ -1,0 +1,189 @@
+"""A stack of MoE layers on one GPU or expert-parallel over the GPUs of one box.
+
+This is the call a user of the library makes for a batch of decode tokens:
+
+    model = MoeStack(cfg, layers=8, max_tokens=128, seed=0, rank=r, world=R, dist=dist)
+    model.forward(x, out)        # x[layers, tokens_local, H] 16-bit, out fp32
+
+Per layer: router top-k -> shared expert (the accumulator's initial value) -> routed
+experts. Weights are synthetic (see synth.py); a real model uploads payloads into the pools.
+
+Expert parallelism (world > 1). Expert e lives on rank e // (E / world); gate and shared
+expert are replicated; every rank owns tokens_local = tokens / world tokens.
+  dispatch  all-gather of the activation rows, so every rank holds the whole batch. At decode
+            batch sizes a padded equal-split all-to-all moves exactly the same bytes, and
+            the gather needs no count exchange and no host synchronisation. The router then
+            runs replicated on identical inputs, so routing is bit-identical on every rank
+            and needs no exchange either.
+  compute   each rank runs only its resident experts (absent experts are skipped) into a
+            zeroed fp32 partial [tokens, H].
+  combine   equal-split all-to-all of the partial rows to their owners, then the owners add
+            the `world` partial slices in rank order to their shared-expert rows: a fixed
+            summation order, independent of arrival order.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+import aeon_b200
+from aeon_b200 import synth
+
+
+def _torch_bits(bits: np.ndarray, dtype: int, device):
+    import torch
+    t = torch.from_numpy(bits.view(np.int16).copy()).to(device)
+    return t.view(torch.bfloat16 if dtype == aeon_b200.BF16 else torch.float16)
+
+
+class MoeLayerWeights:
+    """Device-resident weights of one layer for one rank's expert slice."""
+
+    def __init__(self, cfg, layer: int, seed: int, device: int, first_expert: int, count: int,
+                 tables):
+        import torch
+        dev = f"cuda:{device}"
+        scale_table, dense_table = tables
+        self.pool = aeon_b200.ExpertPool(cfg, count, device)
+        self.pool.fill_synthetic(0, count, seed, layer, first_expert, scale_table)
+        slot_of = np.full(cfg.experts, -1, dtype=np.int32)
+        slot_of[first_expert:first_expert + count] = np.arange(count, dtype=np.int32)
+        self.slot_of = torch.from_numpy(slot_of).to(dev)
+        rng = np.random.default_rng([seed, layer, 0x6A7E])
+        self.gate_bits = synth.normal_bits(rng, (cfg.experts, cfg.hidden), 0.01, cfg.act_dtype)
+        self.gate = _torch_bits(self.gate_bits, cfg.act_dtype, dev)
+        n = cfg.hidden * cfg.intermediate
+        self.shared = []
+        for stream_id in range(3):
+            t = torch.empty(n, dtype=torch.int16, device=dev)
+            aeon_b200.synth_fill_dense16(t, seed, layer, stream_id, dense_table)
+            self.shared.append(t)
+
+
+class MoeStack:
+    def __init__(self, cfg, layers: int, max_tokens: int, seed: int = 0, device: int = 0,
+                 rank: int = 0, world: int = 1, dist=None):
+        import torch
+        if world > 1 and (cfg.experts % world or max_tokens % world):
+            raise aeon_b200.AeonError(1, "experts and tokens must divide by the number of ranks")
+        self.cfg, self.layers, self.world, self.rank, self.dist = cfg, layers, world, rank, dist
+        self.device = device
+        self.max_tokens = max_tokens
+        dev = f"cuda:{device}"
+        scale_np = synth.half_normal_table(0.02, 1e-4, 4096, dtype=aeon_b200.F16)
+        dense_np = synth.half_normal_table(0.02, 0.0, 4096, dtype=cfg.act_dtype)
+        tables = (torch.from_numpy(scale_np.view(np.int16).copy()).to(dev),
+                  torch.from_numpy(dense_np.view(np.int16).copy()).to(dev))
+        self.scale_table_np, self.dense_table_np = scale_np, dense_np
+        per_rank = cfg.experts // world
+        self.first_expert = rank * per_rank
+        self.weights = [MoeLayerWeights(cfg, l, seed, device, self.first_expert, per_rank, tables)
+                        for l in range(layers)]
+        self.ctx = aeon_b200.Context(cfg, device, max_tokens)
+        self._stats = [dict(distinct=0, draws=0, tokens=0) for _ in range(layers)]
+        if world > 1:
+            H = cfg.hidden
+            self.x_all = torch.empty(max_tokens, H, dtype=self.weights[0].gate.dtype, device=dev)
+            self.partial = torch.empty(max_tokens, H, dtype=torch.float32, device=dev)
+            self.recv = torch.empty(world, max_tokens // world, H, dtype=torch.float32, device=dev)
+        self._extra_launches = 0
+        torch.cuda.synchronize(device)
+
+    # -- bookkeeping ----------------------------------------------------------------------
+    @property
+    def launches(self) -> int:
+        return self.ctx.launches + self._extra_launches
+
+    def set_timing(self, enabled: bool) -> None:
+        self.ctx.set_timing(enabled)
+
+    def kernel_times(self):
+        return self.ctx.kernel_times()
+
+    def routing_stats(self):
+        """Per layer: distinct resident experts touched, draws served here, tokens seen."""
+        return self._stats
+
+    # -- the step -------------------------------------------------------------------------
+    def forward(self, x, out, collect_stats: bool = False):
+        """x[layers, tokens_local, H] 16-bit -> out[layers, tokens_local, H] fp32."""
+        for l in range(self.layers):
+            self.forward_layer(l, x[l], out[l], collect_stats)
+
+    def forward_layer(self, l: int, x, out, collect_stats: bool = False, return_routing: bool = False):
+        w = self.weights[l]
+        ctx = self.ctx
+        if self.world == 1:
+            weights, ids = ctx.router_topk(x, w.gate)
+            ctx.shared_expert(w.shared[0], w.shared[1], w.shared[2], x, out)
+            ctx.moe_decode(w.pool.base, w.slot_of, x, ids, weights, out)
+            tokens_seen = x.shape[0]
+        else:
+            tl = x.shape[0]
+            tokens_seen = tl * self.world
+            x_all = self.x_all[:tokens_seen]
+            self.dist.all_gather_into_tensor(x_all, x)                     # dispatch
+            weights, ids = ctx.router_topk(x_all, w.gate)                  # replicated routing
+            ctx.shared_expert(w.shared[0], w.shared[1], w.shared[2], x, out)
+            partial = self.partial[:tokens_seen]
+            partial.zero_()
+            ctx.moe_decode(w.pool.base, w.slot_of, x_all, ids, weights, partial, skip_absent=True)
+            recv = self.recv[:, :tl]
+            if recv.is_contiguous():
+                self.dist.all_to_all_single(recv, partial)                 # combine
+            else:
+                tmp = recv.contiguous()
+                self.dist.all_to_all_single(tmp, partial)
+                recv = tmp
+            aeon_b200.ep_combine(out, recv)
+            self._extra_launches += 2
+        if collect_stats:
+            distinct, _ = ctx.last_stats()
+            flat = ids.flatten()
+            local = ((flat >= self.first_expert) &
+                     (flat < self.first_expert + self.cfg.experts // self.world)).sum().item()
+            self._stats[l] = dict(distinct=distinct, draws=int(local), tokens=tokens_seen)
+        if return_routing:
+            return weights, ids
+
+    # -- configuration-1 sweep: one layer at batch 1/8/32/128, rotating over the layers so
+    #    consecutive iterations stream different weights (a batch-1 step touches ~180 MB,
+    #    the order of the L2 capacity) ----------------------------------------------------
+    def batch_sweep(self, batches, x, out, peak_gbs: float, iters: int = 20):
+        import torch
+        cfg = self.cfg
+        lay = aeon_b200.expert_layout(cfg)
+        expert_bytes = 2 * (lay.w13_packed_bytes + lay.w13_scale_bytes) + lay.w2_packed_bytes + lay.w2_scale_bytes
+        results = []
+        for b in batches:
+            if b > x.shape[1]:
+                continue
+            distinct = []
+            for l in range(self.layers):          # warm-up pass, also collects the routing stats
+                self.forward_layer(l, x[l, :b], out[l, :b], collect_stats=True)
+                distinct.append(self._stats[l]["distinct"])
+            torch.cuda.synchronize()
+            total_iters = max(iters, self.layers)
+            self.ctx.set_timing(True)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(total_iters):
+                l = i % self.layers
+                self.forward_layer(l, x[l, :b], out[l, :b])
+            end.record()
+            torch.cuda.synchronize()
+            (ms_a, n_a), (ms_b, n_b) = self.ctx.kernel_times()
+            self.ctx.set_timing(False)
+            us_layer = start.elapsed_time(end) * 1e3 / total_iters
+            mean_d = float(np.mean(distinct))
+            routed_bytes = mean_d * expert_bytes
+            kernel_us = (ms_a + ms_b) * 1e3 / max(n_a, 1)
+            results.append({
+                "batch": b, "us_per_layer": us_layer, "tokens_per_s_per_layer": b / (us_layer * 1e-6),
+                "distinct_experts": mean_d, "routed_weight_bytes": routed_bytes,
+                "routed_kernels_us": kernel_us,
+                "routed_kernels_gbs": routed_bytes / (kernel_us * 1e-6) / 1e9,
+                "routed_kernels_frac_of_peak": routed_bytes / (kernel_us * 1e-6) / 1e9 / peak_gbs,
+                "layer_gbs_incl_router_shared": (routed_bytes + cfg.experts * cfg.hidden * 2 +
+                                                 3 * cfg.hidden * cfg.intermediate * 2) / (us_layer * 1e-6) / 1e9,
+            })
+        return results

@@ -421,7 +421,7 @@ int aeon_b200_expert_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, in
         DeviceGuard guard(ctx->device);
         launch_permutation(ctx, topk_ids, tokens, slots, experts, expert_offsets, token_indices,
                            draw_indices, weights, weights_by_position, nullptr, nullptr, nullptr,
-                           as_stream(stream));
+                           false, as_stream(stream));
     });
 }
 
@@ -439,12 +439,19 @@ int aeon_b200_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, 
 int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                          const void* x, int64_t x_stride, const int32_t* topk_ids,
                          const float* topk_weights, int tokens, float* moe_accum,
-                         int64_t accum_stride, void* stream) {
+                         int64_t accum_stride, uint32_t flags, void* stream) {
     return guarded([&] {
         require(ctx != nullptr, "aeon_b200_moe_decode: null context");
         DeviceGuard guard(ctx->device);
         launch_moe_decode(ctx, pool_base, slot_of_expert, x, x_stride, topk_ids, topk_weights, tokens,
-                          moe_accum, accum_stride, as_stream(stream));
+                          moe_accum, accum_stride, flags, as_stream(stream));
+    });
+}
+
+int aeon_b200_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks, int tokens,
+                         int hidden, void* stream) {
+    return guarded([&] {
+        launch_ep_combine(out, out_stride, partials, ranks, tokens, hidden, as_stream(stream));
     });
 }
 

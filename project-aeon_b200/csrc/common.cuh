@@ -137,11 +137,13 @@ void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens,
                         int experts, int32_t* expert_offsets, int32_t* token_indices,
                         int32_t* draw_indices, const float* weights, float* weights_by_position,
                         const int32_t* slot_of_expert, WorkEntry* entries, int32_t* counts,
-                        cudaStream_t stream);
+                        bool skip_absent, cudaStream_t stream);
 void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                        const void* x, int64_t x_stride, const int32_t* topk_ids,
                        const float* topk_weights, int tokens, float* moe_accum,
-                       int64_t accum_stride, cudaStream_t stream);
+                       int64_t accum_stride, uint32_t flags, cudaStream_t stream);
+void launch_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks,
+                       int tokens, int hidden, cudaStream_t stream);
 void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
                           const void* x, int64_t x_stride, int tokens, float* moe_accum,
                           int64_t accum_stride, cudaStream_t stream);

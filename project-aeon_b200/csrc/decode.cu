@@ -61,6 +61,8 @@ struct DecodeParams {
     const int32_t* draw_idx;
     const float* wpos;
     const int32_t* topk_ids;
+    const int32_t* slot_of;
+    int skip_absent;
     int experts;
     __half* hid_hi;
     __half* hid_lo;
@@ -545,7 +547,7 @@ moe_w2_accum_kernel(const DecodeParams p) {
                 for (int slot = 0; slot < p.top_k; ++slot) {
                     const int draw = token * p.top_k + slot;
                     const int id = p.topk_ids[draw];
-                    if (id >= 0 && id < p.experts)
+                    if (id >= 0 && id < p.experts && !(p.skip_absent && p.slot_of[id] < 0))
                         a += __ldcg(&p.contrib[static_cast<size_t>(draw) * p.H + row]);
                 }
                 p.accum[static_cast<size_t>(token) * p.accum_stride + row] = a;
@@ -606,12 +608,42 @@ void launch_decode_kernels(aeon_b200_ctx* ctx, const DecodeParams& p, cudaStream
     ctx->launches += 2;
 }
 
+__global__ void ep_combine_kernel(float* __restrict__ out, int64_t out_stride,
+                                  const float* __restrict__ partials, int ranks, int tokens,
+                                  int hidden) {
+    const int64_t total = static_cast<int64_t>(tokens) * hidden / 4;
+    const int64_t plane = static_cast<int64_t>(tokens) * hidden / 4;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t token = (i * 4) / hidden;
+        const int64_t col = (i * 4) - token * hidden;
+        float4* dst = reinterpret_cast<float4*>(out + token * out_stride + col);
+        float4 a = *dst;
+        for (int r = 0; r < ranks; ++r) {
+            const float4 v = reinterpret_cast<const float4*>(partials)[r * plane + i];
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        *dst = a;
+    }
+}
+
 }  // namespace
+
+void launch_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks,
+                       int tokens, int hidden, cudaStream_t stream) {
+    require(out && partials, "aeon_b200_ep_combine: null pointer argument");
+    require(ranks > 0 && tokens > 0 && hidden > 0 && hidden % 4 == 0 && out_stride % 4 == 0,
+            "aeon_b200_ep_combine: hidden and out_stride must be multiples of 4");
+    const int64_t total = static_cast<int64_t>(tokens) * hidden / 4;
+    const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 2048));
+    ep_combine_kernel<<<blocks, 256, 0, stream>>>(out, out_stride, partials, ranks, tokens, hidden);
+    AEON_CUDA_CHECK(cudaGetLastError());
+}
 
 void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                        const void* x, int64_t x_stride, const int32_t* topk_ids,
                        const float* topk_weights, int tokens, float* moe_accum,
-                       int64_t accum_stride, cudaStream_t stream) {
+                       int64_t accum_stride, uint32_t flags, cudaStream_t stream) {
     const aeon_b200_moe_config& cfg = ctx->cfg;
     require(pool_base && slot_of_expert && x && topk_ids && topk_weights && moe_accum,
             "aeon_b200_moe_decode: null pointer argument");
@@ -636,7 +668,8 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     // 2. draws sorted by expert + work list
     launch_permutation(ctx, topk_ids, tokens, cfg.top_k, cfg.experts, ctx->d_offsets,
                        ctx->d_token_idx, ctx->d_draw_idx, topk_weights, ctx->d_wpos,
-                       slot_of_expert, ctx->d_entries, ctx->d_counts, stream);
+                       slot_of_expert, ctx->d_entries, ctx->d_counts,
+                       (flags & AEON_B200_DECODE_SKIP_ABSENT) != 0, stream);
 
     // 3. the two streaming kernels
     DecodeParams p{};
@@ -656,6 +689,8 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     p.draw_idx = ctx->d_draw_idx;
     p.wpos = ctx->d_wpos;
     p.topk_ids = topk_ids;
+    p.slot_of = slot_of_expert;
+    p.skip_absent = (flags & AEON_B200_DECODE_SKIP_ABSENT) ? 1 : 0;
     p.experts = cfg.experts;
     p.hid_hi = ctx->d_hidden_hi;
     p.hid_lo = ctx->d_hidden_lo;

@@ -52,7 +52,7 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
                           const float* __restrict__ weights, float* __restrict__ wpos,
                           const int32_t* __restrict__ slot_of, WorkEntry* __restrict__ entries,
                           int32_t* __restrict__ counts, int32_t* __restrict__ tile_done,
-                          int tile_done_n) {
+                          int tile_done_n, int skip_absent) {
     extern __shared__ int hist[];   // [walk_warps][experts]
     __shared__ int warp_sums[32];
     __shared__ int scan_total;
@@ -124,14 +124,18 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
 
     // Decode work list: one entry per (expert, group of up to 8 of its positions).
     if (entries != nullptr) {
-        const int chunks = (tid < experts) ? (total + 7) / 8 : 0;
+        const int my_slot = (tid < experts) ? (slot_of != nullptr ? slot_of[tid] : tid) : -1;
+        // An expert without a pool slot gets no entry when absent experts are skipped
+        // (expert-parallel slice); otherwise it keeps its entries and the kernels flag it.
+        const bool listed = tid < experts && !(skip_absent && my_slot < 0);
+        const int chunks = listed ? (total + 7) / 8 : 0;
         const int ebase = block_exclusive_scan(chunks, warp_sums, &scan_total);
         const int n_entries = scan_total;
-        const int distinct = block_exclusive_scan((tid < experts && total > 0) ? 1 : 0, warp_sums,
+        const int distinct = block_exclusive_scan((listed && total > 0) ? 1 : 0, warp_sums,
                                                   &scan_total);
         (void)distinct;
-        if (tid < experts) {
-            const int slot = slot_of != nullptr ? slot_of[tid] : tid;
+        if (listed) {
+            const int slot = my_slot;
             for (int c = 0; c < chunks; ++c) {
                 WorkEntry w;
                 w.expert = tid;
@@ -155,13 +159,16 @@ void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens,
                         int experts, int32_t* expert_offsets, int32_t* token_indices,
                         int32_t* draw_indices, const float* weights, float* weights_by_position,
                         const int32_t* slot_of_expert, WorkEntry* entries, int32_t* counts,
-                        cudaStream_t stream) {
-    require(topk_ids && expert_offsets && token_indices && draw_indices,
-            "aeon_b200_expert_permutation: null pointer argument");
+                        bool skip_absent, cudaStream_t stream) {
     require(tokens >= 0 && slots > 0, "aeon_b200_expert_permutation: bad token or slot count");
+    // An empty chunk is legal (the reference's permutation gate runs T = 0): only the
+    // offsets are written then, so the per-draw arrays may be absent.
+    require(expert_offsets != nullptr &&
+                (tokens == 0 || (topk_ids && token_indices && draw_indices)),
+            "aeon_b200_expert_permutation: null pointer argument");
     require(experts > 0 && experts <= kPermThreads,
             "aeon_b200_expert_permutation: experts must be in [1, 1024]");
-    require(weights == nullptr || weights_by_position != nullptr,
+    require(weights == nullptr || weights_by_position != nullptr || tokens == 0,
             "aeon_b200_expert_permutation: weights given without weights_by_position");
     const int draws = tokens * slots;
     int walk_warps = std::min(32, std::max(1, (40 * 1024) / (experts * 4)));
@@ -171,7 +178,7 @@ void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens,
     expert_permutation_kernel<<<1, kPermThreads, smem, stream>>>(
         topk_ids, draws, slots, experts, walk_warps, expert_offsets, token_indices, draw_indices,
         weights, weights_by_position, slot_of_expert, entries, counts,
-        entries != nullptr ? ctx->d_tile_done : nullptr, tiles);
+        entries != nullptr ? ctx->d_tile_done : nullptr, tiles, skip_absent ? 1 : 0);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 1;
 }
