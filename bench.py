@@ -39,12 +39,14 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/8/32/128 sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default="full", choices=["full", "small"],
+    ap.add_argument("--case", default="full", choices=["full", "small", "b1"],
                     help="small: one layer of 64 experts at batch 32 (1.45 GB of weights, larger "
                          "than L2), the case the ncu captures under profiles/ run; not a bench value")
     args = ap.parse_args()
     if args.case == "small":
         args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 32, True, True
+    if args.case == "b1":      # configuration 1 at batch 1 over 8 layers (launch lists)
+        args.batch, args.no_sweep, args.no_cpu_baseline = 1, True, True
     return args
 
 
@@ -268,7 +270,7 @@ def main():
     ms_step = ms / args.steps
     tokens_per_s = T / (ms_step * 1e-3)
 
-    if args.case == "small":
+    if args.case != "full":
         ms_e2e = ms
     else:
         ms_e2e, _ = timed(step_e2e, args.steps, 3)
