@@ -137,6 +137,21 @@ int aeon_b200_router_topk(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, c
                           int tokens, float* topk_weights, int32_t* topk_ids, float* logits_out,
                           void* stream);
 
+/* The same router for callers that cannot allocate device memory: code running during
+ * stream capture, under a fixed memory budget, or in a host that forbids allocation after
+ * start-up. It takes no context (creating one allocates) and makes no cudaMalloc, cudaFree
+ * or other allocating call: its logits scratch is a 256 KiB array built into the library,
+ * which every GPU that loads the library holds until the process exits. Limits: tokens <=
+ * 64 and experts <= 1024; larger sizes return AEON_B200_ERR_INVALID_ARGUMENT. The table
+ * (hash) branch is not offered. It runs on the current device; the first call on each
+ * device looks up the scratch's device address, so make that first call outside any stream
+ * capture. All calls on a device share the one scratch (it holds the last call's logits;
+ * nothing in it needs clearing): calls that overlap on the GPU, e.g. on two streams, race.
+ * This entry point has no counterpart in the reference. */
+int aeon_b200_router_topk_noalloc(const aeon_b200_moe_config* cfg_host, const void* x,
+                                  int64_t x_stride, const void* gate, const float* bias, int tokens,
+                                  float* topk_weights, int32_t* topk_ids, void* stream);
+
 /* Counting sort of the (token, slot) draws by expert. Replaces
  * dispatch_expert_permutation (src/platform/ops/expert_permutation.hpp:44-175):
  * expert_offsets[experts+1], token_indices[draws], draw_indices[draws] and,

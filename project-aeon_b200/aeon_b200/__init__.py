@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_router_topk", "aeon_b200_expert_permutation", "aeon_b200_shared_expert",
     "aeon_b200_moe_decode", "aeon_b200_ctx_last_stats", "aeon_b200_synth_fill_experts",
     "aeon_b200_synth_fill_dense16", "aeon_b200_ctx_set_timing", "aeon_b200_ctx_kernel_times",
-    "aeon_b200_ep_combine",
+    "aeon_b200_ep_combine", "aeon_b200_router_topk_noalloc",
 ]
 
 
@@ -101,6 +101,8 @@ def lib() -> ctypes.CDLL:
     L.aeon_b200_pool_upload.argtypes = [c_void_p, c_uint64, c_uint32, c_void_p, c_void_p]
     L.aeon_b200_router_topk.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    L.aeon_b200_router_topk_noalloc.argtypes = [POINTER(MoeConfig), c_void_p, c_int64, c_void_p,
+                                                c_void_p, c_int, c_void_p, c_void_p, c_void_p]
     L.aeon_b200_expert_permutation.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     L.aeon_b200_shared_expert.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
@@ -280,6 +282,15 @@ class Context:
                                          x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
                                          _ptr(moe_accum), moe_accum.stride(0),
                                          DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
+
+
+def router_topk_noalloc(cfg: MoeConfig, x, gate, weights_out, ids_out, bias=None) -> None:
+    """Router without a context and without any allocation: every buffer, outputs included,
+    is the caller's; the logits scratch is built into the library (<= 64 tokens, <= 1024
+    experts). For callers that cannot call cudaMalloc at the point of use."""
+    check(lib().aeon_b200_router_topk_noalloc(ctypes.byref(cfg), _ptr(x), x.stride(0), _ptr(gate),
+                                              _ptr(bias), x.shape[0], _ptr(weights_out),
+                                              _ptr(ids_out), _stream()))
 
 
 def ep_combine(out, partials) -> None:

@@ -412,6 +412,16 @@ int aeon_b200_router_topk(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, c
     });
 }
 
+int aeon_b200_router_topk_noalloc(const aeon_b200_moe_config* cfg, const void* x, int64_t x_stride,
+                                  const void* gate, const float* bias, int tokens,
+                                  float* topk_weights, int32_t* topk_ids, void* stream) {
+    return guarded([&] {
+        require(cfg != nullptr, "aeon_b200_router_topk_noalloc: null config");
+        launch_router_noalloc(*cfg, x, x_stride, gate, bias, tokens, topk_weights, topk_ids,
+                              as_stream(stream));
+    });
+}
+
 int aeon_b200_expert_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens, int slots,
                                  int experts, int32_t* expert_offsets, int32_t* token_indices,
                                  int32_t* draw_indices, const float* weights,

@@ -133,6 +133,9 @@ void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const vo
                    const float* bias, const int64_t* hash_table, const int32_t* token_ids,
                    int tokens, float* topk_weights, int32_t* topk_ids, float* logits_out,
                    cudaStream_t stream);
+void launch_router_noalloc(const aeon_b200_moe_config& cfg, const void* x, int64_t x_stride,
+                           const void* gate, const float* bias, int tokens, float* topk_weights,
+                           int32_t* topk_ids, cudaStream_t stream);
 void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens, int slots,
                         int experts, int32_t* expert_offsets, int32_t* token_indices,
                         int32_t* draw_indices, const float* weights, float* weights_by_position,

@@ -18,6 +18,8 @@
 // selected experts, divided by their sum when renormalising, then scaled.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace aeon_b200 {
 
 namespace {
@@ -186,6 +188,77 @@ void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const vo
         cfg.renormalize, cfg.routed_scaling, topk_weights, topk_ids);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 2;
+}
+
+// ---------------------------------------------------------------------------------------
+// Router entry point for callers that must not allocate device memory.
+//
+// Some callers cannot call cudaMalloc where they need the router: code running while a
+// stream is being captured into a graph, code that works under a fixed memory budget that
+// a context's scratch was never part of, or a plugin host that forbids allocation after
+// start-up. aeon_b200_router_topk needs a context, and creating a context allocates. This
+// variant needs none: its only scratch, the fp32 logits [tokens, experts], lives in the
+// file-scope device array below, which every GPU that loads this library holds until the
+// process exits (kNoAllocMaxTokens * kNoAllocMaxExperts * 4 bytes = 256 KiB).
+//
+// In host code the array's name is only a host-side handle, not a device address, so the
+// device address is looked up once per device with cudaGetSymbolAddress (with that device
+// current) and handed to the kernels as an ordinary pointer.
+constexpr int kNoAllocMaxTokens = 64;
+constexpr int kNoAllocMaxExperts = 1024;
+static __device__ __align__(256) float g_noalloc_logits[kNoAllocMaxTokens * kNoAllocMaxExperts];
+
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_logits_ptr[kNoAllocMaxDevices] = {};
+static std::mutex g_noalloc_mutex;
+
+static float* noalloc_scratch_for_current_device() {
+    int device = -1;
+    AEON_CUDA_CHECK(cudaGetDevice(&device));
+    if (device < 0 || device >= kNoAllocMaxDevices)
+        throw StatusError(AEON_B200_ERR_UNSUPPORTED,
+                          "aeon_b200_router_topk_noalloc: device index above 63");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_logits_ptr[device] == nullptr) {
+        float* ptr = nullptr;
+        AEON_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_logits));
+        g_noalloc_logits_ptr[device] = ptr;
+    }
+    return g_noalloc_logits_ptr[device];
+}
+
+void launch_router_noalloc(const aeon_b200_moe_config& cfg, const void* x, int64_t x_stride,
+                           const void* gate, const float* bias, int tokens, float* topk_weights,
+                           int32_t* topk_ids, cudaStream_t stream) {
+    validate_config(cfg);
+    require(x && gate && topk_weights && topk_ids,
+            "aeon_b200_router_topk_noalloc: null pointer argument");
+    require(tokens > 0, "aeon_b200_router_topk_noalloc: tokens must be positive");
+    if (tokens > kNoAllocMaxTokens || cfg.experts > kNoAllocMaxExperts)
+        throw StatusError(AEON_B200_ERR_INVALID_ARGUMENT,
+                          "aeon_b200_router_topk_noalloc: at most 64 tokens and 1024 experts fit the "
+                          "built-in scratch; use aeon_b200_router_topk with a context beyond that");
+    require(x_stride >= cfg.hidden && x_stride % 8 == 0,
+            "aeon_b200_router_topk_noalloc: x_stride must be >= hidden and a multiple of 8");
+    float* logits = noalloc_scratch_for_current_device();
+
+    const dim3 grid((cfg.experts + kLogitWarps - 1) / kLogitWarps,
+                    (tokens + kLogitTokens - 1) / kLogitTokens);
+    if (cfg.act_dtype == AEON_B200_BF16) {
+        router_logits_kernel<true><<<grid, kLogitWarps * 32, 0, stream>>>(
+            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
+            cfg.experts, cfg.hidden, logits);
+    } else {
+        router_logits_kernel<false><<<grid, kLogitWarps * 32, 0, stream>>>(
+            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
+            cfg.experts, cfg.hidden, logits);
+    }
+    AEON_CUDA_CHECK(cudaGetLastError());
+    const size_t smem = static_cast<size_t>(kSelectWarps) * cfg.experts * sizeof(float);
+    router_select_kernel<<<(tokens + kSelectWarps - 1) / kSelectWarps, kSelectWarps * 32, smem, stream>>>(
+        logits, bias, nullptr, nullptr, tokens, cfg.experts, cfg.top_k, cfg.score_fn, cfg.renormalize,
+        cfg.routed_scaling, topk_weights, topk_ids);
+    AEON_CUDA_CHECK(cudaGetLastError());
 }
 
 }  // namespace aeon_b200
