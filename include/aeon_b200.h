@@ -137,9 +137,8 @@ int aeon_b200_router_topk(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, c
                           int tokens, float* topk_weights, int32_t* topk_ids, float* logits_out,
                           void* stream);
 
-/* The same router for callers that cannot allocate device memory: code running during
- * stream capture, under a fixed memory budget, or in a host that forbids allocation after
- * start-up. It takes no context (creating one allocates) and makes no cudaMalloc, cudaFree
+/* The same router for callers that cannot allocate device memory: code that works under a
+ * fixed memory budget, or runs in a host that forbids allocation after start-up. It takes no context (creating one allocates) and makes no cudaMalloc, cudaFree
  * or other allocating call: its logits scratch is a 256 KiB array built into the library,
  * which every GPU that loads the library holds until the process exits. Limits: tokens <=
  * 64 and experts <= 1024; larger sizes return AEON_B200_ERR_INVALID_ARGUMENT. The table

@@ -193,10 +193,9 @@ void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const vo
 // ---------------------------------------------------------------------------------------
 // Router entry point for callers that must not allocate device memory.
 //
-// Some callers cannot call cudaMalloc where they need the router: code running while a
-// stream is being captured into a graph, code that works under a fixed memory budget that
-// a context's scratch was never part of, or a plugin host that forbids allocation after
-// start-up. aeon_b200_router_topk needs a context, and creating a context allocates. This
+// Some callers cannot call cudaMalloc where they need the router: code that works under a
+// fixed memory budget that a context's scratch was never part of, or a plugin host that
+// forbids allocation after start-up. aeon_b200_router_topk needs a context, and creating a context allocates. This
 // variant needs none: its only scratch, the fp32 logits [tokens, experts], lives in the
 // file-scope device array below, which every GPU that loads this library holds until the
 // process exits (kNoAllocMaxTokens * kNoAllocMaxExperts * 4 bytes = 256 KiB).

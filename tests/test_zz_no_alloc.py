@@ -1,8 +1,8 @@
 """The allocation-free router entry point against the context-based one.
 
 aeon_b200_router_topk_noalloc exists for callers that cannot call cudaMalloc where they
-need the router (during stream capture, under a fixed memory budget, inside a host that
-forbids allocation after start-up): it takes no context and keeps its logits scratch in an
+need the router (under a fixed memory budget, inside a host that forbids allocation after
+start-up): it takes no context and keeps its logits scratch in an
 array built into the library. Both entry points run the same kernels, so ids and weights
 must be identical. Two calls in a row are made because all calls share the one scratch,
 which still holds the previous call's logits when the next call starts.
