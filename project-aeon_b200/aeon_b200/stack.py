@@ -35,6 +35,46 @@ def _torch_bits(bits: np.ndarray, dtype: int, device):
     return t.view(torch.bfloat16 if dtype == aeon_b200.BF16 else torch.float16)
 
 
+def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv):
+    """One expert-parallel MoE layer on this rank (the protocol of the module docstring).
+
+    `ops` supplies the compute: router(x) -> (weights, ids); shared(x, out) writes the shared
+    expert into out; routed(x, ids, weights, out, skip_absent) adds the resident experts'
+    contributions; combine(out, recv) adds recv[r] for r = 0..world-1 in that order. The
+    collectives are `dist`'s (NCCL on GPUs; gloo in the CPU tests of the protocol).
+    Returns the (replicated) routing of the whole batch."""
+    dist.all_gather_into_tensor(x_all, x_local)                 # dispatch
+    weights, ids = ops.router(x_all)                            # replicated, identical inputs
+    ops.shared(x_local, out_local)
+    partial.zero_()
+    ops.routed(x_all, ids, weights, partial, skip_absent=True)
+    if not recv.is_contiguous():
+        raise ValueError("the receive buffer must be a dense [world, tokens_local, hidden] block")
+    dist.all_to_all_single(recv.view(-1, recv.shape[-1]), partial)   # combine: rows to owners
+    ops.combine(out_local, recv)
+    return weights, ids
+
+
+class _DeviceOps:
+    """The library's kernels behind the four calls ep_layer_forward needs."""
+
+    def __init__(self, ctx, w):
+        self.ctx, self.w = ctx, w
+
+    def router(self, x):
+        return self.ctx.router_topk(x, self.w.gate)
+
+    def shared(self, x, out):
+        self.ctx.shared_expert(self.w.shared[0], self.w.shared[1], self.w.shared[2], x, out)
+
+    def routed(self, x, ids, weights, out, skip_absent):
+        self.ctx.moe_decode(self.w.pool.base, self.w.slot_of, x, ids, weights, out,
+                            skip_absent=skip_absent)
+
+    def combine(self, out, recv):
+        aeon_b200.ep_combine(out, recv)
+
+
 class MoeLayerWeights:
     """Device-resident weights of one layer for one rank's expert slice."""
 
@@ -112,29 +152,18 @@ class MoeStack:
     def forward_layer(self, l: int, x, out, collect_stats: bool = False, return_routing: bool = False):
         w = self.weights[l]
         ctx = self.ctx
+        ops = _DeviceOps(ctx, w)
         if self.world == 1:
-            weights, ids = ctx.router_topk(x, w.gate)
-            ctx.shared_expert(w.shared[0], w.shared[1], w.shared[2], x, out)
-            ctx.moe_decode(w.pool.base, w.slot_of, x, ids, weights, out)
+            weights, ids = ops.router(x)
+            ops.shared(x, out)
+            ops.routed(x, ids, weights, out, skip_absent=False)
             tokens_seen = x.shape[0]
         else:
             tl = x.shape[0]
             tokens_seen = tl * self.world
-            x_all = self.x_all[:tokens_seen]
-            self.dist.all_gather_into_tensor(x_all, x)                     # dispatch
-            weights, ids = ctx.router_topk(x_all, w.gate)                  # replicated routing
-            ctx.shared_expert(w.shared[0], w.shared[1], w.shared[2], x, out)
-            partial = self.partial[:tokens_seen]
-            partial.zero_()
-            ctx.moe_decode(w.pool.base, w.slot_of, x_all, ids, weights, partial, skip_absent=True)
-            recv = self.recv[:, :tl]
-            if recv.is_contiguous():
-                self.dist.all_to_all_single(recv, partial)                 # combine
-            else:
-                tmp = recv.contiguous()
-                self.dist.all_to_all_single(tmp, partial)
-                recv = tmp
-            aeon_b200.ep_combine(out, recv)
+            weights, ids = ep_layer_forward(ops, self.dist, self.world, x, out,
+                                            self.x_all[:tokens_seen], self.partial[:tokens_seen],
+                                            self.recv[:, :tl])
             self._extra_launches += 2
         if collect_stats:
             distinct, _ = ctx.last_stats()
