@@ -23,6 +23,9 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "project-aeon_b200"))
+# stdout carries exactly one JSON line: keep NCCL's version banner out of it
+if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+    os.environ["NCCL_DEBUG"] = "WARN"
 
 LAYERS = 8
 BATCH = 128
@@ -316,7 +319,7 @@ def main():
             "unit": "GB/s", "frac": (achieved_a / peak_gbs) if achieved_a else None,
             "peak_source": peak_kind, "traffic": None,
             "algorithmic_bytes_per_launch": bytes_a, "avg_launch_ms": avg_a_ms, "launches_timed": n_a,
-            "second_kernel": {"kernel": "moe_w2_accum_kernel", "achieved": achieved_b,
+            "second_kernel": {"kernel": "moe_w2_contrib_kernel", "achieved": achieved_b,
                               "frac": (achieved_b / peak_gbs) if achieved_b else None,
                               "algorithmic_bytes_per_launch": bytes_b, "avg_launch_ms": avg_b_ms},
             "whole_step": {"algorithmic_bytes": step_bytes,

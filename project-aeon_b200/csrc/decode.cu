@@ -131,6 +131,39 @@ __device__ __forceinline__ void load_chunk(ChunkRegs<G, kMats>& r, const uint8_t
         }
 }
 
+// Per-(token, scale group) sums of the activation tile, the zero-point term of
+// ptx::fold_group. `rows` activation rows of `groups` scale groups of G fp16 values each sit
+// in shared memory `row_stride` bytes apart (a second plane, the lo part of the hidden vector,
+// `plane_stride` bytes after the first when planes == 2). Output xs[(grp * planes + plane) * 8
+// + row] as fp32; rows >= valid_rows get 0. Warps take (plane, row, group) triples round
+// robin; every sum is a fixed lane pattern plus a butterfly, so it is reproducible.
+template <int G>
+__device__ __forceinline__ void group_sums(uint32_t act_smem, int row_stride, int plane_stride,
+                                           int planes, int valid_rows, int groups, float* xs,
+                                           int warp, int warps, int lane) {
+    const int total = planes * kTokTile * groups;
+    for (int idx = warp; idx < total; idx += warps) {
+        const int grp = idx % groups;
+        const int row = (idx / groups) % kTokTile;
+        const int plane = idx / (groups * kTokTile);
+        float v = 0.f;
+        if (row < valid_rows) {
+            const uint32_t at = act_smem + row * row_stride + plane * plane_stride + grp * (G * 2);
+            if constexpr (G == 128) {
+                const uint2 q = ptx::lds64(at + lane * 8);
+                const __half2 a = *reinterpret_cast<const __half2*>(&q.x);
+                const __half2 b = *reinterpret_cast<const __half2*>(&q.y);
+                v = (__low2float(a) + __high2float(a)) + (__low2float(b) + __high2float(b));
+            } else {
+                v = __half2float(__ushort_as_half(static_cast<unsigned short>(ptx::lds16(at + lane * 2))));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+        }
+        if (lane == 0) xs[(grp * planes + plane) * kTokTile + row] = v;
+    }
+}
+
 // ----- kernel A: W1/W3 dual product + clamped SwiGLU -----------------------------------
 // One 16-row tile per item; the CTA's KW warps split K, NCH chunks of 128 columns each
 // (KW * NCH * 128 == hidden), chunk j of warp w being chunk j * KW + w so that the warps
@@ -144,8 +177,10 @@ struct GeomA {
     static constexpr int kBlockScaleBytes = (kHidden / 256) * ((G == 128) ? 16 : 64);
     static constexpr int kScaleBuf = 2 * 4 * kBlockScaleBytes;       // 2 matrices x 4 row-blocks
     static constexpr int kRedBuf = KW * 2 * 128 * 4;
+    static constexpr int kGroups = kHidden / G;
+    static constexpr int kXsBytes = kGroups * kTokTile * 4;
     static constexpr int kBarBytes = 64;
-    static constexpr int kSmem = kBarBytes + kActBytes + 2 * kScaleBuf + 2 * kRedBuf;
+    static constexpr int kSmem = kBarBytes + kActBytes + 2 * kScaleBuf + 2 * kRedBuf + kXsBytes;
 };
 
 template <int G, int KW, int NCH>
@@ -159,6 +194,8 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
     const uint32_t act_smem = smem_base + S::kBarBytes;
     const uint32_t scale_smem = act_smem + S::kActBytes;
     float* red = reinterpret_cast<float*>(smem + S::kBarBytes + S::kActBytes + 2 * S::kScaleBuf);
+    float* xs = red + 2 * (S::kRedBuf / 4);
+    const uint32_t xs_smem = scale_smem + 2 * S::kScaleBuf + 2 * S::kRedBuf;
     __shared__ WorkEntry s_entries[kSmemEntries];
     __shared__ int32_t s_token_idx[kSmemDraws];
 
@@ -267,6 +304,9 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
             if (!ptx::mbar_wait(act_bar, act_phase & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
             ++act_phase;
             cur_entry = m;
+            __syncwarp();
+            group_sums<G>(act_smem, S::kActRow, 0, 1, e.ntok, S::kGroups, xs, warp, KW, lane);
+            __syncthreads();
         }
         const WorkEntry cur = e;
         const int cur_rt = rt;
@@ -302,25 +342,18 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
                 for (int i = 0; i < 4; ++i)
                     bfrag[i] = (g < cur.ntok) ? ptx::lds128(a_row + (c * 128 + i * 32 + t * 8) * 2)
                                               : make_uint4(0, 0, 0, 0);
+                const float2 xsum = ptx::lds_f2(xs_smem + (c * kTokTile + 2 * t) * 4);
 #pragma unroll
                 for (int mat = 0; mat < 2; ++mat) {
                     const uint32_t sc_at = sc_smem + mat * 4 * S::kBlockScaleBytes + (c >> 1) * 16 + (c & 1) * 2;
                     const float sca = ptx::lds_half_as_float(sc_at + lane_sc[0]);
                     const float scb = ptx::lds_half_as_float(sc_at + lane_sc[1]);
-                    float tmp0[4] = {0.f, 0.f, 0.f, 0.f};
-                    float tmp1[4] = {0.f, 0.f, 0.f, 0.f};
+                    float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                    float thi[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t pa[4], pb[4];
-                        ptx::unpack_word(wbuf[j].w[mat][0][i], pa);
-                        ptx::unpack_word(wbuf[j].w[mat][1][i], pb);
-                        ptx::mma_f16(tmp0, pa[0], pb[0], pa[1], pb[1], bfrag[i].x, bfrag[i].y);
-                        ptx::mma_f16(tmp1, pa[2], pb[2], pa[3], pb[3], bfrag[i].z, bfrag[i].w);
-                    }
-                    acc[mat][0] = fmaf(sca, tmp0[0] + tmp1[0], acc[mat][0]);
-                    acc[mat][1] = fmaf(sca, tmp0[1] + tmp1[1], acc[mat][1]);
-                    acc[mat][2] = fmaf(scb, tmp0[2] + tmp1[2], acc[mat][2]);
-                    acc[mat][3] = fmaf(scb, tmp0[3] + tmp1[3], acc[mat][3]);
+                    for (int i = 0; i < 4; ++i)
+                        ptx::mma_word(tlo, thi, wbuf[j].w[mat][0][i], wbuf[j].w[mat][1][i], bfrag[i]);
+                    ptx::fold_group(acc[mat], tlo, thi, sca, scb, xsum);
                 }
             } else {
                 // group 32: atom a of the chunk is one scale group; the lane holds word t of it
@@ -328,22 +361,17 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
                 for (int a = 0; a < 4; ++a) {
                     const uint4 bf = (g < cur.ntok) ? ptx::lds128(a_row + (c * 128 + a * 32 + t * 8) * 2)
                                                     : make_uint4(0, 0, 0, 0);
+                    const float2 xsum = ptx::lds_f2(xs_smem + ((c * 4 + a) * kTokTile + 2 * t) * 4);
 #pragma unroll
                     for (int mat = 0; mat < 2; ++mat) {
                         const uint32_t sc_at = sc_smem + mat * 4 * S::kBlockScaleBytes + (c >> 1) * 64 +
                                                ((c & 1) * 4 + a) * 2;
                         const float sca = ptx::lds_half_as_float(sc_at + lane_sc[0]);
                         const float scb = ptx::lds_half_as_float(sc_at + lane_sc[1]);
-                        float tmp[4] = {0.f, 0.f, 0.f, 0.f};
-                        uint32_t pa[4], pb[4];
-                        ptx::unpack_word(wbuf[j].w[mat][0][a], pa);
-                        ptx::unpack_word(wbuf[j].w[mat][1][a], pb);
-                        ptx::mma_f16(tmp, pa[0], pb[0], pa[1], pb[1], bf.x, bf.y);
-                        ptx::mma_f16(tmp, pa[2], pb[2], pa[3], pb[3], bf.z, bf.w);
-                        acc[mat][0] = fmaf(sca, tmp[0], acc[mat][0]);
-                        acc[mat][1] = fmaf(sca, tmp[1], acc[mat][1]);
-                        acc[mat][2] = fmaf(scb, tmp[2], acc[mat][2]);
-                        acc[mat][3] = fmaf(scb, tmp[3], acc[mat][3]);
+                        float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                        float thi[4] = {0.f, 0.f, 0.f, 0.f};
+                        ptx::mma_word(tlo, thi, wbuf[j].w[mat][0][a], wbuf[j].w[mat][1][a], bf);
+                        ptx::fold_group(acc[mat], tlo, thi, sca, scb, xsum);
                     }
                 }
             }
@@ -405,8 +433,10 @@ struct GeomB {
     static constexpr int kBlockScaleBytes = (kInter / 128) * ((G == 128) ? 16 : 64);
     static constexpr int kScaleBuf = 2 * kBlockScaleBytes;            // a worker's two row-blocks
     static constexpr int kRedBuf = KW * 128 * 4;
+    static constexpr int kGroups = kInter / G;
+    static constexpr int kXsBytes = kGroups * 2 * kTokTile * 4;       // [group][hi|lo][token]
     static constexpr int kBarBytes = 128;
-    static constexpr int kSmem = kBarBytes + kActBytes + MW * 2 * kScaleBuf + MW * 2 * kRedBuf;
+    static constexpr int kSmem = kBarBytes + kActBytes + MW * 2 * kScaleBuf + MW * 2 * kRedBuf + kXsBytes;
 };
 
 template <int G, int MW, int KW, int NCH, int P>
@@ -421,6 +451,8 @@ moe_w2_contrib_kernel(const DecodeParams p) {
     const uint32_t act_smem = smem_base + S::kBarBytes;
     const uint32_t scale_smem0 = act_smem + S::kActBytes;
     float* red0 = reinterpret_cast<float*>(smem + S::kBarBytes + S::kActBytes + MW * 2 * S::kScaleBuf);
+    float* xs = red0 + MW * 2 * (S::kRedBuf / 4);
+    const uint32_t xs_smem = scale_smem0 + MW * 2 * S::kScaleBuf + MW * 2 * S::kRedBuf;
     __shared__ WorkEntry s_entries[kSmemEntries];
     __shared__ int32_t s_draw_idx[kSmemDraws];
     __shared__ float s_wpos[kSmemDraws];
@@ -543,6 +575,10 @@ moe_w2_contrib_kernel(const DecodeParams p) {
                 if (!ptx::mbar_wait(act_bar, act_phase & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
                 ++act_phase;
                 cur_entry = m;
+                __syncwarp();
+                group_sums<G>(act_smem, S::kActRow, S::kInter * 2, 2, e.ntok, S::kGroups, xs, warp,
+                              MW * KW, lane);
+                __syncthreads();
             }
 
             // next item's scales (this worker), next-P item's weight addresses
@@ -562,59 +598,53 @@ moe_w2_contrib_kernel(const DecodeParams p) {
                 flag_error(p.error, kErrWaitTimeout);
             __syncwarp();
             const uint32_t sc_smem = scale_smem + (idx & 1) * S::kScaleBuf;
-            const uint32_t a_row = act_smem + g * S::kActRow;
 
+            // Up to four tokens: the hi and lo parts ride in one MMA as eight token columns
+            // (columns 0-3 hi of tokens 0-3, columns 4-7 lo), halving the MMA count; the two
+            // column halves are added after the K-split sum. More tokens: one pass per part.
+            const bool packed = e.ntok <= 4;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int j = 0; j < NCH; ++j) {
                 const int c = j * KW + kw;
-                if constexpr (G == 128) {
-                    uint4 bhi[4], blo[4];
+                const int passes = packed ? 1 : 2;
+                for (int part = 0; part < passes; ++part) {
+                    const int tok = packed ? (g & 3) : g;
+                    const int my_part = packed ? (g >> 2) : part;
+                    const bool live = tok < e.ntok;
+                    const uint32_t b_row = act_smem + tok * S::kActRow + my_part * (S::kInter * 2);
+                    // xs columns of this lane's accumulators: tokens 2t, 2t+1 of the pass
+                    const uint32_t xs_col = packed ? ((t >> 1) * kTokTile + 2 * (t & 1))
+                                                   : (part * kTokTile + 2 * t);
+                    if constexpr (G == 128) {
+                        uint4 bf[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t off = (c * 128 + i * 32 + t * 8) * 2;
-                        bhi[i] = (g < e.ntok) ? ptx::lds128(a_row + off) : make_uint4(0, 0, 0, 0);
-                        blo[i] = (g < e.ntok) ? ptx::lds128(a_row + S::kInter * 2 + off) : make_uint4(0, 0, 0, 0);
-                    }
-                    const float sca = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[0]);
-                    const float scb = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[1]);
-                    float tmp0[4] = {0.f, 0.f, 0.f, 0.f};
-                    float tmp1[4] = {0.f, 0.f, 0.f, 0.f};
+                        for (int i = 0; i < 4; ++i)
+                            bf[i] = live ? ptx::lds128(b_row + (c * 128 + i * 32 + t * 8) * 2)
+                                         : make_uint4(0, 0, 0, 0);
+                        const float2 xsum = ptx::lds_f2(xs_smem + (c * 2 * kTokTile + xs_col) * 4);
+                        const float sca = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[0]);
+                        const float scb = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[1]);
+                        float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                        float thi[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t pa[4], pb[4];
-                        ptx::unpack_word(wbuf[q][j].w[0][0][i], pa);
-                        ptx::unpack_word(wbuf[q][j].w[0][1][i], pb);
-                        ptx::mma_f16(tmp0, pa[0], pb[0], pa[1], pb[1], bhi[i].x, bhi[i].y);
-                        ptx::mma_f16(tmp1, pa[0], pb[0], pa[1], pb[1], blo[i].x, blo[i].y);
-                        ptx::mma_f16(tmp0, pa[2], pb[2], pa[3], pb[3], bhi[i].z, bhi[i].w);
-                        ptx::mma_f16(tmp1, pa[2], pb[2], pa[3], pb[3], blo[i].z, blo[i].w);
-                    }
-                    acc[0] = fmaf(sca, tmp0[0] + tmp1[0], acc[0]);
-                    acc[1] = fmaf(sca, tmp0[1] + tmp1[1], acc[1]);
-                    acc[2] = fmaf(scb, tmp0[2] + tmp1[2], acc[2]);
-                    acc[3] = fmaf(scb, tmp0[3] + tmp1[3], acc[3]);
-                } else {
+                        for (int i = 0; i < 4; ++i)
+                            ptx::mma_word(tlo, thi, wbuf[q][j].w[0][0][i], wbuf[q][j].w[0][1][i], bf[i]);
+                        ptx::fold_group(acc, tlo, thi, sca, scb, xsum);
+                    } else {
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        const uint32_t off = (c * 128 + a * 32 + t * 8) * 2;
-                        const uint4 bh = (g < e.ntok) ? ptx::lds128(a_row + off) : make_uint4(0, 0, 0, 0);
-                        const uint4 bl = (g < e.ntok) ? ptx::lds128(a_row + S::kInter * 2 + off)
-                                                      : make_uint4(0, 0, 0, 0);
-                        const float sca = ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[0]);
-                        const float scb = ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[1]);
-                        float tmp[4] = {0.f, 0.f, 0.f, 0.f};
-                        uint32_t pa[4], pb[4];
-                        ptx::unpack_word(wbuf[q][j].w[0][0][a], pa);
-                        ptx::unpack_word(wbuf[q][j].w[0][1][a], pb);
-                        ptx::mma_f16(tmp, pa[0], pb[0], pa[1], pb[1], bh.x, bh.y);
-                        ptx::mma_f16(tmp, pa[0], pb[0], pa[1], pb[1], bl.x, bl.y);
-                        ptx::mma_f16(tmp, pa[2], pb[2], pa[3], pb[3], bh.z, bh.w);
-                        ptx::mma_f16(tmp, pa[2], pb[2], pa[3], pb[3], bl.z, bl.w);
-                        acc[0] = fmaf(sca, tmp[0], acc[0]);
-                        acc[1] = fmaf(sca, tmp[1], acc[1]);
-                        acc[2] = fmaf(scb, tmp[2], acc[2]);
-                        acc[3] = fmaf(scb, tmp[3], acc[3]);
+                        for (int a = 0; a < 4; ++a) {
+                            const uint4 bf = live ? ptx::lds128(b_row + (c * 128 + a * 32 + t * 8) * 2)
+                                                  : make_uint4(0, 0, 0, 0);
+                            const float2 xsum =
+                                ptx::lds_f2(xs_smem + ((c * 4 + a) * 2 * kTokTile + xs_col) * 4);
+                            const float sca = ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[0]);
+                            const float scb = ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[1]);
+                            float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                            float thi[4] = {0.f, 0.f, 0.f, 0.f};
+                            ptx::mma_word(tlo, thi, wbuf[q][j].w[0][0][a], wbuf[q][j].w[0][1][a], bf);
+                            ptx::fold_group(acc, tlo, thi, sca, scb, xsum);
+                        }
                     }
                 }
                 if (refill) load_chunk<G, 1>(wbuf[q][j], nbase, c * 512);
@@ -624,12 +654,21 @@ moe_w2_contrib_kernel(const DecodeParams p) {
             *reinterpret_cast<float4*>(&rbuf[kw * 128 + lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
             ptx::named_bar_sync(1 + wk, KW * 32);
             if (wtid < 128) {
+                const int lo4 = wtid >> 2, c = wtid & 3;
+                const int go = lo4 >> 2, to = lo4 & 3;
                 float sum = 0.f;
 #pragma unroll
                 for (int w = 0; w < KW; ++w) sum += rbuf[w * 128 + wtid];
-                const int lo4 = wtid >> 2, c = wtid & 3;
-                const int go = lo4 >> 2, to = lo4 & 3;
-                const int token = 2 * to + (c & 1);
+                if (packed) {
+                    // columns 2to+(c&1) (hi) and the same + 4 (lo) are two lanes apart: +8 floats
+                    float lo_part = 0.f;
+                    if (to < 2) {
+#pragma unroll
+                        for (int w = 0; w < KW; ++w) lo_part += rbuf[w * 128 + wtid + 8];
+                    }
+                    sum += lo_part;
+                }
+                const int token = (packed && to >= 2) ? kTokTile : 2 * to + (c & 1);
                 const int row = (rt * MW + wk) * 16 + go + 8 * (c >> 1);
                 if (token < e.ntok) {
                     const int pos = e.pos0 + token;

@@ -170,5 +170,54 @@ __device__ __forceinline__ void unpack_word(uint32_t w, uint32_t (&pairs)[4]) {
     pairs[3] = hfma2_u32(p3, kSixteenth, kMinus72);
 }
 
+// Cheaper form used by the streaming kernels. The masked bits of a swizzled word are
+// already valid fp16 numbers: (w & 0x000F000F) read as two fp16 values is the pair of
+// SUBNORMALS nibble * 2^-24, and (w & 0x00F000F0) is nibble * 2^-20. The tensor core takes
+// fp16 subnormals at full precision, so the unsigned nibbles can go into the MMA as they are
+// (one AND per column pair, no subtract); the power-of-two factor and the zero point are
+// applied once per scale group in fp32:
+//     sum_k (u_k - 8) x_k  =  2^24 * (T_lo + T_hi / 16)  -  8 * sum_k x_k
+// where T_lo / T_hi accumulate the low-plane / high-plane products (they need separate
+// accumulators because their factors differ) and sum_k x_k is a per-(token, group) constant.
+// One word (8 columns of rows g and g+8) costs two MMAs: the low plane holds columns
+// {0,1} and {4,5} of the word, the high plane {2,3} and {6,7}; `b` holds the token's
+// activations for the 8 columns as (x,y,z,w) = column pairs (0,1),(2,3),(4,5),(6,7).
+__device__ __forceinline__ void mma_word(float (&tlo)[4], float (&thi)[4], uint32_t wa, uint32_t wb,
+                                         const uint4& b) {
+    const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+    mma_f16(tlo, wa & 0x000F000Fu, wb & 0x000F000Fu, wa8 & 0x000F000Fu, wb8 & 0x000F000Fu, b.x, b.z);
+    mma_f16(thi, wa & 0x00F000F0u, wb & 0x00F000F0u, wa8 & 0x00F000F0u, wb8 & 0x00F000F0u, b.y, b.w);
+}
+
+// acc += scale * (2^24 * (tlo + thi/16) - 8 * xsum): rows g (sa) and g+8 (sb), token
+// columns 2t (xs.x) and 2t+1 (xs.y).
+__device__ __forceinline__ void fold_group(float (&acc)[4], const float (&tlo)[4],
+                                           const float (&thi)[4], float sa, float sb, float2 xs) {
+    const float sa24 = sa * 16777216.0f, sb24 = sb * 16777216.0f;
+    const float sa8 = -8.0f * sa, sb8 = -8.0f * sb;
+    acc[0] = fmaf(sa24, fmaf(thi[0], 0.0625f, tlo[0]), fmaf(sa8, xs.x, acc[0]));
+    acc[1] = fmaf(sa24, fmaf(thi[1], 0.0625f, tlo[1]), fmaf(sa8, xs.y, acc[1]));
+    acc[2] = fmaf(sb24, fmaf(thi[2], 0.0625f, tlo[2]), fmaf(sb8, xs.x, acc[2]));
+    acc[3] = fmaf(sb24, fmaf(thi[3], 0.0625f, tlo[3]), fmaf(sb8, xs.y, acc[3]));
+}
+
+__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
 }  // namespace ptx
 }  // namespace aeon_b200

@@ -24,7 +24,7 @@ namespace aeon_b200 {
 
 namespace {
 
-constexpr int kLogitWarps = 8;      // experts per CTA
+constexpr int kLogitWarps = 2;      // experts per CTA (many small CTAs: the kernel is latency-bound)
 constexpr int kLogitTokens = 4;     // tokens per CTA
 
 template <bool kBf16>
@@ -61,6 +61,7 @@ router_logits_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
 
     const uint4* grow = reinterpret_cast<const uint4*>(gate + static_cast<size_t>(e) * hidden);
     const int vectors = hidden / 8;
+#pragma unroll 8
     for (int v = lane; v < vectors; v += 32) {
         float gv[8];
         widen8<kBf16>(__ldg(grow + v), gv);
