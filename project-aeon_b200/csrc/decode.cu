@@ -419,30 +419,31 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
 }
 
 // ----- kernel B: W2 product, per-draw weighted slices -------------------------------------
-// MW workers of KW warps per CTA; a worker owns one 16-row tile of the CTA's MW*16-row item
-// and splits K = intermediate over its warps (KW * NCH * 128 == intermediate). Workers share
-// the entry's hidden rows in shared memory and nothing else (own scale buffers, own named
-// barrier), so they only meet when the entry changes. P items of weights are kept in flight
-// per lane.
-template <int G, int MW, int KW, int NCH, int P>
+// MW workers of KW warps per CTA; a worker owns MT 16-row tiles of the CTA's MW*MT*16-row
+// item and splits K = intermediate over its warps (KW * NCH * 128 == intermediate). The MT
+// tiles of a worker share every activation fragment read from shared memory. Workers share
+// the entry's hidden rows and nothing else (own scale buffers, own named barrier), so they
+// only meet when the entry changes. P items of weights are kept in flight per lane.
+template <int G, int MW, int MT, int KW, int NCH, int P>
 struct GeomB {
     static constexpr int kThreads = MW * KW * 32;
     static constexpr int kInter = KW * NCH * 128;
+    static constexpr int kItemRows = MW * MT * 16;
     static constexpr int kActRow = 2 * kInter * 2 + kPad;            // hi then lo
     static constexpr int kActBytes = kTokTile * kActRow;
     static constexpr int kBlockScaleBytes = (kInter / 128) * ((G == 128) ? 16 : 64);
-    static constexpr int kScaleBuf = 2 * kBlockScaleBytes;            // a worker's two row-blocks
-    static constexpr int kRedBuf = KW * 128 * 4;
+    static constexpr int kScaleBuf = 2 * MT * kBlockScaleBytes;       // a worker's row-blocks
+    static constexpr int kRedBuf = KW * MT * 128 * 4;
     static constexpr int kGroups = kInter / G;
     static constexpr int kXsBytes = kGroups * 2 * kTokTile * 4;       // [group][hi|lo][token]
     static constexpr int kBarBytes = 128;
     static constexpr int kSmem = kBarBytes + kActBytes + MW * 2 * kScaleBuf + MW * 2 * kRedBuf + kXsBytes;
 };
 
-template <int G, int MW, int KW, int NCH, int P>
+template <int G, int MW, int MT, int KW, int NCH, int P>
 __global__ void __launch_bounds__(MW * KW * 32, 1)
 moe_w2_contrib_kernel(const DecodeParams p) {
-    using S = GeomB<G, MW, KW, NCH, P>;
+    using S = GeomB<G, MW, MT, KW, NCH, P>;
     static_assert(MW <= 4, "barrier slots");
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t smem_base = ptx::smem_u32(smem);
@@ -468,7 +469,7 @@ moe_w2_contrib_kernel(const DecodeParams p) {
 
     const int entries = p.counts[0];
     const int placed = p.counts[2];
-    const int tiles = p.H / (16 * MW);
+    const int tiles = p.H / S::kItemRows;
     const int total_items = entries * tiles;
     const int lo = static_cast<int>(static_cast<int64_t>(total_items) * blockIdx.x / gridDim.x);
     const int hi = static_cast<int>(static_cast<int64_t>(total_items) * (blockIdx.x + 1) / gridDim.x);
@@ -499,50 +500,62 @@ moe_w2_contrib_kernel(const DecodeParams p) {
     const uint32_t scale_smem = scale_smem0 + wk * 2 * S::kScaleBuf;
     float* red = red0 + wk * 2 * (S::kRedBuf / 4);
 
-    // W2 row-blocks hold 8 rows: rows g of the tile are block 0, rows g+8 block 1, and a
-    // warp's 32 lanes read one contiguous 512-byte line per block.
-    uint32_t lane_off[2], lane_sc[2];
+    // W2 row-blocks hold 8 rows: rows g of a tile are its first block, rows g+8 the second,
+    // and a warp's 32 lanes read one contiguous 512-byte line per block.
+    uint32_t lane_off[MT][2], lane_sc[MT][2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        if constexpr (G == 128) {
-            lane_off[h] = h * p.w2.block_bytes + (g * 4 + t) * 16;
-            lane_sc[h] = h * S::kBlockScaleBytes + g * 2;
-        } else {
-            lane_off[h] = h * p.w2.block_bytes + g * 64 + t * 4;
-            lane_sc[h] = h * S::kBlockScaleBytes + g * 8;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int blk = mt * 2 + h;
+            if constexpr (G == 128) {
+                lane_off[mt][h] = blk * p.w2.block_bytes + (g * 4 + t) * 16;
+                lane_sc[mt][h] = blk * S::kBlockScaleBytes + g * 2;
+            } else {
+                lane_off[mt][h] = blk * p.w2.block_bytes + g * 64 + t * 4;
+                lane_sc[mt][h] = blk * S::kBlockScaleBytes + g * 8;
+            }
         }
-    }
     const uint64_t stream_policy = ptx::policy_evict_first();
     const uint64_t keep_policy = ptx::policy_evict_last();
 
-    auto item_bases = [&](int it, const uint8_t* (&base)[1][2], const uint8_t*& scales) {
-        const int m = it / tiles;
-        const int rt = it - m * tiles;
+    // (entry index, row tile) of an item; items advance one row tile at a time
+    auto locate = [&](int it, int& m, int& rt) { m = it / tiles; rt = it - m * tiles; };
+    auto weights_of = [&](int m, int rt) -> const uint8_t* {
         const WorkEntry e = ent[m];
-        const uint8_t* payload = p.pool + static_cast<uint64_t>(e.slot < 0 ? 0 : e.slot) * p.payload_bytes;
-        const size_t block0 = static_cast<size_t>(rt * MW + wk) * 2;
-        const uint8_t* w = payload + p.w2.packed_offset + block0 * p.w2.block_bytes;
-        base[0][0] = w + lane_off[0];
-        base[0][1] = w + lane_off[1];
-        scales = payload + p.w2.scale_offset + block0 * S::kBlockScaleBytes;
+        return p.pool + static_cast<uint64_t>(e.slot < 0 ? 0 : e.slot) * p.payload_bytes;
     };
-    auto issue_scales = [&](const uint8_t* sc, int buf) {
+    auto set_bases = [&](const uint8_t* payload, int rt, const uint8_t* (&base)[MT][2]) {
+        const size_t block0 = static_cast<size_t>(rt * MW + wk) * 2 * MT;
+        const uint8_t* w = payload + p.w2.packed_offset + block0 * p.w2.block_bytes;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            base[mt][0] = w + lane_off[mt][0];
+            base[mt][1] = w + lane_off[mt][1];
+        }
+    };
+    auto issue_scales = [&](const uint8_t* payload, int rt, int buf) {
+        const size_t block0 = static_cast<size_t>(rt * MW + wk) * 2 * MT;
         const uint32_t bar = scale_bar + 8 * buf;
         ptx::mbar_arrive_expect_tx(bar, S::kScaleBuf);
-        ptx::bulk_g2s(scale_smem + buf * S::kScaleBuf, sc, S::kScaleBuf, bar, stream_policy);
+        ptx::bulk_g2s(scale_smem + buf * S::kScaleBuf,
+                      payload + p.w2.scale_offset + block0 * S::kBlockScaleBytes, S::kScaleBuf, bar,
+                      stream_policy);
     };
 
     // ---- prologue: P items of weights in flight, first item's scales ----
-    ChunkRegs<G, 1> wbuf[P][NCH];
+    ChunkRegs<G, MT> wbuf[P][NCH];
 #pragma unroll
     for (int q = 0; q < P; ++q) {
         if (lo + q < hi) {
-            const uint8_t* b[1][2];
-            const uint8_t* sc;
-            item_bases(lo + q, b, sc);
-            if (q == 0 && wtid == 0) issue_scales(sc, 0);
+            int m, rt;
+            locate(lo + q, m, rt);
+            const uint8_t* payload = weights_of(m, rt);
+            const uint8_t* b[MT][2];
+            set_bases(payload, rt, b);
+            if (q == 0 && wtid == 0) issue_scales(payload, rt, 0);
 #pragma unroll
-            for (int j = 0; j < NCH; ++j) load_chunk<G, 1>(wbuf[q][j], b, (j * KW + kw) * 512);
+            for (int j = 0; j < NCH; ++j) load_chunk<G, MT>(wbuf[q][j], b, (j * KW + kw) * 512);
         }
     }
 
@@ -554,8 +567,8 @@ moe_w2_contrib_kernel(const DecodeParams p) {
             const int it = base_it + q;
             if (it >= hi) break;
             const int idx = it - lo;
-            const int m = it / tiles;
-            const int rt = it - m * tiles;
+            int m, rt;
+            locate(it, m, rt);
             const WorkEntry e = ent[m];
 
             if (m != cur_entry) {
@@ -581,18 +594,18 @@ moe_w2_contrib_kernel(const DecodeParams p) {
                 __syncthreads();
             }
 
-            // next item's scales (this worker), next-P item's weight addresses
+            // next item's scales (one thread of this worker); addresses of the item P ahead
             if (it + 1 < hi && wtid == 0) {
-                const uint8_t* b[1][2];
-                const uint8_t* sc;
-                item_bases(it + 1, b, sc);
-                issue_scales(sc, (idx + 1) & 1);
+                int nm, nrt;
+                locate(it + 1, nm, nrt);
+                issue_scales(weights_of(nm, nrt), nrt, (idx + 1) & 1);
             }
             const bool refill = it + P < hi;
-            const uint8_t* nbase[1][2] = {{nullptr, nullptr}};
-            if (refill) {
-                const uint8_t* sc;
-                item_bases(it + P, nbase, sc);
+            const uint8_t* nbase[MT][2];
+            {
+                int nm = m, nrt = rt;
+                if (refill) locate(it + P, nm, nrt);
+                set_bases(weights_of(nm, nrt), nrt, nbase);
             }
             if (!ptx::mbar_wait(scale_bar + 8 * (idx & 1), (idx >> 1) & 1, p.error))
                 flag_error(p.error, kErrWaitTimeout);
@@ -603,7 +616,11 @@ moe_w2_contrib_kernel(const DecodeParams p) {
             // (columns 0-3 hi of tokens 0-3, columns 4-7 lo), halving the MMA count; the two
             // column halves are added after the K-split sum. More tokens: one pass per part.
             const bool packed = e.ntok <= 4;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[mt][c] = 0.f;
 #pragma unroll
             for (int j = 0; j < NCH; ++j) {
                 const int c = j * KW + kw;
@@ -623,14 +640,17 @@ moe_w2_contrib_kernel(const DecodeParams p) {
                             bf[i] = live ? ptx::lds128(b_row + (c * 128 + i * 32 + t * 8) * 2)
                                          : make_uint4(0, 0, 0, 0);
                         const float2 xsum = ptx::lds_f2(xs_smem + (c * 2 * kTokTile + xs_col) * 4);
-                        const float sca = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[0]);
-                        const float scb = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[1]);
-                        float tlo[4] = {0.f, 0.f, 0.f, 0.f};
-                        float thi[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            ptx::mma_word(tlo, thi, wbuf[q][j].w[0][0][i], wbuf[q][j].w[0][1][i], bf[i]);
-                        ptx::fold_group(acc, tlo, thi, sca, scb, xsum);
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const float sca = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[mt][0]);
+                            const float scb = ptx::lds_half_as_float(sc_smem + c * 16 + lane_sc[mt][1]);
+                            float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                            float thi[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                ptx::mma_word(tlo, thi, wbuf[q][j].w[mt][0][i], wbuf[q][j].w[mt][1][i], bf[i]);
+                            ptx::fold_group(acc[mt], tlo, thi, sca, scb, xsum);
+                        }
                     } else {
 #pragma unroll
                         for (int a = 0; a < 4; ++a) {
@@ -638,38 +658,47 @@ moe_w2_contrib_kernel(const DecodeParams p) {
                                                   : make_uint4(0, 0, 0, 0);
                             const float2 xsum =
                                 ptx::lds_f2(xs_smem + ((c * 4 + a) * 2 * kTokTile + xs_col) * 4);
-                            const float sca = ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[0]);
-                            const float scb = ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[1]);
-                            float tlo[4] = {0.f, 0.f, 0.f, 0.f};
-                            float thi[4] = {0.f, 0.f, 0.f, 0.f};
-                            ptx::mma_word(tlo, thi, wbuf[q][j].w[0][0][a], wbuf[q][j].w[0][1][a], bf);
-                            ptx::fold_group(acc, tlo, thi, sca, scb, xsum);
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const float sca =
+                                    ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[mt][0]);
+                                const float scb =
+                                    ptx::lds_half_as_float(sc_smem + c * 64 + a * 2 + lane_sc[mt][1]);
+                                float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                                float thi[4] = {0.f, 0.f, 0.f, 0.f};
+                                ptx::mma_word(tlo, thi, wbuf[q][j].w[mt][0][a], wbuf[q][j].w[mt][1][a], bf);
+                                ptx::fold_group(acc[mt], tlo, thi, sca, scb, xsum);
+                            }
                         }
                     }
                 }
-                if (refill) load_chunk<G, 1>(wbuf[q][j], nbase, c * 512);
+                if (refill) load_chunk<G, MT>(wbuf[q][j], nbase, c * 512);
             }
 
             float* rbuf = red + (idx & 1) * (S::kRedBuf / 4);
-            *reinterpret_cast<float4*>(&rbuf[kw * 128 + lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                *reinterpret_cast<float4*>(&rbuf[(kw * MT + mt) * 128 + lane * 4]) =
+                    make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
             ptx::named_bar_sync(1 + wk, KW * 32);
-            if (wtid < 128) {
-                const int lo4 = wtid >> 2, c = wtid & 3;
+            for (int o = wtid; o < MT * 128; o += KW * 32) {
+                const int mt = o >> 7, idx128 = o & 127;
+                const int lo4 = idx128 >> 2, c = idx128 & 3;
                 const int go = lo4 >> 2, to = lo4 & 3;
                 float sum = 0.f;
 #pragma unroll
-                for (int w = 0; w < KW; ++w) sum += rbuf[w * 128 + wtid];
+                for (int w = 0; w < KW; ++w) sum += rbuf[(w * MT + mt) * 128 + idx128];
                 if (packed) {
                     // columns 2to+(c&1) (hi) and the same + 4 (lo) are two lanes apart: +8 floats
                     float lo_part = 0.f;
                     if (to < 2) {
 #pragma unroll
-                        for (int w = 0; w < KW; ++w) lo_part += rbuf[w * 128 + wtid + 8];
+                        for (int w = 0; w < KW; ++w) lo_part += rbuf[(w * MT + mt) * 128 + idx128 + 8];
                     }
                     sum += lo_part;
                 }
                 const int token = (packed && to >= 2) ? kTokTile : 2 * to + (c & 1);
-                const int row = (rt * MW + wk) * 16 + go + 8 * (c >> 1);
+                const int row = ((rt * MW + wk) * MT + mt) * 16 + go + 8 * (c >> 1);
                 if (token < e.ntok) {
                     const int pos = e.pos0 + token;
                     p.contrib[static_cast<size_t>(draw_idx[pos]) * p.H + row] = wpos[pos] * sum;
@@ -763,13 +792,14 @@ void launch_pair(aeon_b200_ctx* ctx, const DecodeParams& p, KernelA ka, int thre
 template <int G, int KWA, int NCHA>
 void launch_decode_kernels(aeon_b200_ctx* ctx, const DecodeParams& p, cudaStream_t stream) {
     using SA = GeomA<G, KWA, NCHA>;
-    // intermediate = 2048: two workers of eight warps, two chunks each, four items in flight
-    using SB = GeomB<G, 2, 8, 2, 4>;
+    // intermediate = 2048: two workers of eight warps, two 16-row tiles per worker, two chunks
+    // per warp, two items in flight
+    using SB = GeomB<G, 2, 2, 8, 2, 1>;
     if (p.I != SB::kInter || p.H != SA::kHidden)
         throw StatusError(AEON_B200_ERR_UNSUPPORTED,
                           "aeon_b200_moe_decode: no kernel instance for this hidden/intermediate size");
     launch_pair(ctx, p, moe_w13_swiglu_kernel<G, KWA, NCHA>, SA::kThreads, SA::kSmem,
-                moe_w2_contrib_kernel<G, 2, 8, 2, 4>, SB::kThreads, SB::kSmem, stream);
+                moe_w2_contrib_kernel<G, 2, 2, 8, 2, 1>, SB::kThreads, SB::kSmem, stream);
 }
 
 __global__ void ep_combine_kernel(float* __restrict__ out, int64_t out_stride,
