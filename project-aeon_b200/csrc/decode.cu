@@ -441,7 +441,7 @@ struct GeomB {
 };
 
 template <int G, int MW, int MT, int KW, int NCH, int P>
-__global__ void __launch_bounds__(MW * KW * 32, 1)
+__global__ void __launch_bounds__(MW * KW * 32, (MW * KW <= 8) ? 2 : 1)
 moe_w2_contrib_kernel(const DecodeParams p) {
     using S = GeomB<G, MW, MT, KW, NCH, P>;
     static_assert(MW <= 4, "barrier slots");
@@ -759,7 +759,7 @@ __global__ void stage_activations_kernel(const void* __restrict__ x, int64_t x_s
 
 template <class KernelA, class KernelB>
 void launch_pair(aeon_b200_ctx* ctx, const DecodeParams& p, KernelA ka, int threads_a, int smem_a,
-                 KernelB kb, int threads_b, int smem_b, cudaStream_t stream) {
+                 KernelB kb, int threads_b, int smem_b, int ctas_per_sm_b, cudaStream_t stream) {
     AEON_CUDA_CHECK(cudaFuncSetAttribute(ka, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_a));
     AEON_CUDA_CHECK(cudaFuncSetAttribute(kb, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_b));
     cudaEvent_t* ev = nullptr;
@@ -777,7 +777,7 @@ void launch_pair(aeon_b200_ctx* ctx, const DecodeParams& p, KernelA ka, int thre
     ka<<<ctx->sm_count, threads_a, smem_a, stream>>>(p);
     AEON_CUDA_CHECK(cudaGetLastError());
     if (ev) AEON_CUDA_CHECK(cudaEventRecord(ev[1], stream));
-    kb<<<ctx->sm_count, threads_b, smem_b, stream>>>(p);
+    kb<<<ctx->sm_count * ctas_per_sm_b, threads_b, smem_b, stream>>>(p);
     AEON_CUDA_CHECK(cudaGetLastError());
     if (ev) AEON_CUDA_CHECK(cudaEventRecord(ev[2], stream));
     const int64_t vecs = static_cast<int64_t>(p.tokens) * p.H / 4;
@@ -793,13 +793,14 @@ template <int G, int KWA, int NCHA>
 void launch_decode_kernels(aeon_b200_ctx* ctx, const DecodeParams& p, cudaStream_t stream) {
     using SA = GeomA<G, KWA, NCHA>;
     // intermediate = 2048: two workers of eight warps, two 16-row tiles per worker, two chunks
-    // per warp, two items in flight
+    // per warp (64-row items). (Four K-warps x four chunks with two CTAs per SM was measured
+    // slower: the 128-register cap makes it spill.)
     using SB = GeomB<G, 2, 2, 8, 2, 1>;
     if (p.I != SB::kInter || p.H != SA::kHidden)
         throw StatusError(AEON_B200_ERR_UNSUPPORTED,
                           "aeon_b200_moe_decode: no kernel instance for this hidden/intermediate size");
     launch_pair(ctx, p, moe_w13_swiglu_kernel<G, KWA, NCHA>, SA::kThreads, SA::kSmem,
-                moe_w2_contrib_kernel<G, 2, 2, 8, 2, 1>, SB::kThreads, SB::kSmem, stream);
+                moe_w2_contrib_kernel<G, 2, 2, 8, 2, 1>, SB::kThreads, SB::kSmem, 1, stream);
 }
 
 __global__ void ep_combine_kernel(float* __restrict__ out, int64_t out_stride,
