@@ -189,6 +189,23 @@ int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_
                          const float* topk_weights, int tokens, float* moe_accum,
                          int64_t accum_stride, uint32_t flags, void* stream);
 
+/* Prefill path: the same contract as aeon_b200_moe_decode (moe_accum[t,:] += routed sum in
+ * slot order, fp32) for chunks of many tokens, computed as per-expert grouped GEMMs on the
+ * tcgen05 tensor cores: int4 weights are dequantised to fp16 into shared memory, the expert's
+ * tokens (gathered in expert order) are the other operand, accumulation is fp32 in tensor
+ * memory. Replaces V4TieredExpertExecutor::accumulate_routed_batch's grouped branch
+ * (src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:379-461), run_moe_grouped_expert_batch
+ * (src/architecture/deepseek_v4/moe/moe_grouped_batch.hpp:55-147) and the kernels
+ * moe_grouped_gate_up_kernel / moe_grouped_down_kernel
+ * (src/platform/rdna3/moe_grouped_ffn.hpp:77-288). MMA operands are fp16 (weights rounded once
+ * from q*scale, the hidden vector rounded to fp16 between the two GEMMs). Scratch for the
+ * chunk is allocated on the first call and grown when a larger chunk arrives (the reference's
+ * allocate_chunk_scratch, v4_expert_executor.hpp:127-153). tokens <= 65536. */
+int aeon_b200_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
+                          const void* x, int64_t x_stride, const int32_t* topk_ids,
+                          const float* topk_weights, int tokens, float* moe_accum,
+                          int64_t accum_stride, uint32_t flags, void* stream);
+
 /* Expert-parallel combine: out[t, :] += sum over r = 0..ranks-1, in rank order, of
  * partials[r, t, :] (fp32; partials is [ranks, tokens, hidden] dense, as an equal-split
  * all-to-all delivers it). The fixed order makes the result independent of arrival order.

@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_router_topk", "aeon_b200_expert_permutation", "aeon_b200_shared_expert",
     "aeon_b200_moe_decode", "aeon_b200_ctx_last_stats", "aeon_b200_synth_fill_experts",
     "aeon_b200_synth_fill_dense16", "aeon_b200_ctx_set_timing", "aeon_b200_ctx_kernel_times",
-    "aeon_b200_ep_combine", "aeon_b200_router_topk_noalloc",
+    "aeon_b200_ep_combine", "aeon_b200_router_topk_noalloc", "aeon_b200_moe_prefill",
 ]
 
 
@@ -109,6 +109,7 @@ def lib() -> ctypes.CDLL:
                                           c_int, c_void_p, c_int64, c_void_p]
     L.aeon_b200_moe_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                        c_void_p, c_int, c_void_p, c_int64, c_uint32, c_void_p]
+    L.aeon_b200_moe_prefill.argtypes = L.aeon_b200_moe_decode.argtypes
     L.aeon_b200_ep_combine.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]
     L.aeon_b200_synth_fill_experts.argtypes = [POINTER(MoeConfig), c_void_p, c_uint32, c_uint32,
                                                c_uint64, c_uint32, c_uint32, c_void_p, c_uint32,
@@ -282,6 +283,17 @@ class Context:
                                          x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
                                          _ptr(moe_accum), moe_accum.stride(0),
                                          DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
+
+
+def _moe_prefill(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum,
+                 skip_absent: bool = False):
+    check(lib().aeon_b200_moe_prefill(self._h, c_void_p(pool_base), _ptr(slot_of_expert), _ptr(x),
+                                      x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
+                                      _ptr(moe_accum), moe_accum.stride(0),
+                                      DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
+
+
+Context.moe_prefill = _moe_prefill
 
 
 def router_topk_noalloc(cfg: MoeConfig, x, gate, weights_out, ids_out, bias=None) -> None:

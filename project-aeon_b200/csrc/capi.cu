@@ -151,6 +151,7 @@ void free_ctx_buffers(aeon_b200_ctx* c) {
                     c->d_tile_done, c->d_error, c->d_sh_hi, c->d_sh_mid, c->d_sh_lo};
     for (void* b : bufs)
         if (b) (void)cudaFree(b);
+    free_prefill_scratch(c);
     if (c->timing_events) {
         for (cudaEvent_t e : *c->timing_events) (void)cudaEventDestroy(e);
         delete c->timing_events;
@@ -455,6 +456,18 @@ int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_
         DeviceGuard guard(ctx->device);
         launch_moe_decode(ctx, pool_base, slot_of_expert, x, x_stride, topk_ids, topk_weights, tokens,
                           moe_accum, accum_stride, flags, as_stream(stream));
+    });
+}
+
+int aeon_b200_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
+                          const void* x, int64_t x_stride, const int32_t* topk_ids,
+                          const float* topk_weights, int tokens, float* moe_accum,
+                          int64_t accum_stride, uint32_t flags, void* stream) {
+    return guarded([&] {
+        require(ctx != nullptr, "aeon_b200_moe_prefill: null context");
+        DeviceGuard guard(ctx->device);
+        launch_moe_prefill(ctx, pool_base, slot_of_expert, x, x_stride, topk_ids, topk_weights, tokens,
+                           moe_accum, accum_stride, flags, as_stream(stream));
     });
 }
 

@@ -120,6 +120,9 @@ struct aeon_b200_ctx {
     double timing_ms[2];
     int64_t timing_launches[2];
 
+    // prefill (grouped GEMM) scratch, allocated on first use and grown on demand
+    void* prefill;
+
     // shared expert scratch
     __half* d_sh_hi;        // [max_tokens, I] (hi/mid/lo split of the fp32 hidden)
     __half* d_sh_mid;
@@ -145,6 +148,11 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
                        const void* x, int64_t x_stride, const int32_t* topk_ids,
                        const float* topk_weights, int tokens, float* moe_accum,
                        int64_t accum_stride, uint32_t flags, cudaStream_t stream);
+void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
+                        const void* x, int64_t x_stride, const int32_t* topk_ids,
+                        const float* topk_weights, int tokens, float* moe_accum, int64_t accum_stride,
+                        uint32_t flags, cudaStream_t stream);
+void free_prefill_scratch(aeon_b200_ctx* ctx);
 void launch_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks,
                        int tokens, int hidden, cudaStream_t stream);
 void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,

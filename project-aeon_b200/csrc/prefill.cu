@@ -1,0 +1,582 @@
+// Prefill path: per-expert grouped GEMMs on the tcgen05 tensor cores of sm_100a.
+//
+// Stands in for the reference's grouped expert pair and its scheduler:
+// moe_grouped_gate_up_kernel / moe_grouped_down_kernel
+// (src/platform/rdna3/moe_grouped_ffn.hpp:77-288), the dequantising feed
+// (src/backend/swizzled_w4a16/kernels/swizzled_w4a16_feed.hpp:52-92) and
+// run_moe_grouped_expert_batch (src/architecture/deepseek_v4/moe/moe_grouped_batch.hpp:55-147).
+// The reference batches experts eight at a time from the host after a device-to-host copy of
+// the offsets; here the tile list is built on the device and one persistent launch per GEMM
+// walks it, so there is no host round trip and no per-launch expert limit.
+//
+// Shape of one tile. The weight rows are the MMA M dimension (128 per tile, always full),
+// the expert's tokens the N dimension (16..256, so ragged token counts cost little), K runs in
+// blocks of 64:
+//     D[128 weight rows, N tokens] += Wq[128, 64] * X[N, 64]^T        (tcgen05.mma kind::f16)
+// with the fp32 accumulator in tensor memory (two buffers of 256 columns, so the epilogue of
+// one tile overlaps the main loop of the next).
+//
+// Warp roles of a CTA (320 threads):
+//   warps 0-3  epilogue: tcgen05.ld their TMEM lane quadrant, finish (SwiGLU / routing weight),
+//              store;
+//   warps 4-7  dequantise: each thread owns one weight row of the tile, loads its packed int4
+//              atoms with 128-bit loads, converts to fp16 * scale in registers and writes the
+//              row into the 128-byte-swizzled K-major operand tile in shared memory;
+//   warp 8     one thread issues the tiled TMA loads of the activation operand (no multicast);
+//   warp 9     one thread issues the MMAs and the commits; the warp owns the TMEM allocation.
+// A 4-stage ring of (weight tile, activation tile) pairs connects them through mbarriers.
+// Every wait is bounded; a wait that runs out sets the context's error flag, after which all
+// waits fall through and the kernel ends (TMEM is always freed).
+//
+// Numerics. MMA operands are fp16: the weight operand is fp16(q * scale) (one rounding of the
+// exact product), activations are the 16-bit inputs converted to fp16, the hidden vector is
+// rounded to fp16 between the two GEMMs, accumulation is fp32. The parity oracle applies the
+// same three roundings (the method of the reference's own grouped gate,
+// tests/test_v4_grouped_wmma_oracle.cpp:63-73,219-228).
+//
+// GEMM 1 tiles interleave W1 and W3: tile row r is row (rb*64 + (r/32)*16 + r%16) of W1 when
+// (r/16) is even and of W3 when odd, so a gate value and its up value sit 16 lanes apart in one
+// warp of the epilogue and meet through one shuffle.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tc5.cuh"
+
+#include <algorithm>
+#include <mutex>
+
+namespace aeon_b200 {
+
+namespace {
+
+constexpr int kTileM = 128;         // weight rows per tile
+constexpr int kTileK = 64;          // K per pipeline stage (one 128-byte swizzled row)
+constexpr int kMaxN = 256;          // tokens per tile
+constexpr int kStages = 4;
+constexpr int kEpilogueWarps = 4, kDequantWarps = 4;
+constexpr int kThreads = (kEpilogueWarps + kDequantWarps + 2) * 32;
+constexpr int kStageA = kTileM * kTileK * 2;          // 16 KB
+constexpr int kStageB = kMaxN * kTileK * 2;           // 32 KB
+constexpr int kSmemBytes = 1024 /*align*/ + kStages * (kStageA + kStageB) + 256 /*barriers*/;
+constexpr int kTmemCols = 512;
+
+struct PrefillTile {
+    int slot;      // pool slot of the expert
+    int pos0;      // first position (expert-sorted order)
+    int ntok;      // tokens of this tile (<= kMaxN)
+    int pad;
+};
+
+struct PrefillParams {
+    const uint8_t* pool;
+    uint64_t payload_bytes;
+    MatrixGeom w1, w2, w3;
+    int group;
+    int H, I;
+    const PrefillTile* tiles;
+    const int32_t* n_tiles;
+    const int32_t* draw_idx;
+    const float* wpos;
+    __half* hidden;       // [positions, I] fp16
+    float* contrib;       // [draws, H] fp32
+    float limit;
+    int32_t* error;
+};
+
+__device__ __forceinline__ void flag_error(int32_t* error, int code) { atomicCAS(error, kErrNone, code); }
+
+__device__ __forceinline__ uint4 ldg128(const uint8_t* p) {
+    uint4 v;
+    asm("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// One packed word (8 columns) -> 8 fp16 values fp16((nibble - 8) * scale) in column order.
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, uint32_t scale2) {
+    uint32_t p[4];
+    ptx::unpack_word(w, p);     // exact integers nibble - 8 as fp16 pairs
+    return make_uint4(hmul2_u32(p[0], scale2), hmul2_u32(p[1], scale2), hmul2_u32(p[2], scale2),
+                      hmul2_u32(p[3], scale2));
+}
+
+// kGateUp: GEMM 1 (W1/W3 interleaved rows, K = hidden, SwiGLU epilogue -> hidden fp16)
+// else:    GEMM 2 (W2 rows, K = intermediate, routing-weight epilogue -> contrib fp32)
+template <bool kGateUp, int G>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap act_map) {
+    extern __shared__ uint8_t smem_raw[];
+    // the swizzled operand tiles need 1024-byte alignment
+    const uint32_t smem0 = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem0 - ptx::smem_u32(smem_raw));
+    const uint32_t a_smem = smem0;
+    const uint32_t b_smem = smem0 + kStages * kStageA;
+    const uint32_t bar0 = b_smem + kStages * kStageB;
+    const uint32_t full_bar = bar0;                    // kStages
+    const uint32_t empty_bar = bar0 + 8 * kStages;     // kStages
+    const uint32_t acc_full = bar0 + 16 * kStages;     // 2
+    const uint32_t acc_empty = acc_full + 16;          // 2
+    const uint32_t tmem_slot = acc_empty + 16;         // 4 B
+    volatile uint32_t* tmem_slot_gen =
+        reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem0));
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(full_bar + 8 * s, kDequantWarps + 1);
+            ptx::mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(acc_full + 8 * b, 1);
+            ptx::mbar_init(acc_empty + 8 * b, kEpilogueWarps);
+        }
+        ptx::fence_barrier_init();
+    }
+    if (warp == 9) {
+        tc5::tmem_alloc(tmem_slot, kTmemCols);
+        tc5::tmem_relinquish();
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    const int K = kGateUp ? p.H : p.I;
+    const int row_blocks = kGateUp ? (2 * p.I) / kTileM : p.H / kTileM;
+    const int kblocks = K / kTileK;
+    const int n_tiles = *p.n_tiles;
+    const int total_items = n_tiles * row_blocks;
+
+    if (warp == 8) {
+        // ------------------------------ TMA: activation operand ------------------------------
+        if (lane == 0) {
+            uint32_t n = 0;
+            for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+                const PrefillTile tile = p.tiles[item / row_blocks];
+                const int boxes = (tile.ntok + 63) / 64;
+                for (int kb = 0; kb < kblocks; ++kb, ++n) {
+                    const int s = n % kStages;
+                    const uint32_t parity = (n / kStages) & 1;
+                    if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
+                    ptx::mbar_arrive_expect_tx(full_bar + 8 * s, boxes * 64 * kTileK * 2);
+                    for (int b = 0; b < boxes; ++b)
+                        tc5::tma_load_2d(b_smem + s * kStageB + b * (64 * kTileK * 2), &act_map,
+                                         kb * kTileK, tile.pos0 + b * 64, full_bar + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------ MMA issue ---------------------------------------------
+        if (lane == 0) {
+            uint32_t n = 0, it = 0;
+            for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+                const PrefillTile tile = p.tiles[item / row_blocks];
+                const uint32_t n_mma = static_cast<uint32_t>((tile.ntok + 15) & ~15);
+                const uint32_t idesc = tc5::idesc_f16(kTileM, n_mma);
+                const uint32_t buf = it & 1;
+                if (!ptx::mbar_wait(acc_empty + 8 * buf, ((it >> 1) & 1) ^ 1, p.error))
+                    flag_error(p.error, kErrWaitTimeout);
+                tc5::fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * kMaxN;
+                for (int kb = 0; kb < kblocks; ++kb, ++n) {
+                    const int s = n % kStages;
+                    const uint32_t parity = (n / kStages) & 1;
+                    if (!ptx::mbar_wait(full_bar + 8 * s, parity, p.error)) flag_error(p.error, kErrWaitTimeout);
+                    tc5::fence_after_sync();
+                    const uint32_t a_addr = a_smem + s * kStageA;
+                    const uint32_t b_addr = b_smem + s * kStageB;
+#pragma unroll
+                    for (int kk = 0; kk < kTileK / 16; ++kk) {
+                        tc5::mma_f16_ss(d_tmem, tc5::smem_desc_sw128(a_addr + kk * 32),
+                                        tc5::smem_desc_sw128(b_addr + kk * 32), idesc,
+                                        (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc5::commit(empty_bar + 8 * s);      // stage free when these MMAs are done
+                }
+                tc5::commit(acc_full + 8 * buf);         // accumulator complete
+            }
+        }
+    } else if (warp >= kEpilogueWarps) {
+        // ------------------------------ dequantise the weight operand ------------------------
+        const int r = tid - kEpilogueWarps * 32;          // tile row owned by this thread, 0..127
+        const uint64_t stream_policy = ptx::policy_evict_first();
+        (void)stream_policy;
+        uint32_t n = 0;
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+            const int ti = item / row_blocks;
+            const int rb = item - ti * row_blocks;
+            const PrefillTile tile = p.tiles[ti];
+            const uint8_t* payload = p.pool + static_cast<uint64_t>(tile.slot < 0 ? 0 : tile.slot) * p.payload_bytes;
+            // which matrix and which row of it this thread feeds
+            const MatrixGeom* gm;
+            int row;
+            if constexpr (kGateUp) {
+                gm = ((r >> 4) & 1) ? &p.w3 : &p.w1;
+                row = rb * 64 + (r >> 5) * 16 + (r & 15);
+            } else {
+                gm = &p.w2;
+                row = rb * kTileM + r;
+            }
+            const int rpw = gm->rpw, lpr = gm->lpr;
+            const int blk = row / rpw, rib = row - blk * rpw;
+            // packed atoms of a row: iteration `itn` holds lpr consecutive atoms (32 columns
+            // each) at (blk * iters + itn) * 512 + rib * lpr * 16
+            const uint8_t* packed = payload + gm->packed_offset + static_cast<size_t>(blk) * gm->block_bytes +
+                                    rib * lpr * 16;
+            const uint8_t* scales = payload + gm->scale_offset + static_cast<size_t>(blk) * gm->block_scale_bytes;
+            const int apg = G / 32;                        // atoms per scale group
+            const int scales_per_iter_row = lpr / apg;     // scales of one row in one iteration
+            const int scale_row_stride = 32 / apg * 2;     // bytes of scales per iteration
+            const uint32_t row_smem = (r >> 3) * 1024 + (r & 7) * 128;
+            for (int kb = 0; kb < kblocks; ++kb, ++n) {
+                const int s = n % kStages;
+                const uint32_t parity = (n / kStages) & 1;
+                // the two atoms (64 columns) of this k-block
+                const int atom0 = kb * 2;
+                const int itn = atom0 / lpr, sl = atom0 - itn * lpr;
+                const uint8_t* src = packed + static_cast<size_t>(itn) * 512 + sl * 16;
+                const uint4 q0 = ldg128(src);
+                const uint4 q1 = ldg128(src + 16);
+                const uint8_t* sc = scales + itn * scale_row_stride + (rib * scales_per_iter_row) * 2;
+                const uint16_t s0 = __ldg(reinterpret_cast<const uint16_t*>(sc) + sl / apg);
+                const uint16_t s1 = __ldg(reinterpret_cast<const uint16_t*>(sc) + (sl + 1) / apg);
+                const uint32_t s0x2 = static_cast<uint32_t>(s0) * 0x10001u;
+                const uint32_t s1x2 = static_cast<uint32_t>(s1) * 0x10001u;
+                if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
+                uint8_t* dst = smem_gen + (s * kStageA) + row_smem;
+                const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = dequant_word(words[c], c < 4 ? s0x2 : s1x2);
+                    *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = v;
+                }
+                // generic-proxy writes must be visible to the tensor core (async proxy)
+                ptx::fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(full_bar + 8 * s);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue -------------------------------------------------
+        const int quad = warp;                              // TMEM lanes 32*quad .. +31
+        uint32_t it = 0;
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+            const int ti = item / row_blocks;
+            const int rb = item - ti * row_blocks;
+            const PrefillTile tile = p.tiles[ti];
+            const uint32_t buf = it & 1;
+            if (!ptx::mbar_wait(acc_full + 8 * buf, (it >> 1) & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
+            tc5::fence_after_sync();
+            const uint32_t taddr = tmem_base + ((static_cast<uint32_t>(quad) * 32u) << 16) + buf * kMaxN;
+            for (int c0 = 0; c0 < tile.ntok; c0 += 32) {
+                uint32_t v[32];
+                tc5::ld_32x32(taddr + c0, v);
+                tc5::ld_wait();
+                if constexpr (kGateUp) {
+                    const int hcol = rb * 64 + quad * 16 + (lane & 15);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float mine = __uint_as_float(v[j]);
+                        const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 16);
+                        if (lane < 16 && c0 + j < tile.ntok) {
+                            float gate = fminf(mine, p.limit);
+                            float up = fminf(fmaxf(other, -p.limit), p.limit);
+                            const float h = (gate / (1.0f + expf(-gate))) * up;
+                            p.hidden[static_cast<size_t>(tile.pos0 + c0 + j) * p.I + hcol] = __float2half_rn(h);
+                        }
+                    }
+                } else {
+                    const int row = rb * kTileM + quad * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (c0 + j < tile.ntok) {
+                            const int pos = tile.pos0 + c0 + j;
+                            p.contrib[static_cast<size_t>(p.draw_idx[pos]) * p.H + row] =
+                                p.wpos[pos] * __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+            tc5::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty + 8 * buf);
+        }
+    }
+
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == 9) {
+        tc5::fence_after_sync();
+        tc5::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// Activation rows gathered into expert-sorted order as fp16: xg[pos, :] = fp16(x[token_idx[pos], :]).
+__global__ void gather_activations_kernel(const void* __restrict__ x, int64_t x_stride, int dtype,
+                                          const int32_t* __restrict__ token_idx,
+                                          const int32_t* __restrict__ counts, int H,
+                                          __half* __restrict__ xg) {
+    const int placed = counts[2];
+    const int vec_per_row = H / 8;
+    const int64_t total = static_cast<int64_t>(placed) * vec_per_row;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int pos = static_cast<int>(i / vec_per_row);
+        const int v = static_cast<int>(i - static_cast<int64_t>(pos) * vec_per_row);
+        const int token = token_idx[pos];
+        const uint4 in = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + token * x_stride)[v];
+        uint4 out = in;
+        if (dtype == AEON_B200_BF16) {
+            const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float lo = __uint_as_float(w[k] << 16), hi = __uint_as_float(w[k] & 0xFFFF0000u);
+                const __half2 h = __floats2half2_rn(lo, hi);
+                o[k] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            out = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        reinterpret_cast<uint4*>(xg + static_cast<size_t>(pos) * H)[v] = out;
+    }
+}
+
+// Tile list: every expert's positions in runs of at most kMaxN. One CTA; experts <= 1024.
+__global__ void build_tiles_kernel(const int32_t* __restrict__ offsets, const int32_t* __restrict__ slot_of,
+                                   int experts, int skip_absent, PrefillTile* __restrict__ tiles,
+                                   int32_t* __restrict__ n_tiles, int32_t* __restrict__ error) {
+    __shared__ int base[1025];
+    const int e = threadIdx.x;
+    int count = 0, slot = -1;
+    if (e < experts) {
+        count = offsets[e + 1] - offsets[e];
+        slot = slot_of ? slot_of[e] : e;
+        if (slot < 0 && count > 0) {
+            if (skip_absent) count = 0;
+            else atomicCAS(error, kErrNone, kErrExpertAbsent);
+        }
+    }
+    const int mine = (count + kMaxN - 1) / kMaxN;
+    base[e] = mine;
+    __syncthreads();
+    if (e == 0) {
+        int run = 0;
+        for (int i = 0; i < experts; ++i) { const int c = base[i]; base[i] = run; run += c; }
+        base[experts] = run;
+        *n_tiles = run;
+    }
+    __syncthreads();
+    if (e < experts) {
+        for (int c = 0; c < mine; ++c) {
+            PrefillTile t;
+            t.slot = slot;
+            t.pos0 = offsets[e] + c * kMaxN;
+            t.ntok = min(kMaxN, count - c * kMaxN);
+            t.pad = e;
+            tiles[base[e] + c] = t;
+        }
+    }
+}
+
+__global__ void moe_accumulate_prefill_kernel(float* __restrict__ accum, int64_t accum_stride,
+                                              const float* __restrict__ contrib,
+                                              const int32_t* __restrict__ ids,
+                                              const int32_t* __restrict__ slot_of, int skip_absent,
+                                              int experts, int tokens, int top_k, int H) {
+    const int vec_per_row = H / 4;
+    const int64_t total = static_cast<int64_t>(tokens) * vec_per_row;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int token = static_cast<int>(i / vec_per_row);
+        const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
+        float4* dst = reinterpret_cast<float4*>(accum + token * accum_stride) + v;
+        float4 a = *dst;
+        for (int slot = 0; slot < top_k; ++slot) {
+            const int draw = token * top_k + slot;
+            const int id = ids[draw];
+            if (id >= 0 && id < experts && !(skip_absent && slot_of[id] < 0)) {
+                const float4 c = reinterpret_cast<const float4*>(contrib + static_cast<size_t>(draw) * H)[v];
+                a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
+            }
+        }
+        *dst = a;
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    if (!fn) throw StatusError(AEON_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    return fn;
+}
+
+// Row-major fp16 matrix [rows, cols]; box = 64 columns (128 B) x 64 rows, 128-byte swizzle.
+CUtensorMap make_act_map(const void* base, uint64_t rows, uint64_t cols) {
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {cols, rows};
+    const cuuint64_t gstride[1] = {cols * 2};
+    const cuuint32_t box[2] = {kTileK, 64};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult rc = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim,
+                                       gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS)
+        throw StatusError(AEON_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(rc));
+    return map;
+}
+
+}  // namespace
+
+struct PrefillScratch {
+    int max_tokens{0};
+    __half* xg{nullptr};
+    __half* hidden{nullptr};
+    float* contrib{nullptr};
+    int32_t *offsets{nullptr}, *token_idx{nullptr}, *draw_idx{nullptr}, *counts{nullptr}, *n_tiles{nullptr};
+    float* wpos{nullptr};
+    PrefillTile* tiles{nullptr};
+    WorkEntry* entries{nullptr};
+    CUtensorMap x_map, h_map;
+    uint64_t bytes{0};
+};
+
+void free_prefill_scratch(aeon_b200_ctx* ctx) {
+    PrefillScratch* s = static_cast<PrefillScratch*>(ctx->prefill);
+    if (!s) return;
+    void* bufs[] = {s->xg, s->hidden, s->contrib, s->offsets, s->token_idx, s->draw_idx, s->counts,
+                    s->n_tiles, s->wpos, s->tiles, s->entries};
+    for (void* b : bufs)
+        if (b) (void)cudaFree(b);
+    delete s;
+    ctx->prefill = nullptr;
+}
+
+static PrefillScratch* ensure_scratch(aeon_b200_ctx* ctx, int tokens) {
+    PrefillScratch* s = static_cast<PrefillScratch*>(ctx->prefill);
+    if (s && s->max_tokens >= tokens) return s;
+    free_prefill_scratch(ctx);
+    s = new PrefillScratch();
+    ctx->prefill = s;
+    const aeon_b200_moe_config& cfg = ctx->cfg;
+    const size_t draws = static_cast<size_t>(tokens) * cfg.top_k;
+    auto alloc = [&](auto*& ptr, size_t count) {
+        AEON_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&ptr), count * sizeof(*ptr)));
+        s->bytes += count * sizeof(*ptr);
+    };
+    // 64 spare rows so a TMA box that starts inside the last tile stays inside the allocation
+    alloc(s->xg, (draws + 64) * cfg.hidden);
+    alloc(s->hidden, (draws + 64) * cfg.intermediate);
+    alloc(s->contrib, draws * cfg.hidden);
+    alloc(s->offsets, cfg.experts + 1);
+    alloc(s->token_idx, draws);
+    alloc(s->draw_idx, draws);
+    alloc(s->wpos, draws);
+    alloc(s->counts, 4);
+    alloc(s->n_tiles, 1);
+    alloc(s->tiles, cfg.experts + draws / kMaxN + 1);
+    alloc(s->entries, cfg.experts + draws / 8 + 1);
+    AEON_CUDA_CHECK(cudaMemset(s->xg, 0, (draws + 64) * cfg.hidden * sizeof(__half)));
+    AEON_CUDA_CHECK(cudaMemset(s->hidden, 0, (draws + 64) * cfg.intermediate * sizeof(__half)));
+    s->x_map = make_act_map(s->xg, draws + 64, cfg.hidden);
+    s->h_map = make_act_map(s->hidden, draws + 64, cfg.intermediate);
+    s->max_tokens = tokens;
+    return s;
+}
+
+void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
+                        const void* x, int64_t x_stride, const int32_t* topk_ids,
+                        const float* topk_weights, int tokens, float* moe_accum, int64_t accum_stride,
+                        uint32_t flags, cudaStream_t stream) {
+    const aeon_b200_moe_config& cfg = ctx->cfg;
+    require(pool_base && slot_of_expert && x && topk_ids && topk_weights && moe_accum,
+            "aeon_b200_moe_prefill: null pointer argument");
+    require(tokens > 0 && tokens <= 65536, "aeon_b200_moe_prefill: tokens must be in [1, 65536]");
+    require(x_stride >= cfg.hidden && x_stride % 8 == 0 && accum_stride >= cfg.hidden && accum_stride % 4 == 0,
+            "aeon_b200_moe_prefill: bad row stride");
+    require(cfg.hidden % kTileM == 0 && (2 * cfg.intermediate) % kTileM == 0,
+            "aeon_b200_moe_prefill: hidden and 2*intermediate must be multiples of 128");
+    PrefillScratch* s = ensure_scratch(ctx, tokens);
+    const bool skip = (flags & AEON_B200_DECODE_SKIP_ABSENT) != 0;
+
+    launch_permutation(ctx, topk_ids, tokens, cfg.top_k, cfg.experts, s->offsets, s->token_idx, s->draw_idx,
+                       topk_weights, s->wpos, slot_of_expert, s->entries, s->counts, skip, stream);
+    build_tiles_kernel<<<1, 1024, 0, stream>>>(s->offsets, slot_of_expert, cfg.experts, skip ? 1 : 0, s->tiles,
+                                               s->n_tiles, ctx->d_error);
+    AEON_CUDA_CHECK(cudaGetLastError());
+    gather_activations_kernel<<<4 * ctx->sm_count, 256, 0, stream>>>(x, x_stride, cfg.act_dtype, s->token_idx,
+                                                                     s->counts, cfg.hidden, s->xg);
+    AEON_CUDA_CHECK(cudaGetLastError());
+
+    PrefillParams p{};
+    p.pool = static_cast<const uint8_t*>(pool_base);
+    p.payload_bytes = ctx->geom.payload_bytes;
+    p.w1 = ctx->geom.w1;
+    p.w2 = ctx->geom.w2;
+    p.w3 = ctx->geom.w3;
+    p.group = cfg.group_size;
+    p.H = cfg.hidden;
+    p.I = cfg.intermediate;
+    p.tiles = s->tiles;
+    p.n_tiles = s->n_tiles;
+    p.draw_idx = s->draw_idx;
+    p.wpos = s->wpos;
+    p.hidden = s->hidden;
+    p.contrib = s->contrib;
+    p.limit = cfg.swiglu_limit;
+    p.error = ctx->d_error;
+
+    cudaEvent_t* ev = nullptr;
+    if (ctx->timing_enabled) {
+        std::vector<cudaEvent_t>& pool = *ctx->timing_events;
+        if (ctx->timing_used + 3 > pool.size()) {
+            const size_t old = pool.size();
+            pool.resize(old + 96);
+            for (size_t i = old; i < pool.size(); ++i) AEON_CUDA_CHECK(cudaEventCreate(&pool[i]));
+        }
+        ev = &pool[ctx->timing_used];
+        ctx->timing_used += 3;
+        AEON_CUDA_CHECK(cudaEventRecord(ev[0], stream));
+    }
+    auto launch = [&](auto kernel, const CUtensorMap& map) {
+        AEON_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        kernel<<<ctx->sm_count, kThreads, kSmemBytes, stream>>>(p, map);
+        AEON_CUDA_CHECK(cudaGetLastError());
+    };
+    if (cfg.group_size == 128) launch(moe_grouped_gemm_kernel<true, 128>, s->x_map);
+    else launch(moe_grouped_gemm_kernel<true, 32>, s->x_map);
+    if (ev) AEON_CUDA_CHECK(cudaEventRecord(ev[1], stream));
+    if (cfg.group_size == 128) launch(moe_grouped_gemm_kernel<false, 128>, s->h_map);
+    else launch(moe_grouped_gemm_kernel<false, 32>, s->h_map);
+    if (ev) AEON_CUDA_CHECK(cudaEventRecord(ev[2], stream));
+
+    const int64_t vecs = static_cast<int64_t>(tokens) * cfg.hidden / 4;
+    const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 8 * ctx->sm_count));
+    moe_accumulate_prefill_kernel<<<blocks, 256, 0, stream>>>(moe_accum, accum_stride, s->contrib, topk_ids,
+                                                              slot_of_expert, skip ? 1 : 0, cfg.experts, tokens,
+                                                              cfg.top_k, cfg.hidden);
+    AEON_CUDA_CHECK(cudaGetLastError());
+    ctx->launches += 6;
+}
+
+}  // namespace aeon_b200

@@ -1,0 +1,115 @@
+// Inline-PTX wrappers for the 5th-generation tensor core path of sm_100a: tensor memory
+// (TMEM) allocation, tcgen05.mma with shared-memory operand descriptors, commit to an
+// mbarrier, TMEM loads, and the tiled TMA load that feeds the activation operand.
+#pragma once
+
+#include <cuda.h>
+#include <cstdint>
+
+namespace aeon_b200 {
+namespace tc5 {
+
+// ---- tensor memory -----------------------------------------------------------------------
+// One warp allocates `cols` TMEM columns (a power of two >= 32) and the base address lands
+// in shared memory; the same warp frees them before the CTA exits.
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(cols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---- operand descriptors ---------------------------------------------------------------------
+// K-major operand tile in shared memory with the 128-byte swizzle: a row is 64 16-bit
+// elements (128 B); 8 rows form a 1024-byte group inside which the 16-byte chunk c of row r
+// sits at chunk (c ^ (r & 7)); groups follow each other every 1024 B (the stride byte offset).
+// Descriptor fields (64 bit): [0,14) start address >> 4, [16,30) leading byte offset >> 4
+// (unused for swizzled K-major, set to 1), [32,46) stride byte offset >> 4, [46,48) version
+// (1 on sm_100), [61,64) swizzle mode (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16 with fp16 operands, fp32 accumulation, both operands
+// K-major: [4,6) D format (1 = f32), [7,10) A format (0 = f16), [10,13) B format (0 = f16),
+// bit 15 / 16 A / B major (0 = K), [17,23) N >> 3, [24,29) M >> 4.
+__device__ __forceinline__ uint32_t idesc_f16(uint32_t m, uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, one CTA, issued by a single thread.
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The mbarrier gets one arrival when every MMA issued so far by this thread has finished
+// (implies tcgen05.fence::before_thread_sync).
+__device__ __forceinline__ void commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar)
+                 : "memory");
+}
+
+// 32 lanes x 32 columns of fp32 accumulators: thread i of the warp gets lane (base lane + i),
+// columns [col, col + 32). A warp may only touch the TMEM lane quadrant 32 * (warp % 4).
+__device__ __forceinline__ void ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- tiled TMA load (no multicast) --------------------------------------------------------------
+// 2-D box of a row-major 16-bit matrix into shared memory; x is the element offset in a row
+// (a multiple of 8, i.e. 16 bytes), y the row. Rows past the matrix end are zero-filled.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(mbar)
+        : "memory");
+}
+
+}  // namespace tc5
+}  // namespace aeon_b200
