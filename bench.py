@@ -42,12 +42,14 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/8/32/128 sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default="full", choices=["full", "small", "b1"],
+    ap.add_argument("--case", default="full", choices=["full", "small", "b1", "prefill_small"],
                     help="small: one layer of 64 experts at batch 32 (1.45 GB of weights, larger "
                          "than L2), the case the ncu captures under profiles/ run; not a bench value")
     args = ap.parse_args()
     if args.case == "small":
         args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 32, True, True
+    if args.case == "prefill_small":   # 64 experts, 512 tokens through the grouped GEMMs (ncu captures)
+        args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 8, True, True
     if args.case == "b1":      # configuration 1 at batch 1 over 8 layers (launch lists)
         args.batch, args.no_sweep, args.no_cpu_baseline = 1, True, True
     return args
@@ -183,6 +185,63 @@ def workload_config(args, n_gpus):
 
 
 # ----------------------------------------------------------------------------------------
+# Prefill (benchmark configuration 2): 4096 tokens through one layer, router logits plus a
+# Zipf(s = 1.1)-shaped bias over a seeded expert permutation so per-expert token counts are
+# ragged; measures the grouped int4 -> fp16 tcgen05 GEMMs.
+# ----------------------------------------------------------------------------------------
+def prefill_bench(model, cfg, peaks, tokens=4096, iters=5):
+    import numpy as np
+    import torch
+    from aeon_b200 import synth
+    w = model.weights[0]
+    ctx = model.ctx
+    H, I, E, k = cfg.hidden, cfg.intermediate, cfg.experts, cfg.top_k
+    x_bits = synth.normal_bits(np.random.default_rng([SEED, 0xF111]), (tokens, H), 1.0, cfg.act_dtype)
+    x = torch.from_numpy(x_bits.view(np.int16)).view(torch.bfloat16).cuda()
+    # routing: input preparation, not part of the timed path
+    rank_of = np.random.default_rng([SEED, 0x21FF]).permutation(E) + 1
+    bias = torch.from_numpy((-1.1 * 0.35 * np.log(rank_of)).astype(np.float32)).cuda()
+    logits = x.float() @ w.gate.float().T + bias
+    scores = torch.sigmoid(logits)
+    top_w, top_i = torch.topk(scores, k, dim=1)
+    weights = (top_w / top_w.sum(dim=1, keepdim=True)).contiguous()
+    ids = top_i.to(torch.int32).contiguous()
+    counts = torch.bincount(ids.flatten().long(), minlength=E).cpu().numpy()
+    out = torch.zeros(tokens, H, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        ctx.moe_prefill(w.pool.base, w.slot_of, x, ids, weights, out)
+    ctx.check()
+    ctx.set_timing(True)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        ctx.moe_prefill(w.pool.base, w.slot_of, x, ids, weights, out)
+    end.record()
+    torch.cuda.synchronize()
+    (ms1, n1), (ms2, n2) = ctx.kernel_times()
+    ctx.set_timing(False)
+    ms = start.elapsed_time(end) / iters
+    flops = tokens * k * 6.0 * H * I
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    sustained = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    gemm_ms = (ms1 + ms2) / max(n1, 1)
+    return {
+        "workload": f"cfg2: {tokens} tokens x top-{k}, one layer, Zipf-biased routing",
+        "tokens_per_expert": {"min": int(counts.min()), "mean": float(counts.mean()),
+                              "max": int(counts.max()), "empty": int((counts == 0).sum())},
+        "ms_per_layer": ms, "tokens_per_s": tokens / (ms * 1e-3),
+        "routed_tflops": flops / (ms * 1e-3) / 1e12,
+        "gemm_kernels_ms": gemm_ms, "gemm1_ms": ms1 / max(n1, 1), "gemm2_ms": ms2 / max(n2, 1),
+        "gemm_kernels_tflops": flops / (gemm_ms * 1e-3) / 1e12,
+        "roofline": {"bound": "tensor", "achieved": flops / (gemm_ms * 1e-3) / 1e12, "peak": peak,
+                     "unit": "TFLOP/s", "frac": flops / (gemm_ms * 1e-3) / 1e12 / peak,
+                     "frac_of_sustained": flops / (gemm_ms * 1e-3) / 1e12 / sustained,
+                     "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst)" if "bf16_tflops" in peaks
+                     else "fallback 1590 TFLOP/s"},
+    }
+
+
+# ----------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------
 def main():
@@ -210,7 +269,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     cfg = aeon_b200.preset("baseline")
-    if args.case == "small":
+    if args.case in ("small", "prefill_small"):
         cfg = cfg.copy(experts=64)
     model = stack.MoeStack(cfg, layers=args.layers, max_tokens=args.batch, seed=SEED,
                            device=local_rank, rank=rank, world=world, dist=dist)
@@ -333,6 +392,10 @@ def main():
     if world == 1 and not args.no_sweep:
         line["decode_sweep"] = model.batch_sweep([1, 8, 32, 128], x_dev, out_dev, peak_gbs,
                                                  iters=max(10, args.steps))
+    if world == 1 and not args.no_sweep:
+        line["prefill"] = prefill_bench(model, cfg, peaks, iters=max(3, min(args.steps, 10)))
+    if args.case == "prefill_small":
+        line["prefill"] = prefill_bench(model, cfg, peaks, tokens=512, iters=2)
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
         tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, 1)
         line["cpu_baseline"] = {

@@ -16,14 +16,15 @@
 // with the fp32 accumulator in tensor memory (two buffers of 256 columns, so the epilogue of
 // one tile overlaps the main loop of the next).
 //
-// Warp roles of a CTA (320 threads):
+// Warp roles of a CTA (448 threads):
 //   warps 0-3  epilogue: tcgen05.ld their TMEM lane quadrant, finish (SwiGLU / routing weight),
 //              store;
-//   warps 4-7  dequantise: each thread owns one weight row of the tile, loads its packed int4
-//              atoms with 128-bit loads, converts to fp16 * scale in registers and writes the
-//              row into the 128-byte-swizzled K-major operand tile in shared memory;
-//   warp 8     one thread issues the tiled TMA loads of the activation operand (no multicast);
-//   warp 9     one thread issues the MMAs and the commits; the warp owns the TMEM allocation.
+//   warps 4-11 dequantise: two threads per weight row of the tile; a thread loads its packed
+//              int4 atom with a 128-bit load (four k-blocks ahead), converts it to
+//              fp16(q * scale) in registers and writes its half of the row into the
+//              128-byte-swizzled K-major operand tile in shared memory;
+//   warp 12    one thread issues the tiled TMA loads of the activation operand (no multicast);
+//   warp 13    one thread issues the MMAs and the commits; the warp owns the TMEM allocation.
 // A 4-stage ring of (weight tile, activation tile) pairs connects them through mbarriers.
 // Every wait is bounded; a wait that runs out sets the context's error flag, after which all
 // waits fall through and the kernel ends (TMEM is always freed).
@@ -52,7 +53,8 @@ constexpr int kTileM = 128;         // weight rows per tile
 constexpr int kTileK = 64;          // K per pipeline stage (one 128-byte swizzled row)
 constexpr int kMaxN = 256;          // tokens per tile
 constexpr int kStages = 4;
-constexpr int kEpilogueWarps = 4, kDequantWarps = 4;
+constexpr int kEpilogueWarps = 4, kDequantWarps = 8;
+constexpr int kPrefetch = 4;         // k-blocks of packed weights a dequantising thread keeps in flight
 constexpr int kThreads = (kEpilogueWarps + kDequantWarps + 2) * 32;
 constexpr int kStageA = kTileM * kTileK * 2;          // 16 KB
 constexpr int kStageB = kMaxN * kTileK * 2;           // 32 KB
@@ -139,7 +141,7 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         }
         ptx::fence_barrier_init();
     }
-    if (warp == 9) {
+    if (warp == kEpilogueWarps + kDequantWarps + 1) {
         tc5::tmem_alloc(tmem_slot, kTmemCols);
         tc5::tmem_relinquish();
     }
@@ -154,7 +156,7 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     const int n_tiles = *p.n_tiles;
     const int total_items = n_tiles * row_blocks;
 
-    if (warp == 8) {
+    if (warp == kEpilogueWarps + kDequantWarps) {
         // ------------------------------ TMA: activation operand ------------------------------
         if (lane == 0) {
             uint32_t n = 0;
@@ -172,7 +174,7 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == kEpilogueWarps + kDequantWarps + 1) {
         // ------------------------------ MMA issue ---------------------------------------------
         if (lane == 0) {
             uint32_t n = 0, it = 0;
@@ -205,9 +207,13 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         }
     } else if (warp >= kEpilogueWarps) {
         // ------------------------------ dequantise the weight operand ------------------------
-        const int r = tid - kEpilogueWarps * 32;          // tile row owned by this thread, 0..127
-        const uint64_t stream_policy = ptx::policy_evict_first();
-        (void)stream_policy;
+        // Two threads per tile row: thread (r, half) converts atom `half` (32 columns) of the
+        // k-block. Packed words and scales are loaded kPrefetch k-blocks ahead, so the global
+        // latency is off the critical path of the ring.
+        const int d = tid - kEpilogueWarps * 32;
+        const int r = d >> 1;                             // tile row, 0..127
+        const int half = d & 1;
+        const uint32_t row_smem = (r >> 3) * 1024 + (r & 7) * 128;
         uint32_t n = 0;
         for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
             const int ti = item / row_blocks;
@@ -231,36 +237,48 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             const uint8_t* packed = payload + gm->packed_offset + static_cast<size_t>(blk) * gm->block_bytes +
                                     rib * lpr * 16;
             const uint8_t* scales = payload + gm->scale_offset + static_cast<size_t>(blk) * gm->block_scale_bytes;
-            const int apg = G / 32;                        // atoms per scale group
+            constexpr int apg = G / 32;                    // atoms per scale group
             const int scales_per_iter_row = lpr / apg;     // scales of one row in one iteration
-            const int scale_row_stride = 32 / apg * 2;     // bytes of scales per iteration
-            const uint32_t row_smem = (r >> 3) * 1024 + (r & 7) * 128;
-            for (int kb = 0; kb < kblocks; ++kb, ++n) {
-                const int s = n % kStages;
-                const uint32_t parity = (n / kStages) & 1;
-                // the two atoms (64 columns) of this k-block
-                const int atom0 = kb * 2;
-                const int itn = atom0 / lpr, sl = atom0 - itn * lpr;
-                const uint8_t* src = packed + static_cast<size_t>(itn) * 512 + sl * 16;
-                const uint4 q0 = ldg128(src);
-                const uint4 q1 = ldg128(src + 16);
-                const uint8_t* sc = scales + itn * scale_row_stride + (rib * scales_per_iter_row) * 2;
-                const uint16_t s0 = __ldg(reinterpret_cast<const uint16_t*>(sc) + sl / apg);
-                const uint16_t s1 = __ldg(reinterpret_cast<const uint16_t*>(sc) + (sl + 1) / apg);
-                const uint32_t s0x2 = static_cast<uint32_t>(s0) * 0x10001u;
-                const uint32_t s1x2 = static_cast<uint32_t>(s1) * 0x10001u;
-                if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
-                uint8_t* dst = smem_gen + (s * kStageA) + row_smem;
-                const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            const int scale_iter_bytes = 32 / apg * 2;     // bytes of scales per iteration
+            auto fetch = [&](int kb, uint4& q, uint32_t& s2) {
+                const int atom = kb * 2 + half;
+                const int itn = atom / lpr, sl = atom - itn * lpr;
+                q = ldg128(packed + static_cast<size_t>(itn) * 512 + sl * 16);
+                // raw load only: any arithmetic on the value here would wait for it
+                s2 = __ldg(reinterpret_cast<const uint16_t*>(
+                               scales + itn * scale_iter_bytes + rib * scales_per_iter_row * 2) +
+                           sl / apg);
+            };
+            uint4 qbuf[kPrefetch];
+            uint32_t sbuf[kPrefetch];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 v = dequant_word(words[c], c < 4 ? s0x2 : s1x2);
-                    *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = v;
+            for (int i = 0; i < kPrefetch; ++i)
+                if (i < kblocks) fetch(i, qbuf[i], sbuf[i]);
+            for (int kb0 = 0; kb0 < kblocks; kb0 += kPrefetch) {
+#pragma unroll
+                for (int i = 0; i < kPrefetch; ++i) {
+                    const int kb = kb0 + i;
+                    if (kb >= kblocks) break;
+                    const int s = n % kStages;
+                    const uint32_t parity = (n / kStages) & 1;
+                    ++n;
+                    const uint4 q = qbuf[i];
+                    const uint32_t s2 = sbuf[i] * 0x10001u;     // the scale in both halves
+                    if (kb + kPrefetch < kblocks) fetch(kb + kPrefetch, qbuf[i], sbuf[i]);
+                    if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error))
+                        flag_error(p.error, kErrWaitTimeout);
+                    uint8_t* dst = smem_gen + (s * kStageA) + row_smem;
+                    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint4 v = dequant_word(words[c], s2);
+                        *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (r & 7)) << 4)) = v;
+                    }
+                    // generic-proxy writes must be visible to the tensor core (async proxy)
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(full_bar + 8 * s);
                 }
-                // generic-proxy writes must be visible to the tensor core (async proxy)
-                ptx::fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(full_bar + 8 * s);
             }
         }
     } else {
@@ -312,7 +330,7 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
 
     tc5::fence_before_sync();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kEpilogueWarps + kDequantWarps + 1) {
         tc5::fence_after_sync();
         tc5::tmem_dealloc(tmem_base, kTmemCols);
     }

@@ -25,6 +25,12 @@ __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async;" ::: "memory");
 }
 
+// Shared-memory-only form: orders this thread's shared-memory writes before later
+// async-proxy reads (tensor core, TMA) without waiting on its global loads in flight.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
