@@ -230,50 +230,55 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
                 gm = &p.w2;
                 row = rb * kTileM + r;
             }
-            const int rpw = gm->rpw, lpr = gm->lpr;
-            const int blk = row / rpw, rib = row - blk * rpw;
-            // packed atoms of a row: iteration `itn` holds lpr consecutive atoms (32 columns
-            // each) at (blk * iters + itn) * 512 + rib * lpr * 16
-            const uint8_t* packed = payload + gm->packed_offset + static_cast<size_t>(blk) * gm->block_bytes +
-                                    rib * lpr * 16;
-            const uint8_t* scales = payload + gm->scale_offset + static_cast<size_t>(blk) * gm->block_scale_bytes;
+            // The swizzle configuration is fixed per matrix kind (validated with the config):
+            // W1/W3 rows come 4 to a 512-byte line with 8 atoms each, W2 rows 8 with 4 atoms.
+            constexpr int RPW = kGateUp ? 4 : 8, LPR = kGateUp ? 8 : 4;
             constexpr int apg = G / 32;                    // atoms per scale group
-            const int scales_per_iter_row = lpr / apg;     // scales of one row in one iteration
-            const int scale_iter_bytes = 32 / apg * 2;     // bytes of scales per iteration
-            auto fetch = [&](int kb, uint4& q, uint32_t& s2) {
-                const int atom = kb * 2 + half;
-                const int itn = atom / lpr, sl = atom - itn * lpr;
-                q = ldg128(packed + static_cast<size_t>(itn) * 512 + sl * 16);
+            constexpr int kScaleIterBytes = 32 / apg * 2;  // scale bytes per 512-byte line
+            const int blk = row / RPW, rib = row - blk * RPW;
+            // atom a of the row (32 columns each): line a / LPR, position rib * LPR + a % LPR
+            const uint8_t* packed = payload + gm->packed_offset + static_cast<size_t>(blk) * gm->block_bytes +
+                                    (rib * LPR + half) * 16;
+            const uint16_t* scales = reinterpret_cast<const uint16_t*>(
+                payload + gm->scale_offset + static_cast<size_t>(blk) * gm->block_scale_bytes +
+                rib * (LPR / apg) * 2);
+            // k-block kb0 + i uses atom 2*(kb0+i) + half; with kb0 a multiple of 4 every offset
+            // below is a compile-time constant plus a base that moves 8 atoms per round
+            auto fetch = [&](int kb0, int i, uint4& q, uint32_t& s2) {
+                const int line0 = (kb0 * 2) / LPR;                 // first line of this round
+                constexpr int kLinesPerRound = 8 / LPR;            // 1 (W1/W3) or 2 (W2)
+                (void)kLinesPerRound;
+                const int a = i * 2;                               // atom within the round (even part)
+                const int line = line0 + a / LPR;
+                const int sl = a % LPR;                            // + half, folded into `packed`
+                q = ldg128(packed + static_cast<size_t>(line) * 512 + sl * 16);
                 // raw load only: any arithmetic on the value here would wait for it
-                s2 = __ldg(reinterpret_cast<const uint16_t*>(
-                               scales + itn * scale_iter_bytes + rib * scales_per_iter_row * 2) +
-                           sl / apg);
+                s2 = __ldg(scales + line * (kScaleIterBytes / 2) + (sl + half) / apg);
             };
             uint4 qbuf[kPrefetch];
             uint32_t sbuf[kPrefetch];
 #pragma unroll
-            for (int i = 0; i < kPrefetch; ++i)
-                if (i < kblocks) fetch(i, qbuf[i], sbuf[i]);
+            for (int i = 0; i < kPrefetch; ++i) fetch(0, i, qbuf[i], sbuf[i]);
+            uint32_t dst_off[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dst_off[c] = row_smem + (((half * 4 + c) ^ (r & 7)) << 4);
             for (int kb0 = 0; kb0 < kblocks; kb0 += kPrefetch) {
+                const bool more = kb0 + kPrefetch < kblocks;
 #pragma unroll
                 for (int i = 0; i < kPrefetch; ++i) {
-                    const int kb = kb0 + i;
-                    if (kb >= kblocks) break;
                     const int s = n % kStages;
                     const uint32_t parity = (n / kStages) & 1;
                     ++n;
                     const uint4 q = qbuf[i];
                     const uint32_t s2 = sbuf[i] * 0x10001u;     // the scale in both halves
-                    if (kb + kPrefetch < kblocks) fetch(kb + kPrefetch, qbuf[i], sbuf[i]);
+                    if (more) fetch(kb0 + kPrefetch, i, qbuf[i], sbuf[i]);
                     if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error))
                         flag_error(p.error, kErrWaitTimeout);
-                    uint8_t* dst = smem_gen + (s * kStageA) + row_smem;
+                    uint8_t* dst = smem_gen + s * kStageA;
                     const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint4 v = dequant_word(words[c], s2);
-                        *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (r & 7)) << 4)) = v;
-                    }
+                    for (int c = 0; c < 4; ++c)
+                        *reinterpret_cast<uint4*>(dst + dst_off[c]) = dequant_word(words[c], s2);
                     // generic-proxy writes must be visible to the tensor core (async proxy)
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
@@ -532,8 +537,8 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
     require(tokens > 0 && tokens <= 65536, "aeon_b200_moe_prefill: tokens must be in [1, 65536]");
     require(x_stride >= cfg.hidden && x_stride % 8 == 0 && accum_stride >= cfg.hidden && accum_stride % 4 == 0,
             "aeon_b200_moe_prefill: bad row stride");
-    require(cfg.hidden % kTileM == 0 && (2 * cfg.intermediate) % kTileM == 0,
-            "aeon_b200_moe_prefill: hidden and 2*intermediate must be multiples of 128");
+    require(cfg.hidden % (kTileK * kPrefetch) == 0 && cfg.intermediate % (kTileK * kPrefetch) == 0,
+            "aeon_b200_moe_prefill: hidden and intermediate must be multiples of 256");
     PrefillScratch* s = ensure_scratch(ctx, tokens);
     const bool skip = (flags & AEON_B200_DECODE_SKIP_ABSENT) != 0;
 
