@@ -1,0 +1,838 @@
+// C++ host layer over the C ABI (include/aeon_b200.h), keeping the reference's class and
+// function names for the routed-expert path so engine code compiles against it with
+// hipStream_t -> cudaStream_t as the only type change. Header-only; link libaeon_b200.so.
+//
+//   ParallelTopologyConfig / LayerRange / parse_device_ids / ParallelTopology
+//                               src/infrastructure/parallel/parallel_topology.hpp:34-211
+//   ExpertShardDescriptor       the shard-aware fields the reference only plans
+//                               (plans-and-docs/.../MULTI_GPU_EXECUTION_PLAN.md:151-181) and its
+//                               shard-equivalence tests exercise
+//                               (tests/test_expert_shard_equivalence.cpp:286-340)
+//   ExpertFormatDescriptor      src/infrastructure/expert/storage/expert_format.hpp:10-60
+//   UnifiedVRAMExpertPool       src/backend/swizzled_w4a16/core/vram_expert_pool.hpp:22-82 over
+//                               src/infrastructure/expert/storage/expert_payload_pool.hpp:16-131
+//   ExpertRegistry              src/infrastructure/expert/residency/expert_registry.hpp:26-1064
+//                               (the HBM-resident subset: hot hits, cold misses into free or
+//                               least-recently-used unleased slots, leases, invariant audit)
+//   AeonExpertContainer         the expert half of AeonModelLoader,
+//                               src/infrastructure/artifact/aeon_loader.hpp:145-166,318-441
+//   V4RoutedExpertExecutor      src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:32-112
+//   V4TieredExpertExecutor      src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:178-634
+//   dispatch_router             src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:124-159
+//   dispatch_expert_permutation src/platform/ops/expert_permutation.hpp:130-175
+#pragma once
+
+#include "aeon_b200.h"
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <list>
+#include <stdexcept>
+#include <string>
+#include <string_view>
+#include <unordered_map>
+#include <vector>
+
+namespace aeon::core {
+
+// ---------------------------------------------------------------------------------------------
+// Status -> the exception kinds the reference throws (shape/argument: invalid_argument;
+// protocol: logic_error; ids: out_of_range; device: runtime_error, as CHECK_HIP does,
+// src/infrastructure/hip_check.hpp:20-27).
+// ---------------------------------------------------------------------------------------------
+inline void check_status(int status) {
+    if (status == AEON_B200_OK) return;
+    const std::string what = aeon_b200_last_error();
+    switch (status) {
+        case AEON_B200_ERR_INVALID_ARGUMENT: throw std::invalid_argument(what);
+        case AEON_B200_ERR_LOGIC: throw std::logic_error(what);
+        case AEON_B200_ERR_OUT_OF_RANGE: throw std::out_of_range(what);
+        default: throw std::runtime_error(what);
+    }
+}
+
+inline aeon_b200_moe_config moe_config_preset(const char* name) {
+    aeon_b200_moe_config cfg{};
+    check_status(aeon_b200_config_preset(name, &cfg));
+    return cfg;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Parallel topology (pure host).
+// ---------------------------------------------------------------------------------------------
+struct ParallelTopologyConfig {
+    std::vector<int> device_ids;       // stage-major; empty = 0 .. tp*pp-1
+    uint32_t tensor_parallel{1};
+    uint32_t pipeline_parallel{1};
+    uint32_t expert_parallel{1};       // new: ranks the routed experts are split over
+};
+
+struct LayerRange {
+    uint32_t first{0};
+    uint32_t count{0};
+    uint32_t end() const noexcept { return first + count; }
+    bool contains(uint32_t layer) const noexcept { return layer >= first && layer < end(); }
+};
+
+// "0,1,3" -> {0,1,3}. Empty text = empty list (use the default). Blanks around an entry are
+// ignored; an empty or non-numeric or negative entry is refused, naming the offending text.
+inline std::vector<int> parse_device_ids(std::string_view text) {
+    std::vector<int> ids;
+    if (text.empty()) return ids;
+    size_t start = 0;
+    for (;;) {
+        size_t comma = text.find(',', start);
+        if (comma == std::string_view::npos) comma = text.size();
+        std::string_view entry = text.substr(start, comma - start);
+        while (!entry.empty() && (entry.front() == ' ' || entry.front() == '\t')) entry.remove_prefix(1);
+        while (!entry.empty() && (entry.back() == ' ' || entry.back() == '\t')) entry.remove_suffix(1);
+        if (entry.empty())
+            throw std::invalid_argument("device id list has an empty entry: \"" + std::string(text) + "\"");
+        if (entry.front() == '-' && entry.size() > 1 &&
+            std::all_of(entry.begin() + 1, entry.end(), [](char c) { return c >= '0' && c <= '9'; }))
+            throw std::invalid_argument("device id must be non-negative: \"" + std::string(entry) + "\"");
+        long value = 0;
+        for (char ch : entry) {
+            if (ch < '0' || ch > '9')
+                throw std::invalid_argument("invalid device id: \"" + std::string(entry) + "\"");
+            value = value * 10 + (ch - '0');
+            if (value > (1 << 20))
+                throw std::invalid_argument("invalid device id: \"" + std::string(entry) + "\"");
+        }
+        ids.push_back(static_cast<int>(value));
+        if (comma == text.size()) break;
+        start = comma + 1;
+    }
+    return ids;
+}
+
+// Which experts / which slice of the intermediate dimension one rank owns.
+struct ExpertShardDescriptor {
+    uint32_t rank{0};
+    uint32_t shard_count{1};
+    uint32_t first_expert{0}, expert_count{0};          // expert parallel: contiguous block
+    uint32_t first_intermediate{0}, intermediate_count{0};  // W2-intermediate tensor parallel
+    bool owns_expert(uint32_t e) const noexcept { return e >= first_expert && e < first_expert + expert_count; }
+};
+
+class ParallelTopology {
+public:
+    static ParallelTopology resolve(const ParallelTopologyConfig& config, int visible_devices,
+                                    uint32_t artifact_max_tp, uint32_t num_layers) {
+        const uint32_t tp = config.tensor_parallel, pp = config.pipeline_parallel;
+        const uint32_t ep = config.expert_parallel;
+        if (tp == 0 || pp == 0 || ep == 0)
+            throw std::invalid_argument(
+                "parallel topology: tensor, pipeline and expert degrees must be at least 1 (tensor_parallel=" +
+                std::to_string(tp) + ", pipeline_parallel=" + std::to_string(pp) +
+                ", expert_parallel=" + std::to_string(ep) + ")");
+        if (num_layers == 0) throw std::invalid_argument("parallel topology: the model has no layers");
+        if (artifact_max_tp == 0)
+            throw std::invalid_argument("parallel topology: the artifact's max tensor-parallel degree is 0");
+        if (artifact_max_tp % tp != 0)
+            throw std::invalid_argument("parallel topology: tensor_parallel=" + std::to_string(tp) +
+                                        " does not divide the artifact's max tensor-parallel degree " +
+                                        std::to_string(artifact_max_tp));
+        if (pp > num_layers)
+            throw std::invalid_argument("parallel topology: pipeline_parallel=" + std::to_string(pp) +
+                                        " exceeds the " + std::to_string(num_layers) + " model layers");
+        if (ep > 1 && tp > 1)
+            throw std::invalid_argument(
+                "parallel topology: expert_parallel and tensor_parallel share the ranks of a stage; "
+                "set one of them to 1");
+        const size_t per_stage = static_cast<size_t>(tp) * ep;
+        const size_t rank_count = per_stage * pp;
+        std::vector<int> ids = config.device_ids;
+        if (ids.empty())
+            for (size_t i = 0; i < rank_count; ++i) ids.push_back(static_cast<int>(i));
+        if (ids.size() != rank_count)
+            throw std::invalid_argument("parallel topology: device_ids has " + std::to_string(ids.size()) +
+                                        " entries but tp * ep * pp = " + std::to_string(rank_count));
+        for (size_t i = 0; i < ids.size(); ++i) {
+            if (ids[i] < 0 || ids[i] >= visible_devices)
+                throw std::invalid_argument("parallel topology: device id " + std::to_string(ids[i]) +
+                                            " is out of range for " + std::to_string(visible_devices) +
+                                            " visible devices");
+            for (size_t j = 0; j < i; ++j)
+                if (ids[i] == ids[j])
+                    throw std::invalid_argument("parallel topology: device id " + std::to_string(ids[i]) +
+                                                " is listed more than once");
+        }
+        ParallelTopology topo;
+        topo.tp_ = tp;
+        topo.pp_ = pp;
+        topo.ep_ = ep;
+        topo.device_ids_ = std::move(ids);
+        // contiguous ranges, remainder to the earliest stages
+        const uint32_t base = num_layers / pp, remainder = num_layers % pp;
+        uint32_t first = 0;
+        for (uint32_t stage = 0; stage < pp; ++stage) {
+            const uint32_t count = base + (stage < remainder ? 1u : 0u);
+            topo.stages_.push_back(LayerRange{first, count});
+            first += count;
+        }
+        return topo;
+    }
+
+    uint32_t tp() const noexcept { return tp_; }
+    uint32_t pp() const noexcept { return pp_; }
+    uint32_t ep() const noexcept { return ep_; }
+    uint32_t ranks_per_stage() const noexcept { return tp_ * ep_; }
+    // stage-major: device_ids[stage * ranks_per_stage + rank]
+    int device(uint32_t stage, uint32_t rank) const noexcept {
+        return device_ids_[static_cast<size_t>(stage) * ranks_per_stage() + rank];
+    }
+    LayerRange stage_layers(uint32_t stage) const noexcept { return stages_[stage]; }
+    uint32_t stage_of(uint32_t layer) const noexcept {
+        uint32_t stage = 0;
+        while (stage + 1 < stages_.size() && stages_[stage].end() <= layer) ++stage;
+        return stage;
+    }
+    bool is_single_device() const noexcept { return tp_ == 1 && pp_ == 1 && ep_ == 1; }
+    const std::vector<int>& device_ids() const noexcept { return device_ids_; }
+
+    // The slice of a layer's routed experts that rank `rank` of a stage holds: a contiguous
+    // block of experts under expert parallelism, a contiguous block of the intermediate
+    // dimension (W1/W3 rows, W2 columns) under tensor parallelism.
+    ExpertShardDescriptor rank_slice(uint32_t rank, uint32_t experts, uint32_t intermediate) const {
+        if (rank >= ranks_per_stage()) throw std::out_of_range("parallel topology: rank out of range");
+        if (experts % ep_ != 0)
+            throw std::invalid_argument("parallel topology: expert_parallel=" + std::to_string(ep_) +
+                                        " does not divide the " + std::to_string(experts) + " experts");
+        if (intermediate % (tp_ * 128) != 0)
+            throw std::invalid_argument("parallel topology: every tensor-parallel shard of the intermediate "
+                                        "dimension must be a multiple of 128 columns");
+        ExpertShardDescriptor d;
+        d.rank = rank;
+        d.shard_count = ranks_per_stage();
+        const uint32_t er = ep_ > 1 ? rank : 0, tr = tp_ > 1 ? rank : 0;
+        d.expert_count = experts / ep_;
+        d.first_expert = er * d.expert_count;
+        d.intermediate_count = intermediate / tp_;
+        d.first_intermediate = tr * d.intermediate_count;
+        return d;
+    }
+
+private:
+    uint32_t tp_{1}, pp_{1}, ep_{1};
+    std::vector<int> device_ids_;
+    std::vector<LayerRange> stages_;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Expert payload format and pool.
+// ---------------------------------------------------------------------------------------------
+enum class ExpertFormatKind : uint32_t { OPAQUE = 0, SWIZZLED_W4A16 = 1 };
+
+struct ExpertFormatDescriptor {
+    ExpertFormatKind kind{ExpertFormatKind::SWIZZLED_W4A16};
+    uint32_t version{2};
+    uint32_t sector_size{4096};
+    uint32_t num_layers{0};
+    uint32_t experts_per_layer{0};
+    size_t payload_bytes{0};
+
+    uint64_t total_experts() const noexcept { return static_cast<uint64_t>(num_layers) * experts_per_layer; }
+    void validate_payload() const {
+        if (payload_bytes == 0 || sector_size == 0 || payload_bytes % sector_size != 0)
+            throw std::invalid_argument("ExpertFormatDescriptor: payload must be a positive multiple of the sector size");
+    }
+    void validate_catalog() const {
+        validate_payload();
+        if (num_layers == 0 || experts_per_layer == 0)
+            throw std::invalid_argument("ExpertFormatDescriptor: empty expert catalog");
+    }
+};
+
+inline ExpertFormatDescriptor make_swizzled_expert_format(const aeon_b200_moe_config& cfg, uint32_t layers) {
+    aeon_b200_expert_layout lay{};
+    check_status(aeon_b200_expert_layout_of(&cfg, &lay));
+    return ExpertFormatDescriptor{ExpertFormatKind::SWIZZLED_W4A16, 2, 4096, layers,
+                                  static_cast<uint32_t>(cfg.experts), static_cast<size_t>(lay.payload_bytes)};
+}
+
+// One device slab of slots x payload_bytes; a slot is a byte-identical expert payload.
+class UnifiedVRAMExpertPool {
+public:
+    uint32_t num_slots{0};
+    uint8_t* d_experts{nullptr};
+
+    UnifiedVRAMExpertPool() = default;
+    UnifiedVRAMExpertPool(uint32_t slots, const aeon_b200_moe_config& cfg, ExpertFormatDescriptor format,
+                          int device = 0)
+        : cfg_(cfg), format_(format), device_(device) {
+        format_.validate_payload();
+        check_status(aeon_b200_expert_layout_of(&cfg_, &layout_));
+        if (format_.kind == ExpertFormatKind::SWIZZLED_W4A16 && format_.payload_bytes != layout_.payload_bytes)
+            throw std::invalid_argument("UnifiedVRAMExpertPool: payload size does not match the swizzled layout");
+        if (slots == 0) return;
+        void* base = nullptr;
+        check_status(aeon_b200_pool_create(format_.payload_bytes, slots, device, &base));
+        d_experts = static_cast<uint8_t*>(base);
+        num_slots = slots;
+    }
+    ~UnifiedVRAMExpertPool() { release(); }
+    UnifiedVRAMExpertPool(const UnifiedVRAMExpertPool&) = delete;
+    UnifiedVRAMExpertPool& operator=(const UnifiedVRAMExpertPool&) = delete;
+    UnifiedVRAMExpertPool(UnifiedVRAMExpertPool&& o) noexcept { take(std::move(o)); }
+    UnifiedVRAMExpertPool& operator=(UnifiedVRAMExpertPool&& o) noexcept {
+        if (this != &o) { release(); take(std::move(o)); }
+        return *this;
+    }
+
+    const ExpertFormatDescriptor& format() const noexcept { return format_; }
+    uint8_t* get_slot_base(uint32_t slot) const {
+        if (d_experts == nullptr || slot >= num_slots)
+            throw std::runtime_error("ExpertPayloadPool: Invalid slot index " + std::to_string(slot));
+        return d_experts + static_cast<size_t>(slot) * format_.payload_bytes;
+    }
+    void upload_from_host_expert(uint32_t slot, const uint8_t* host_payload, void* stream = nullptr) {
+        if (slot >= num_slots || host_payload == nullptr)
+            throw std::runtime_error("ExpertPayloadPool: Invalid upload source or slot index");
+        check_status(aeon_b200_pool_upload(d_experts, format_.payload_bytes, slot, host_payload, stream));
+    }
+    // Typed views; only a swizzled-format pool has them (the reference's format guard).
+    const uint32_t* get_w1_packed(uint32_t s) const { return view<uint32_t>(s, layout_.w1_packed_offset); }
+    const uint16_t* get_w1_scale(uint32_t s) const { return view<uint16_t>(s, layout_.w1_scale_offset); }
+    const uint32_t* get_w2_packed(uint32_t s) const { return view<uint32_t>(s, layout_.w2_packed_offset); }
+    const uint16_t* get_w2_scale(uint32_t s) const { return view<uint16_t>(s, layout_.w2_scale_offset); }
+    const uint32_t* get_w3_packed(uint32_t s) const { return view<uint32_t>(s, layout_.w3_packed_offset); }
+    const uint16_t* get_w3_scale(uint32_t s) const { return view<uint16_t>(s, layout_.w3_scale_offset); }
+
+private:
+    template <class T>
+    const T* view(uint32_t slot, uint64_t offset) const {
+        if (format_.kind != ExpertFormatKind::SWIZZLED_W4A16)
+            throw std::logic_error("UnifiedVRAMExpertPool: swizzled views requested from a pool of another format");
+        return reinterpret_cast<const T*>(get_slot_base(slot) + offset);
+    }
+    void release() noexcept {
+        if (d_experts) (void)aeon_b200_pool_destroy(d_experts, device_);
+        d_experts = nullptr;
+        num_slots = 0;
+    }
+    void take(UnifiedVRAMExpertPool&& o) noexcept {
+        num_slots = o.num_slots; d_experts = o.d_experts; cfg_ = o.cfg_; format_ = o.format_;
+        layout_ = o.layout_; device_ = o.device_;
+        o.d_experts = nullptr; o.num_slots = 0;
+    }
+    aeon_b200_moe_config cfg_{};
+    ExpertFormatDescriptor format_{};
+    aeon_b200_expert_layout layout_{};
+    int device_{0};
+};
+
+// ---------------------------------------------------------------------------------------------
+// Registry: which expert of which layer sits in which pool slot. Host integers only.
+// ---------------------------------------------------------------------------------------------
+enum class ExpertTier : uint8_t { HOT_VRAM = 0, WARM_HOST = 1, COLD_NVME = 2 };
+enum class ExpertRequestKind : uint8_t { HOT_HIT = 0, WARM_PROMOTION = 1, COLD_MISS = 2, PENDING = 3, COLD_STAGED = 4 };
+
+struct ExpertRequestReservation {
+    ExpertRequestKind kind{ExpertRequestKind::COLD_MISS};
+    ExpertTier source_tier{ExpertTier::COLD_NVME};
+    uint32_t global_expert_id{0};
+    uint64_t operation_id{0};
+    int32_t vram_slot{-1};
+    bool lease_acquired{false};
+    int32_t evicted_global_id{-1};     // the expert that lost the slot, if any
+};
+
+class ExpertRegistry {
+public:
+    uint32_t num_layers{0};
+    uint32_t experts_per_layer{0};
+    uint32_t vram_capacity{0};
+
+    ExpertRegistry() = default;
+    ExpertRegistry(uint32_t layers, uint32_t experts, uint32_t slots) { init(layers, experts, slots); }
+
+    void init(uint32_t layers, uint32_t experts, uint32_t slots) {
+        if (layers == 0 || experts == 0) throw std::invalid_argument("ExpertRegistry: empty catalog");
+        num_layers = layers;
+        experts_per_layer = experts;
+        vram_capacity = slots;
+        entries_.assign(static_cast<size_t>(layers) * experts, Entry{});
+        free_slots_.clear();
+        for (uint32_t s = slots; s > 0; --s) free_slots_.push_back(static_cast<int32_t>(s - 1));
+        lru_.clear();
+        pending_.clear();
+        next_operation_ = 1;
+        hot_hits = cold_misses = evictions = 0;
+    }
+
+    uint32_t get_global_id(uint32_t layer, uint32_t expert) const {
+        if (layer >= num_layers || expert >= experts_per_layer)
+            throw std::out_of_range("ExpertRegistry: layer or expert id out of range");
+        return layer * experts_per_layer + expert;
+    }
+
+    // Mark every expert resident in slot order (the full-residency start state).
+    void populate_all_hot() {
+        if (vram_capacity < entries_.size())
+            throw std::invalid_argument("ExpertRegistry: the pool is smaller than the catalog");
+        for (uint32_t gid = 0; gid < entries_.size(); ++gid) {
+            if (entries_[gid].slot >= 0) continue;
+            entries_[gid].slot = free_slots_.back();
+            free_slots_.pop_back();
+            entries_[gid].published = true;
+            lru_.push_front(gid);
+            entries_[gid].lru_it = lru_.begin();
+            entries_[gid].in_lru = true;
+        }
+    }
+
+    // A request for (layer, expert) with a lease. Resident: HOT_HIT. Otherwise a slot is taken
+    // from the free list, or from the least recently used resident expert that holds no lease
+    // and has no operation pending; the caller uploads the payload and calls complete_request.
+    ExpertRequestReservation reserve_request(uint32_t layer, uint32_t expert) {
+        const uint32_t gid = get_global_id(layer, expert);
+        Entry& e = entries_[gid];
+        ExpertRequestReservation r;
+        r.global_expert_id = gid;
+        if (e.slot >= 0 && e.published) {
+            ++hot_hits;
+            touch(gid);
+            ++e.lease_count;
+            r.kind = ExpertRequestKind::HOT_HIT;
+            r.source_tier = ExpertTier::HOT_VRAM;
+            r.vram_slot = e.slot;
+            r.lease_acquired = true;
+            return r;
+        }
+        if (e.slot >= 0 && !e.published) {      // an upload for it is already in flight
+            ++e.lease_count;
+            r.kind = ExpertRequestKind::PENDING;
+            r.vram_slot = e.slot;
+            r.operation_id = e.operation_id;
+            r.lease_acquired = true;
+            return r;
+        }
+        int32_t slot = -1;
+        if (!free_slots_.empty()) {
+            slot = free_slots_.back();
+            free_slots_.pop_back();
+        } else {
+            for (auto it = lru_.rbegin(); it != lru_.rend(); ++it) {
+                Entry& victim = entries_[*it];
+                if (victim.lease_count == 0 && victim.published) {
+                    slot = victim.slot;
+                    r.evicted_global_id = static_cast<int32_t>(*it);
+                    victim.slot = -1;
+                    victim.published = false;
+                    victim.in_lru = false;
+                    lru_.erase(victim.lru_it);
+                    ++evictions;
+                    break;
+                }
+            }
+        }
+        if (slot < 0) throw std::runtime_error("ExpertRegistry: no reclaimable Hot VRAM slot");
+        ++cold_misses;
+        e.slot = slot;
+        e.published = false;
+        e.operation_id = next_operation_++;
+        ++e.lease_count;
+        pending_[e.operation_id] = gid;
+        r.kind = ExpertRequestKind::COLD_MISS;
+        r.vram_slot = slot;
+        r.operation_id = e.operation_id;
+        r.lease_acquired = true;
+        return r;
+    }
+
+    void complete_request(uint64_t operation_id) {
+        auto it = pending_.find(operation_id);
+        if (it == pending_.end()) throw std::logic_error("ExpertRegistry: unknown operation id");
+        Entry& e = entries_[it->second];
+        e.published = true;
+        e.operation_id = 0;
+        lru_.push_front(it->second);
+        e.lru_it = lru_.begin();
+        e.in_lru = true;
+        pending_.erase(it);
+    }
+
+    // Roll a failed upload back: the slot returns to the free list, leases on it are dropped.
+    void fail_request(uint64_t operation_id) {
+        auto it = pending_.find(operation_id);
+        if (it == pending_.end()) throw std::logic_error("ExpertRegistry: unknown operation id");
+        Entry& e = entries_[it->second];
+        free_slots_.push_back(e.slot);
+        e = Entry{};
+        pending_.erase(it);
+    }
+
+    void release_lease(uint32_t gid) {
+        if (gid >= entries_.size()) throw std::out_of_range("ExpertRegistry: global id out of range");
+        if (entries_[gid].lease_count == 0) throw std::logic_error("ExpertRegistry: lease released twice");
+        --entries_[gid].lease_count;
+    }
+
+    bool expert_resident(uint32_t layer, uint32_t expert) const {
+        const Entry& e = entries_[get_global_id(layer, expert)];
+        return e.slot >= 0 && e.published;
+    }
+    int32_t slot_of(uint32_t layer, uint32_t expert) const {
+        const Entry& e = entries_[get_global_id(layer, expert)];
+        return (e.slot >= 0 && e.published) ? e.slot : -1;
+    }
+    uint32_t lease_count(uint32_t gid) const { return entries_.at(gid).lease_count; }
+    size_t free_vram_slot_count() const noexcept { return free_slots_.size(); }
+    uint64_t pending_transfer_count() const noexcept { return pending_.size(); }
+
+    // slot table of one layer as the kernels want it: expert -> slot, -1 when absent
+    std::vector<int32_t> layer_slot_table(uint32_t layer) const {
+        std::vector<int32_t> table(experts_per_layer, -1);
+        for (uint32_t e = 0; e < experts_per_layer; ++e) table[e] = slot_of(layer, e);
+        return table;
+    }
+
+    // Audit: every slot is owned at most once, free + owned = capacity, the LRU list holds
+    // exactly the published residents, pending operations point at unpublished owners.
+    bool invariants_hold() const noexcept {
+        std::vector<int> owner(vram_capacity, 0);
+        size_t owned = 0, published = 0;
+        for (const Entry& e : entries_) {
+            if (e.slot < 0) {
+                if (e.published || e.in_lru) return false;
+                continue;
+            }
+            if (static_cast<uint32_t>(e.slot) >= vram_capacity || owner[e.slot]++) return false;
+            ++owned;
+            if (e.published) ++published;
+            if (e.published != e.in_lru) return false;
+        }
+        for (int32_t s : free_slots_)
+            if (s < 0 || static_cast<uint32_t>(s) >= vram_capacity || owner[s]++) return false;
+        if (owned + free_slots_.size() != vram_capacity) return false;
+        if (lru_.size() != published) return false;
+        for (const auto& kv : pending_)
+            if (kv.second >= entries_.size() || entries_[kv.second].published) return false;
+        return true;
+    }
+
+    uint64_t hot_hits{0}, cold_misses{0}, evictions{0};
+
+private:
+    struct Entry {
+        int32_t slot{-1};
+        bool published{false};
+        bool in_lru{false};
+        uint32_t lease_count{0};
+        uint64_t operation_id{0};
+        std::list<uint32_t>::iterator lru_it{};
+    };
+    void touch(uint32_t gid) {
+        Entry& e = entries_[gid];
+        if (e.in_lru) lru_.erase(e.lru_it);
+        lru_.push_front(gid);
+        e.lru_it = lru_.begin();
+        e.in_lru = true;
+    }
+    std::vector<Entry> entries_;
+    std::vector<int32_t> free_slots_;
+    std::list<uint32_t> lru_;
+    std::unordered_map<uint64_t, uint32_t> pending_;
+    uint64_t next_operation_{1};
+};
+
+class ExpertLeaseHolder {
+public:
+    virtual ~ExpertLeaseHolder() = default;
+    virtual void release_leases() = 0;
+    virtual size_t outstanding_leases() const noexcept = 0;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Expert container: `.index` = magic "AEON_EXPERTS", u32 version, u32 layers, u32 experts per
+// layer, u64 expert bytes, then (u64 offset, u64 length) per expert; payloads in a second file.
+// ---------------------------------------------------------------------------------------------
+class AeonExpertContainer {
+public:
+    struct Location { uint64_t offset; uint64_t length; };
+
+    void open(const std::string& index_path, const std::string& experts_path, uint32_t expected_version,
+              size_t expected_payload_bytes) {
+        std::ifstream idx(index_path, std::ios::binary);
+        if (!idx) throw std::runtime_error("AeonModelLoader: Failed to open expert index: " + index_path);
+        std::vector<uint8_t> buf((std::istreambuf_iterator<char>(idx)), std::istreambuf_iterator<char>());
+        if (buf.size() < 32) throw std::runtime_error("AeonModelLoader: Expert index too small for header!");
+        if (std::memcmp(buf.data(), "AEON_EXPERTS", 12) != 0)
+            throw std::runtime_error("AeonModelLoader: Invalid expert index magic!");
+        uint32_t version, layers, experts;
+        uint64_t expert_bytes;
+        std::memcpy(&version, buf.data() + 12, 4);
+        std::memcpy(&layers, buf.data() + 16, 4);
+        std::memcpy(&experts, buf.data() + 20, 4);
+        std::memcpy(&expert_bytes, buf.data() + 24, 8);
+        if (version != expected_version)
+            throw std::runtime_error("AeonModelLoader: Unexpected expert index version " + std::to_string(version) +
+                                     ", expected " + std::to_string(expected_version));
+        if (expected_payload_bytes != 0 && expert_bytes != expected_payload_bytes)
+            throw std::runtime_error("AeonModelLoader: Expert payload size does not match the artifact specification");
+        format_ = ExpertFormatDescriptor{ExpertFormatKind::SWIZZLED_W4A16, version, 4096, layers, experts,
+                                         static_cast<size_t>(expert_bytes)};
+        format_.validate_catalog();
+        const uint64_t total = format_.total_experts();
+        if (buf.size() < 32 + total * 16) throw std::runtime_error("AeonModelLoader: Expert index has incomplete entries!");
+        locations_.resize(total);
+        for (uint64_t i = 0; i < total; ++i) {
+            uint64_t off, len;
+            std::memcpy(&off, buf.data() + 32 + i * 16, 8);
+            std::memcpy(&len, buf.data() + 32 + i * 16 + 8, 8);
+            if (len != expert_bytes || off % format_.sector_size != 0)
+                throw std::runtime_error("AeonModelLoader: Expert index contains an invalid payload entry");
+            locations_[i] = Location{off, len};
+        }
+        std::ifstream exp(experts_path, std::ios::binary | std::ios::ate);
+        if (!exp) throw std::runtime_error("AeonModelLoader: Failed to open experts file: " + experts_path);
+        const uint64_t size = static_cast<uint64_t>(exp.tellg());
+        for (const Location& l : locations_)
+            if (l.offset + l.length > size)
+                throw std::runtime_error("AeonModelLoader: Expert payload lies outside the experts file");
+        exp.seekg(0);
+        data_.resize(size);
+        exp.read(reinterpret_cast<char*>(data_.data()), static_cast<std::streamsize>(size));
+    }
+
+    const ExpertFormatDescriptor& format() const noexcept { return format_; }
+    Location get_expert_location(uint32_t layer, uint32_t expert) const { return locations_.at(index_of(layer, expert)); }
+    const uint8_t* get_expert_data(uint32_t layer, uint32_t expert) const {
+        return data_.data() + locations_.at(index_of(layer, expert)).offset;
+    }
+
+    // Writer used by tools and tests: payloads in (layer, expert) order, sector-aligned.
+    static void write(const std::string& index_path, const std::string& experts_path, uint32_t version,
+                      uint32_t layers, uint32_t experts, uint64_t expert_bytes,
+                      const std::vector<const uint8_t*>& payloads) {
+        if (payloads.size() != static_cast<size_t>(layers) * experts)
+            throw std::invalid_argument("AeonExpertContainer::write: payload count does not match the catalog");
+        std::ofstream idx(index_path, std::ios::binary), exp(experts_path, std::ios::binary);
+        if (!idx || !exp) throw std::runtime_error("AeonExpertContainer::write: cannot create the output files");
+        idx.write("AEON_EXPERTS", 12);
+        idx.write(reinterpret_cast<const char*>(&version), 4);
+        idx.write(reinterpret_cast<const char*>(&layers), 4);
+        idx.write(reinterpret_cast<const char*>(&experts), 4);
+        idx.write(reinterpret_cast<const char*>(&expert_bytes), 8);
+        uint64_t offset = 0;
+        for (const uint8_t* payload : payloads) {
+            idx.write(reinterpret_cast<const char*>(&offset), 8);
+            idx.write(reinterpret_cast<const char*>(&expert_bytes), 8);
+            exp.write(reinterpret_cast<const char*>(payload), static_cast<std::streamsize>(expert_bytes));
+            offset += expert_bytes;
+        }
+    }
+
+private:
+    size_t index_of(uint32_t layer, uint32_t expert) const {
+        if (layer >= format_.num_layers || expert >= format_.experts_per_layer)
+            throw std::out_of_range("AeonModelLoader: expert id out of range");
+        return static_cast<size_t>(layer) * format_.experts_per_layer + expert;
+    }
+    ExpertFormatDescriptor format_{};
+    std::vector<Location> locations_;
+    std::vector<uint8_t> data_;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Device dispatch helpers with the reference's names.
+// ---------------------------------------------------------------------------------------------
+inline void dispatch_router(aeon_b200_ctx* ctx, const void* activation, int activation_stride, const void* gate_weight,
+                            const float* gate_bias, const int64_t* tid2eid, const int32_t* device_token_ids,
+                            float* topk_weights, int32_t* topk_indices, int count, void* stream) {
+    check_status(aeon_b200_router_topk(ctx, activation, activation_stride, gate_weight, gate_bias, tid2eid,
+                                       device_token_ids, count, topk_weights, topk_indices, nullptr, stream));
+}
+
+inline void dispatch_expert_permutation(aeon_b200_ctx* ctx, const int* topk_indices, int token_count, int slots,
+                                        int expert_count, int* expert_offsets, int* token_indices,
+                                        int* draw_indices, const float* weights, float* weights_by_position,
+                                        void* stream) {
+    check_status(aeon_b200_expert_permutation(ctx, topk_indices, token_count, slots, expert_count, expert_offsets,
+                                              token_indices, draw_indices, weights, weights_by_position, stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// The executor seam and its B200 implementation.
+// ---------------------------------------------------------------------------------------------
+class V4RoutedExpertExecutor {
+public:
+    virtual ~V4RoutedExpertExecutor() = default;
+    virtual void on_routing_ready(uint32_t, uint32_t, const std::vector<int32_t>&, const std::vector<float>&) {}
+    virtual void on_routing_ready_batch(uint32_t layer_id, uint32_t first_position,
+                                        const std::vector<std::vector<int32_t>>& ids,
+                                        const std::vector<std::vector<float>>& weights) {
+        for (size_t i = 0; i < ids.size(); ++i)
+            on_routing_ready(layer_id, first_position + static_cast<uint32_t>(i), ids[i], weights[i]);
+    }
+    // moe_accum (fp32 here, fp16 in the reference) holds the shared expert's output on entry.
+    virtual void accumulate_routed(uint32_t layer_id, uint32_t position, const void* expert_input,
+                                   const int* expert_ids, const float* expert_weights, float* moe_accum) = 0;
+    virtual void accumulate_routed_batch(uint32_t layer_id, uint32_t first_position, uint32_t token_count,
+                                         const void* batch_input, int input_stride, const int* batch_ids,
+                                         int ids_stride, const float* batch_weights, int weights_stride,
+                                         float* batch_output, int output_stride) = 0;
+    virtual void on_routed_consumed(uint32_t, uint32_t) {}
+};
+
+// Borrows pool, registry and (optionally) the expert container; owns its context and the
+// device copy of the layer's slot table. Misses are served by uploading the payload from the
+// container into the slot the registry hands out (HBM-first: with every expert resident each
+// request is a hot hit and nothing is copied). Decode-sized chunks go to the streaming
+// kernels, larger ones to the grouped tcgen05 path.
+class V4TieredExpertExecutor final : public V4RoutedExpertExecutor, public ExpertLeaseHolder {
+public:
+    static constexpr uint32_t kDecodeChunk = 128;
+
+    V4TieredExpertExecutor(const aeon_b200_moe_config& cfg, int device, uint32_t max_chunk,
+                           UnifiedVRAMExpertPool& pool, ExpertRegistry& registry,
+                           const AeonExpertContainer* container, void* compute_stream, uint32_t first_layer = 0)
+        : cfg_(cfg), pool_(pool), registry_(registry), container_(container), stream_(compute_stream),
+          first_layer_(first_layer) {
+        if (registry_.vram_capacity == 0)
+            throw std::invalid_argument("V4TieredExpertExecutor: the VRAM expert pool has no slots");
+        if (registry_.experts_per_layer != static_cast<uint32_t>(cfg.experts))
+            throw std::invalid_argument("V4TieredExpertExecutor: registry and config disagree on the expert count");
+        check_status(aeon_b200_ctx_create(&cfg_, device, static_cast<int>(std::min(max_chunk, kDecodeChunk)), &ctx_));
+        device_ = device;
+        check_status(aeon_b200_pool_create(4096, 1, device, &d_slot_table_raw_));   // >= experts * 4 bytes
+        if (static_cast<size_t>(cfg.experts) * sizeof(int32_t) > 4096)
+            throw std::invalid_argument("V4TieredExpertExecutor: more than 1024 experts per layer");
+    }
+    ~V4TieredExpertExecutor() override {
+        if (ctx_) (void)aeon_b200_ctx_destroy(ctx_);
+        if (d_slot_table_raw_) (void)aeon_b200_pool_destroy(d_slot_table_raw_, device_);
+    }
+
+    void on_routing_ready(uint32_t layer_id, uint32_t position, const std::vector<int32_t>& ids,
+                          const std::vector<float>& weights) override {
+        (void)weights;
+        if (ids.size() != static_cast<size_t>(cfg_.top_k))
+            throw std::invalid_argument("V4TieredExpertExecutor: expected " + std::to_string(cfg_.top_k) +
+                                        " routed experts, got " + std::to_string(ids.size()));
+        begin_dispatch(layer_id, position, 1);
+        for (int32_t id : ids) request(layer_id, id);
+        publish_slot_table(layer_id);
+        batch_draws_ += ids.size();
+    }
+
+    void on_routing_ready_batch(uint32_t layer_id, uint32_t first_position,
+                                const std::vector<std::vector<int32_t>>& ids,
+                                const std::vector<std::vector<float>>& weights) override {
+        (void)weights;
+        if (ids.empty())
+            throw std::invalid_argument("V4TieredExpertExecutor: a layer-wide dispatch needs at least one token");
+        begin_dispatch(layer_id, first_position, static_cast<uint32_t>(ids.size()));
+        std::vector<uint8_t> seen(registry_.experts_per_layer, 0);
+        for (const auto& row : ids)
+            for (int32_t id : row) {
+                if (id < 0 || static_cast<uint32_t>(id) >= registry_.experts_per_layer)
+                    throw std::out_of_range("V4TieredExpertExecutor: routed expert id out of range");
+                if (!seen[id]) { seen[id] = 1; request(layer_id, id); }   // the layer's union, once
+                ++batch_draws_;
+            }
+        publish_slot_table(layer_id);
+    }
+
+    void accumulate_routed(uint32_t layer_id, uint32_t position, const void* expert_input, const int* expert_ids,
+                           const float* expert_weights, float* moe_accum) override {
+        if (!dispatched_ || current_layer_ != layer_id)
+            throw std::logic_error("V4TieredExpertExecutor: accumulate_routed without a matching on_routing_ready");
+        if (position < first_position_ || position - first_position_ >= token_count_)
+            throw std::out_of_range("V4TieredExpertExecutor: token index past the batch's token count");
+        check_status(aeon_b200_moe_decode(ctx_, pool_.d_experts, slot_table(), expert_input, cfg_.hidden, expert_ids,
+                                          expert_weights, 1, moe_accum, cfg_.hidden, 0, stream_));
+    }
+
+    void accumulate_routed_batch(uint32_t layer_id, uint32_t first_position, uint32_t token_count,
+                                 const void* batch_input, int input_stride, const int* batch_ids, int ids_stride,
+                                 const float* batch_weights, int weights_stride, float* batch_output,
+                                 int output_stride) override {
+        if (token_count == 0) return;
+        if (!dispatched_ || current_layer_ != layer_id || first_position != first_position_ ||
+            token_count != token_count_)
+            throw std::logic_error("V4TieredExpertExecutor: accumulate_routed_batch without a matching batch dispatch");
+        if (batch_ids == nullptr || ids_stride != cfg_.top_k || weights_stride != cfg_.top_k)
+            throw std::invalid_argument("V4TieredExpertExecutor: batch ids and weights must be [token, top_k]");
+        if (token_count <= kDecodeChunk) {
+            check_status(aeon_b200_moe_decode(ctx_, pool_.d_experts, slot_table(), batch_input, input_stride,
+                                              batch_ids, batch_weights, static_cast<int>(token_count), batch_output,
+                                              output_stride, 0, stream_));
+        } else {
+            check_status(aeon_b200_moe_prefill(ctx_, pool_.d_experts, slot_table(), batch_input, input_stride,
+                                               batch_ids, batch_weights, static_cast<int>(token_count), batch_output,
+                                               output_stride, 0, stream_));
+        }
+    }
+
+    void release_leases() override {
+        for (uint32_t gid : leases_) registry_.release_lease(gid);
+        leases_.clear();
+    }
+    size_t outstanding_leases() const noexcept override { return leases_.size(); }
+    uint64_t batch_draws() const noexcept { return batch_draws_; }
+    uint64_t batch_distinct() const noexcept { return batch_distinct_; }
+    uint32_t last_dispatch_tokens() const noexcept { return token_count_; }
+    aeon_b200_ctx* context() const noexcept { return ctx_; }
+    void check_device() { check_status(aeon_b200_ctx_check(ctx_, stream_)); }
+
+private:
+    void begin_dispatch(uint32_t layer_id, uint32_t first_position, uint32_t tokens) {
+        if (layer_id < first_layer_ || layer_id - first_layer_ >= registry_.num_layers)
+            throw std::out_of_range("V4TieredExpertExecutor: layer outside this stage");
+        current_layer_ = layer_id;
+        first_position_ = first_position;
+        token_count_ = tokens;
+        dispatched_ = true;
+    }
+    void request(uint32_t layer_id, int32_t expert) {
+        if (expert < 0 || static_cast<uint32_t>(expert) >= registry_.experts_per_layer)
+            throw std::out_of_range("V4TieredExpertExecutor: routed expert id out of range");
+        const uint32_t local = layer_id - first_layer_;
+        ExpertRequestReservation r = registry_.reserve_request(local, static_cast<uint32_t>(expert));
+        leases_.push_back(r.global_expert_id);
+        ++batch_distinct_;
+        if (r.kind == ExpertRequestKind::COLD_MISS) {
+            if (container_ == nullptr) {
+                registry_.fail_request(r.operation_id);
+                leases_.pop_back();
+                throw std::logic_error("V4TieredExpertExecutor: a routed expert is not resident and no container was given");
+            }
+            pool_.upload_from_host_expert(static_cast<uint32_t>(r.vram_slot),
+                                          container_->get_expert_data(local, static_cast<uint32_t>(expert)), stream_);
+            registry_.complete_request(r.operation_id);
+        }
+    }
+    void publish_slot_table(uint32_t layer_id) {
+        host_table_ = registry_.layer_slot_table(layer_id - first_layer_);
+        // stream-ordered copy: the kernels that follow on the same stream read the new table
+        check_status(aeon_b200_pool_upload(d_slot_table_raw_, 4096, 0, padded_table(), stream_));
+    }
+    const void* padded_table() {
+        staging_.assign(1024, -1);
+        std::copy(host_table_.begin(), host_table_.end(), staging_.begin());
+        return staging_.data();
+    }
+    const int32_t* slot_table() const { return static_cast<const int32_t*>(d_slot_table_raw_); }
+
+    aeon_b200_moe_config cfg_;
+    UnifiedVRAMExpertPool& pool_;
+    ExpertRegistry& registry_;
+    const AeonExpertContainer* container_;
+    void* stream_;
+    uint32_t first_layer_;
+    aeon_b200_ctx* ctx_{nullptr};
+    void* d_slot_table_raw_{nullptr};
+    int device_{0};
+    std::vector<int32_t> host_table_, staging_;
+    std::vector<uint32_t> leases_;
+    uint32_t current_layer_{0}, first_position_{0}, token_count_{0};
+    bool dispatched_{false};
+    uint64_t batch_draws_{0}, batch_distinct_{0};
+};
+
+}  // namespace aeon::core
