@@ -55,6 +55,32 @@ def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv)
     return weights, ids
 
 
+def tp_layer_forward(ops, dist, world, x, out_local, partial):
+    """One MoE layer with the experts' intermediate dimension split over `world` ranks
+    (W1/W3 rows and W2 columns [r*I/world, (r+1)*I/world) on rank r, each shard swizzled as a
+    matrix of its own; the reference shows this split exact on one GPU in
+    tests/test_expert_shard_equivalence.cpp and tests/test_w2_shard_equivalence.cpp).
+
+    Every rank holds all tokens `x` and all experts' shards: the router runs replicated, the
+    rank computes its shard's contribution for every token into the fp32 `partial`
+    [tokens, H], a reduce-scatter (sum) over NCCL hands each rank the finished rows of its
+    tokens_local = tokens / world tokens, and the shared expert (replicated weights) of those
+    rows is added by their owner. `ops.routed` must run with the shard's configuration
+    (intermediate / world). The cross-rank sum order is the collective's, so results are
+    compared with a tolerance and required to be identical run to run at a fixed world size."""
+    tokens = x.shape[0]
+    tl = tokens // world
+    rank = dist.get_rank()
+    weights, ids = ops.router(x)
+    partial.zero_()
+    ops.routed(x, ids, weights, partial, skip_absent=False)
+    routed_local = out_local.new_empty(out_local.shape)
+    dist.reduce_scatter_tensor(routed_local, partial)
+    ops.shared(x[rank * tl:(rank + 1) * tl], out_local)
+    out_local += routed_local
+    return weights, ids
+
+
 class _DeviceOps:
     """The library's kernels behind the four calls ep_layer_forward needs."""
 

@@ -15,8 +15,11 @@ void set_last_error(const std::string& message) { g_last_error = message; }
 
 void validate_config(const aeon_b200_moe_config& c) {
     require(c.hidden > 0 && c.intermediate > 0, "config: hidden and intermediate must be positive");
-    require(c.hidden % 1024 == 0 && c.intermediate % 1024 == 0,
-            "config: hidden and intermediate must be multiples of 1024 (one pipeline stage)");
+    // 256 = four 64-column k-blocks of the grouped path; a tensor-parallel shard of the
+    // intermediate dimension (2048 / 8 = 256) is a legal "expert" of its own. The decode
+    // kernels additionally need one of their compiled (hidden, intermediate) instances.
+    require(c.hidden % 256 == 0 && c.intermediate % 256 == 0,
+            "config: hidden and intermediate must be multiples of 256");
     require(c.experts > 0 && c.experts <= 1024 && c.experts % 32 == 0,
             "config: experts must be a multiple of 32 in [32, 1024]");
     require(c.top_k > 0 && c.top_k <= 32 && c.top_k <= c.experts, "config: top_k must be in [1, 32]");

@@ -85,6 +85,51 @@ def worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
+class TinyShardMoe(TinyMoe):
+    """The same layer with only the intermediate slice [lo, hi) of every expert."""
+
+    def __init__(self, lo, hi):
+        super().__init__(range(E))
+        self.lo, self.hi = lo, hi
+
+    def routed(self, x, ids, weights, out, skip_absent):
+        lo, hi = self.lo, self.hi
+        for t in range(x.shape[0]):
+            for s in range(K):
+                e = int(ids[t, s])
+                h = torch.nn.functional.silu(self.w1[e, lo:hi] @ x[t]) * (self.w3[e, lo:hi] @ x[t])
+                out[t] += weights[t, s] * (self.w2[e][:, lo:hi] @ h)
+
+
+def tp_worker(rank, world, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(7), dtype=torch.float64)
+        tl = T // world
+        per = I // world
+        moe = TinyShardMoe(rank * per, (rank + 1) * per)
+        out_local = torch.empty(tl, H, dtype=torch.float64)
+        partial = torch.empty(T, H, dtype=torch.float64)
+        w, ids = stack.tp_layer_forward(moe, dist, world, x, out_local, partial)
+        want, want_ids = single_rank(x)
+        err = (out_local - want[rank * tl:(rank + 1) * tl]).abs().max().item()
+        results[rank] = (torch.equal(ids, want_ids), err)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_protocol_matches_single_rank(world):
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(tp_worker, args=(world, free_port(), results), nprocs=world, join=True)
+    for rank in range(world):
+        ok_ids, err = results[rank]
+        assert ok_ids and err < 1e-12, (rank, err)
+
+
 def free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
