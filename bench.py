@@ -42,7 +42,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/8/32/128 sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default="full", choices=["full", "small", "b1", "prefill_small"],
+    ap.add_argument("--case", default="full", choices=["full", "small", "b1", "prefill_small", "tp"],
                     help="small: one layer of 64 experts at batch 32 (1.45 GB of weights, larger "
                          "than L2), the case the ncu captures under profiles/ run; not a bench value")
     args = ap.parse_args()
@@ -242,6 +242,80 @@ def prefill_bench(model, cfg, peaks, tokens=4096, iters=5):
 
 
 # ----------------------------------------------------------------------------------------
+# W2-intermediate tensor parallel (benchmark configuration 4): 16384 tokens, uniform routing,
+# one layer; each rank holds intermediate / N of every expert, computes its partial output for
+# all tokens with the grouped tcgen05 GEMMs, and a reduce-scatter (fp32 sum over NCCL) hands
+# every rank the finished rows of its tokens. Shard weights are generated per rank (same
+# generator, rank-specific seed); the numerical equivalence of real shards is the job of
+# tests/test_gpu_tp_shards.py.
+# ----------------------------------------------------------------------------------------
+def tp_bench(args, cfg, dist, rank, world, local_rank, peaks):
+    import numpy as np
+    import torch
+    import aeon_b200
+    from aeon_b200 import synth
+    tokens = 16384
+    H, I, E, k = cfg.hidden, cfg.intermediate, cfg.experts, cfg.top_k
+    cfg_shard = cfg.copy(intermediate=I // world)
+    dev = f"cuda:{local_rank}"
+    table = torch.from_numpy(synth.half_normal_table(0.02, 1e-4, 4096, dtype=aeon_b200.F16)
+                             .view(np.int16).copy()).to(dev)
+    pool = aeon_b200.ExpertPool(cfg_shard, E, local_rank)
+    pool.fill_synthetic(0, E, SEED + 1000 * rank, 0, 0, table)
+    slot_of = torch.arange(E, dtype=torch.int32, device=dev)
+    x_bits = synth.normal_bits(np.random.default_rng([SEED, 0x7E50]), (tokens, H), 1.0, cfg.act_dtype)
+    x = torch.from_numpy(x_bits.view(np.int16)).view(torch.bfloat16).to(dev)
+    draws = torch.arange(tokens * k, dtype=torch.int64, device=dev)
+    ids = (draws % E).to(torch.int32).reshape(tokens, k).contiguous()          # uniform, round robin
+    weights = torch.full((tokens, k), 1.0 / k, dtype=torch.float32, device=dev)
+    ctx = aeon_b200.Context(cfg_shard, local_rank, 128)
+    partial = torch.empty(tokens, H, dtype=torch.float32, device=dev)
+    out_local = torch.empty(tokens // world, H, dtype=torch.float32, device=dev)
+
+    def step():
+        partial.zero_()
+        ctx.moe_prefill(pool.base, slot_of, x, ids, weights, partial)
+        if world > 1:
+            dist.reduce_scatter_tensor(out_local, partial)
+        else:
+            out_local.copy_(partial)
+
+    for _ in range(2):
+        step()
+    ctx.check()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    iters = max(3, min(args.steps, 10))
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        step()
+    end.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / iters
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    flops = tokens * k * 6.0 * H * I
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    return {
+        "metric": "moe_prefill_tp_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "data": "synthetic", "dtype": "int4 weights -> f16 MMA operands, f32 accumulate",
+        "config": {"workload": f"cfg4: {tokens} tokens x top-{k}, uniform routing, one layer, "
+                               f"intermediate {I} split {world}-way (W1/W3 rows, W2 columns), fp32 "
+                               "reduce-scatter of the partial outputs over NCCL; routed experts only"},
+        "routed_tflops_aggregate": flops / (ms * 1e-3) / 1e12,
+        "frac_of_measured_bf16_peak_per_gpu": flops / (ms * 1e-3) / 1e12 / world / peak,
+        "nvlink_bytes_per_rank": int(tokens * H * 4 * (world - 1) / world) if world > 1 else 0,
+    }
+
+
+# ----------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------
 def main():
@@ -269,6 +343,17 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     cfg = aeon_b200.preset("baseline")
+    if args.case == "tp":
+        peaks = {}
+        if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        line = tp_bench(args, cfg, dist, rank, world, local_rank, peaks)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     if args.case in ("small", "prefill_small"):
         cfg = cfg.copy(experts=64)
     model = stack.MoeStack(cfg, layers=args.layers, max_tokens=args.batch, seed=SEED,
