@@ -441,7 +441,7 @@ struct GeomB {
 };
 
 template <int G, int MW, int MT, int KW, int NCH, int P>
-__global__ void __launch_bounds__(MW * KW * 32, (MW * KW <= 8) ? 2 : 1)
+__global__ void __launch_bounds__(MW * KW * 32, 1)
 moe_w2_contrib_kernel(const DecodeParams p) {
     using S = GeomB<G, MW, MT, KW, NCH, P>;
     static_assert(MW <= 4, "barrier slots");
@@ -793,8 +793,9 @@ template <int G, int KWA, int NCHA>
 void launch_decode_kernels(aeon_b200_ctx* ctx, const DecodeParams& p, cudaStream_t stream) {
     using SA = GeomA<G, KWA, NCHA>;
     // intermediate = 2048: two workers of eight warps, two 16-row tiles per worker, two chunks
-    // per warp (64-row items). (Four K-warps x four chunks with two CTAs per SM was measured
-    // slower: the 128-register cap makes it spill.)
+    // per warp (64-row items). Measured alternatives, all slower on B200: four K-warps x four
+    // chunks with two CTAs per SM (spills under the 128-register cap, 2.0 TB/s), one worker of
+    // four tiles (2.8 TB/s), one worker with two items in flight (2.8 TB/s); this one 3.1 TB/s.
     using SB = GeomB<G, 2, 2, 8, 2, 1>;
     if (p.I != SB::kInter || p.H != SA::kHidden)
         throw StatusError(AEON_B200_ERR_UNSUPPORTED,
