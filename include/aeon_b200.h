@@ -183,11 +183,25 @@ int aeon_b200_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, 
  * then draws of absent experts contribute nothing, which is the expert-parallel case
  * where this GPU holds a slice of the experts and moe_accum is a partial sum). Each
  * distinct expert's weights are read once per call. tokens <= the context's max_tokens. */
-enum { AEON_B200_DECODE_SKIP_ABSENT = 1 };
+enum {
+    AEON_B200_DECODE_SKIP_ABSENT = 1,
+    /* Stop after the per-draw slices are written; the caller finishes with
+     * aeon_b200_moe_accumulate. Lets the shared expert (which produces moe_accum's initial
+     * value) run on another stream while the routed experts stream their weights. */
+    AEON_B200_DECODE_DEFER_ACCUMULATE = 2
+};
 int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                          const void* x, int64_t x_stride, const int32_t* topk_ids,
                          const float* topk_weights, int tokens, float* moe_accum,
                          int64_t accum_stride, uint32_t flags, void* stream);
+
+/* Second half of a deferred decode call: moe_accum[t,:] += the slot-order sum of the per-draw
+ * slices the last aeon_b200_moe_decode(..., AEON_B200_DECODE_DEFER_ACCUMULATE) of this context
+ * left in its scratch. Same ids / slot table / flags as that call. Replaces
+ * moe_accumulate_fixed_order_kernel (src/platform/ops/moe_accumulate.hpp:73-92). */
+int aeon_b200_moe_accumulate(aeon_b200_ctx* ctx, const int32_t* slot_of_expert, const int32_t* topk_ids,
+                             int tokens, float* moe_accum, int64_t accum_stride, uint32_t flags,
+                             void* stream);
 
 /* Prefill path: the same contract as aeon_b200_moe_decode (moe_accum[t,:] += routed sum in
  * slot order, fp32) for chunks of many tokens, computed as per-expert grouped GEMMs on the

@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libaeon_b200.so")
 F16, BF16 = 0, 1
 SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID = 0, 1
 DECODE_SKIP_ABSENT = 1
+DECODE_DEFER_ACCUMULATE = 2
 
 STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "LOGIC", 3: "CUDA", 4: "OUT_OF_RANGE",
                 5: "TIMEOUT", 6: "UNSUPPORTED"}
@@ -32,7 +33,7 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_router_topk", "aeon_b200_expert_permutation", "aeon_b200_shared_expert",
     "aeon_b200_moe_decode", "aeon_b200_ctx_last_stats", "aeon_b200_synth_fill_experts",
     "aeon_b200_synth_fill_dense16", "aeon_b200_ctx_set_timing", "aeon_b200_ctx_kernel_times",
-    "aeon_b200_ep_combine", "aeon_b200_router_topk_noalloc", "aeon_b200_moe_prefill",
+    "aeon_b200_ep_combine", "aeon_b200_router_topk_noalloc", "aeon_b200_moe_prefill", "aeon_b200_moe_accumulate",
 ]
 
 
@@ -110,6 +111,8 @@ def lib() -> ctypes.CDLL:
     L.aeon_b200_moe_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
                                        c_void_p, c_int, c_void_p, c_int64, c_uint32, c_void_p]
     L.aeon_b200_moe_prefill.argtypes = L.aeon_b200_moe_decode.argtypes
+    L.aeon_b200_moe_accumulate.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64,
+                                           c_uint32, c_void_p]
     L.aeon_b200_ep_combine.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]
     L.aeon_b200_synth_fill_experts.argtypes = [POINTER(MoeConfig), c_void_p, c_uint32, c_uint32,
                                                c_uint64, c_uint32, c_uint32, c_void_p, c_uint32,
@@ -278,11 +281,16 @@ class Context:
                                             moe_accum.stride(0), _stream()))
 
     def moe_decode(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum,
-                   skip_absent: bool = False):
+                   skip_absent: bool = False, defer_accumulate: bool = False):
+        flags = (DECODE_SKIP_ABSENT if skip_absent else 0) | (DECODE_DEFER_ACCUMULATE if defer_accumulate else 0)
         check(lib().aeon_b200_moe_decode(self._h, c_void_p(pool_base), _ptr(slot_of_expert), _ptr(x),
                                          x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
-                                         _ptr(moe_accum), moe_accum.stride(0),
-                                         DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
+                                         _ptr(moe_accum), moe_accum.stride(0), flags, _stream()))
+
+    def moe_accumulate(self, slot_of_expert, ids, moe_accum, skip_absent: bool = False):
+        check(lib().aeon_b200_moe_accumulate(self._h, _ptr(slot_of_expert), _ptr(ids), ids.shape[0],
+                                             _ptr(moe_accum), moe_accum.stride(0),
+                                             DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
 
 
 def _moe_prefill(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum,

@@ -152,6 +152,10 @@ class MoeStack:
             self.partial = torch.empty(max_tokens, H, dtype=torch.float32, device=dev)
             self.recv = torch.empty(world, max_tokens // world, H, dtype=torch.float32, device=dev)
         self._extra_launches = 0
+        self._side = torch.cuda.Stream(device=dev)
+        self._fork = torch.cuda.Event()
+        self._join = torch.cuda.Event()
+        self._graph = None
         torch.cuda.synchronize(device)
 
     # -- bookkeeping ----------------------------------------------------------------------
@@ -172,17 +176,47 @@ class MoeStack:
     # -- the step -------------------------------------------------------------------------
     def forward(self, x, out, collect_stats: bool = False):
         """x[layers, tokens_local, H] 16-bit -> out[layers, tokens_local, H] fp32."""
+        if self._graph is not None and not collect_stats and x.data_ptr() == self._graph_x and \
+                out.data_ptr() == self._graph_out:
+            self._graph.replay()
+            self._extra_launches += self._graph_launches
+            return
         for l in range(self.layers):
             self.forward_layer(l, x[l], out[l], collect_stats)
+
+    def capture(self, x, out):
+        """Records one step over the fixed buffers x / out as a CUDA graph; later forward(x, out)
+        calls with the same buffers replay it (one launch for the whole stack, no per-kernel
+        launch gaps). The step must have run once already (lazy allocations happen there)."""
+        import torch
+        before = self.launches
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            for l in range(self.layers):
+                self.forward_layer(l, x[l], out[l])
+        self._graph_launches = self.launches - before
+        self._graph, self._graph_x, self._graph_out = graph, x.data_ptr(), out.data_ptr()
 
     def forward_layer(self, l: int, x, out, collect_stats: bool = False, return_routing: bool = False):
         w = self.weights[l]
         ctx = self.ctx
         ops = _DeviceOps(ctx, w)
         if self.world == 1:
+            # The shared expert (88 MB of dense weights, no dependence on the routing) runs on
+            # a side stream while the main stream does router -> permutation -> routed experts;
+            # the two meet at the slot-order accumulate, whose initial value it produces.
+            import torch
+            main = torch.cuda.current_stream()
+            self._fork.record(main)
+            with torch.cuda.stream(self._side):
+                self._side.wait_event(self._fork)
+                ops.shared(x, out)
+                self._join.record(self._side)
             weights, ids = ops.router(x)
-            ops.shared(x, out)
-            ops.routed(x, ids, weights, out, skip_absent=False)
+            ctx.moe_decode(w.pool.base, w.slot_of, x, ids, weights, out, defer_accumulate=True)
+            main.wait_event(self._join)
+            ctx.moe_accumulate(w.slot_of, ids, out)
             tokens_seen = x.shape[0]
         else:
             tl = x.shape[0]

@@ -462,6 +462,17 @@ int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_
     });
 }
 
+int aeon_b200_moe_accumulate(aeon_b200_ctx* ctx, const int32_t* slot_of_expert, const int32_t* topk_ids,
+                             int tokens, float* moe_accum, int64_t accum_stride, uint32_t flags,
+                             void* stream) {
+    return guarded([&] {
+        require(ctx != nullptr, "aeon_b200_moe_accumulate: null context");
+        DeviceGuard guard(ctx->device);
+        launch_moe_accumulate(ctx, slot_of_expert, topk_ids, tokens, moe_accum, accum_stride, flags,
+                              as_stream(stream));
+    });
+}
+
 int aeon_b200_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                           const void* x, int64_t x_stride, const int32_t* topk_ids,
                           const float* topk_weights, int tokens, float* moe_accum,

@@ -148,6 +148,9 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
                        const void* x, int64_t x_stride, const int32_t* topk_ids,
                        const float* topk_weights, int tokens, float* moe_accum,
                        int64_t accum_stride, uint32_t flags, cudaStream_t stream);
+void launch_moe_accumulate(aeon_b200_ctx* ctx, const int32_t* slot_of_expert, const int32_t* topk_ids,
+                           int tokens, float* moe_accum, int64_t accum_stride, uint32_t flags,
+                           cudaStream_t stream);
 void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                         const void* x, int64_t x_stride, const int32_t* topk_ids,
                         const float* topk_weights, int tokens, float* moe_accum, int64_t accum_stride,

@@ -780,13 +780,16 @@ void launch_pair(aeon_b200_ctx* ctx, const DecodeParams& p, KernelA ka, int thre
     kb<<<ctx->sm_count * ctas_per_sm_b, threads_b, smem_b, stream>>>(p);
     AEON_CUDA_CHECK(cudaGetLastError());
     if (ev) AEON_CUDA_CHECK(cudaEventRecord(ev[2], stream));
-    const int64_t vecs = static_cast<int64_t>(p.tokens) * p.H / 4;
-    const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 4 * ctx->sm_count));
-    moe_accumulate_kernel<<<blocks, 256, 0, stream>>>(p.accum, p.accum_stride, p.contrib, p.topk_ids,
-                                                      p.slot_of, p.skip_absent, p.experts, p.tokens,
-                                                      p.top_k, p.H);
-    AEON_CUDA_CHECK(cudaGetLastError());
-    ctx->launches += 3;
+    ctx->launches += 2;
+    if (p.accum != nullptr) {
+        const int64_t vecs = static_cast<int64_t>(p.tokens) * p.H / 4;
+        const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 4 * ctx->sm_count));
+        moe_accumulate_kernel<<<blocks, 256, 0, stream>>>(p.accum, p.accum_stride, p.contrib, p.topk_ids,
+                                                          p.slot_of, p.skip_absent, p.experts, p.tokens,
+                                                          p.top_k, p.H);
+        AEON_CUDA_CHECK(cudaGetLastError());
+        ctx->launches += 1;
+    }
 }
 
 template <int G, int KWA, int NCHA>
@@ -834,6 +837,23 @@ void launch_ep_combine(float* out, int64_t out_stride, const float* partials, in
     const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 2048));
     ep_combine_kernel<<<blocks, 256, 0, stream>>>(out, out_stride, partials, ranks, tokens, hidden);
     AEON_CUDA_CHECK(cudaGetLastError());
+}
+
+void launch_moe_accumulate(aeon_b200_ctx* ctx, const int32_t* slot_of_expert, const int32_t* topk_ids,
+                           int tokens, float* moe_accum, int64_t accum_stride, uint32_t flags,
+                           cudaStream_t stream) {
+    const aeon_b200_moe_config& cfg = ctx->cfg;
+    require(slot_of_expert && topk_ids && moe_accum, "aeon_b200_moe_accumulate: null pointer argument");
+    require(tokens > 0 && tokens <= ctx->max_tokens,
+            "aeon_b200_moe_accumulate: tokens must be in [1, max_tokens of the context]");
+    require(accum_stride >= cfg.hidden && accum_stride % 4 == 0, "aeon_b200_moe_accumulate: bad row stride");
+    const int64_t vecs = static_cast<int64_t>(tokens) * cfg.hidden / 4;
+    const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 4 * ctx->sm_count));
+    moe_accumulate_kernel<<<blocks, 256, 0, stream>>>(
+        moe_accum, accum_stride, ctx->d_contrib, topk_ids, slot_of_expert,
+        (flags & AEON_B200_DECODE_SKIP_ABSENT) ? 1 : 0, cfg.experts, tokens, cfg.top_k, cfg.hidden);
+    AEON_CUDA_CHECK(cudaGetLastError());
+    ctx->launches += 1;
 }
 
 void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
@@ -891,7 +911,7 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     p.hid_hi = ctx->d_hidden_hi;
     p.hid_lo = ctx->d_hidden_lo;
     p.contrib = ctx->d_contrib;
-    p.accum = moe_accum;
+    p.accum = (flags & AEON_B200_DECODE_DEFER_ACCUMULATE) ? nullptr : moe_accum;
     p.accum_stride = accum_stride;
     p.limit = cfg.swiglu_limit;
     p.error = ctx->d_error;
