@@ -340,7 +340,9 @@ def main():
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from datetime import timedelta
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=timedelta(seconds=180))
 
     cfg = aeon_b200.preset("baseline")
     if args.case == "tp":
@@ -351,8 +353,7 @@ def main():
         line = tp_bench(args, cfg, dist, rank, world, local_rank, peaks)
         if rank == 0:
             print(json.dumps(line), flush=True)
-        if dist is not None:
-            dist.destroy_process_group()
+        shutdown(dist)
         return
     if args.case in ("small", "prefill_small"):
         cfg = cfg.copy(experts=64)
@@ -419,12 +420,14 @@ def main():
     model.set_timing(False)
     # the timed step replays a CUDA graph of the whole stack (one launch per step)
     graph_note = "cuda graph replay"
-    if args.case == "full":
+    if args.case == "full" and world == 1:
         try:
             model.capture(x_dev, out_dev)
         except Exception as exc:          # keep the eager path if capture is refused
             graph_note = f"eager launches (graph capture failed: {type(exc).__name__})"
     else:
+        # Multi-rank steps stay eager: a graph holding NCCL collectives made
+        # destroy_process_group() block at exit on this software stack.
         graph_note = "eager launches"
     launches_before = model.launches
     ms, clocks = timed(step_resident, args.steps, warmup, sample_clocks=True)
@@ -505,8 +508,23 @@ def main():
                        f"= {sec:.3f} s on {cores} threads, scaled x{args.layers} layers; fp64 oracle")}
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if dist is not None:
+    shutdown(dist)
+
+
+def shutdown(dist):
+    """Leaves the process group; a teardown that blocks must not keep the job alive."""
+    if dist is None:
+        return
+    import threading
+    sys.stdout.flush()
+    watchdog = threading.Timer(60.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    try:
+        dist.barrier()
         dist.destroy_process_group()
+    finally:
+        watchdog.cancel()
 
 
 if __name__ == "__main__":
