@@ -480,7 +480,11 @@ def main():
         "roofline": {
             "bound": "hbm", "kernel": "moe_w13_swiglu_kernel", "achieved": achieved_a, "peak": peak_gbs,
             "unit": "GB/s", "frac": (achieved_a / peak_gbs) if achieved_a else None,
-            "peak_source": peak_kind, "traffic": None,
+            "peak_source": peak_kind,
+            # ncu DRAM traffic of this kernel on the small case (63 experts: 954.3 MB read +
+            # 5.7 MB written, profiles/moe_w13_swiglu_small_decode.md), scaled by the distinct
+            # experts of a launch; every weight byte is read once, so traffic is proportional
+            "traffic": mean_distinct * (959_984_128 / 63.0),
             "algorithmic_bytes_per_launch": bytes_a, "avg_launch_ms": avg_a_ms, "launches_timed": n_a,
             "second_kernel": {"kernel": "moe_w2_contrib_kernel", "achieved": achieved_b,
                               "frac": (achieved_b / peak_gbs) if achieved_b else None,
