@@ -101,6 +101,43 @@ int aeon_b200_unswizzle_w4a16(const uint32_t* src_packed_host, const uint16_t* s
                               uint32_t* dst_packed_host, uint16_t* dst_scale_host,
                               int N, int K, int rpw, int lpr, int group);
 
+/*
+ * Shard-aware expert payloads (host only). The reference plans this layout as
+ * "expert v3" (plans-and-docs/execution/active/MULTI_GPU_EXECUTION_PLAN.md:151-181)
+ * but ships only v2 (writer scripts/convert_safetensors_to_aeon.py:46-187, loader
+ * src/infrastructure/artifact/aeon_loader.hpp:345-405). A payload of `shards`
+ * shards is `shards` complete payloads back to back; shard s holds the slice
+ * [s*I/shards, (s+1)*I/shards) of the intermediate dimension (rows of W1/W3,
+ * columns of W2, cut from the checkpoint layout and swizzled on their own: the
+ * rule of tests/test_expert_shard_equivalence.cpp:286-340). shards == 1 is the
+ * v2 payload. `cfg_host` always describes the whole expert (or, for merge, the
+ * whole slice); source tensors are row-major W1/W3 [I, H/8] words + [I, H/group]
+ * scales and W2 [H, I/8] + [H, I/group].
+ */
+int aeon_b200_expert_shard_bytes(const aeon_b200_moe_config* cfg_host, int shards,
+                                 uint64_t* shard_bytes_host);
+int aeon_b200_pack_expert_shards(const aeon_b200_moe_config* cfg_host, int shards,
+                                 const uint32_t* w1_packed_host, const uint16_t* w1_scale_host,
+                                 const uint32_t* w2_packed_host, const uint16_t* w2_scale_host,
+                                 const uint32_t* w3_packed_host, const uint16_t* w3_scale_host,
+                                 uint8_t* payload_host);
+int aeon_b200_unpack_expert_shards(const aeon_b200_moe_config* cfg_host, int shards,
+                                   const uint8_t* payload_host,
+                                   uint32_t* w1_packed_host, uint16_t* w1_scale_host,
+                                   uint32_t* w2_packed_host, uint16_t* w2_scale_host,
+                                   uint32_t* w3_packed_host, uint16_t* w3_scale_host);
+/* Byte range, inside a payload of `shards` shards, that rank `rank` of a
+ * tensor-parallel group of degree `tp` reads: offset = rank * (shards/tp) *
+ * shard_bytes, length = payload_bytes / tp (the planned AeonModelLoader::rank_slice).
+ * tp must divide shards (invalid_argument otherwise); rank in [0, tp). */
+int aeon_b200_expert_rank_slice(const aeon_b200_moe_config* cfg_host, int shards, int tp, int rank,
+                                uint64_t* offset_host, uint64_t* length_host);
+/* A rank slice of `shards` shards -> one payload of intermediate width
+ * cfg_host->intermediate (= shards * shard width), the form the kernels read.
+ * Done once at load time, so the kernels carry no shard arithmetic. */
+int aeon_b200_merge_expert_shards(const aeon_b200_moe_config* cfg_host, int shards,
+                                  const uint8_t* slice_host, uint8_t* payload_host);
+
 /* A context owns the device scratch of the path for up to `max_tokens` tokens
  * per call. Replaces V4RoutedExpertScratch
  * (src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:95-173). */

@@ -34,6 +34,8 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_moe_decode", "aeon_b200_ctx_last_stats", "aeon_b200_synth_fill_experts",
     "aeon_b200_synth_fill_dense16", "aeon_b200_ctx_set_timing", "aeon_b200_ctx_kernel_times",
     "aeon_b200_ep_combine", "aeon_b200_router_topk_noalloc", "aeon_b200_moe_prefill", "aeon_b200_moe_accumulate",
+    "aeon_b200_expert_shard_bytes", "aeon_b200_pack_expert_shards", "aeon_b200_unpack_expert_shards",
+    "aeon_b200_expert_rank_slice", "aeon_b200_merge_expert_shards",
 ]
 
 
@@ -90,6 +92,13 @@ def lib() -> ctypes.CDLL:
     swz = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
     L.aeon_b200_swizzle_w4a16.argtypes = swz
     L.aeon_b200_unswizzle_w4a16.argtypes = swz
+    L.aeon_b200_expert_shard_bytes.argtypes = [POINTER(MoeConfig), c_int, POINTER(c_uint64)]
+    six = [c_void_p] * 6
+    L.aeon_b200_pack_expert_shards.argtypes = [POINTER(MoeConfig), c_int] + six + [c_void_p]
+    L.aeon_b200_unpack_expert_shards.argtypes = [POINTER(MoeConfig), c_int, c_void_p] + six
+    L.aeon_b200_expert_rank_slice.argtypes = [POINTER(MoeConfig), c_int, c_int, c_int,
+                                              POINTER(c_uint64), POINTER(c_uint64)]
+    L.aeon_b200_merge_expert_shards.argtypes = [POINTER(MoeConfig), c_int, c_void_p, c_void_p]
     L.aeon_b200_ctx_create.argtypes = [POINTER(MoeConfig), c_int, c_int, POINTER(c_void_p)]
     L.aeon_b200_ctx_destroy.argtypes = [c_void_p]
     L.aeon_b200_ctx_check.argtypes = [c_void_p, c_void_p]
@@ -151,6 +160,67 @@ def swizzle_w4a16(src_packed, src_scale, N, K, rpw, lpr, group, inverse=False):
     check(fn(src_packed.ctypes.data, src_scale.ctypes.data, dst_packed.ctypes.data,
              dst_scale.ctypes.data, N, K, rpw, lpr, group))
     return dst_packed, dst_scale
+
+
+def expert_shard_bytes(cfg: MoeConfig, shards: int) -> int:
+    """Bytes of one shard of an expert payload cut into `shards` intermediate-dimension shards."""
+    out = c_uint64()
+    check(lib().aeon_b200_expert_shard_bytes(ctypes.byref(cfg), shards, ctypes.byref(out)))
+    return out.value
+
+
+def source_shapes(cfg: MoeConfig):
+    """Checkpoint-order shapes: (w1_packed, w1_scale, w2_packed, w2_scale, w3_packed, w3_scale)."""
+    H, I, G = cfg.hidden, cfg.intermediate, cfg.group_size
+    return ((I, H // 8), (I, H // G), (H, I // 8), (H, I // G), (I, H // 8), (I, H // G))
+
+
+def pack_expert_shards(cfg: MoeConfig, shards: int, source):
+    """Six checkpoint-order arrays (see source_shapes) -> payload of `shards` shards (numpy uint8)."""
+    import numpy as np
+    arrays = []
+    for arr, shape, dtype in zip(source, source_shapes(cfg), (np.uint32, np.uint16) * 3):
+        a = np.ascontiguousarray(arr, dtype=dtype)
+        if a.shape != shape:
+            raise AeonError(1, f"pack_expert_shards: source tensor has shape {a.shape}, expected {shape}")
+        arrays.append(a)
+    payload = np.empty(shards * expert_shard_bytes(cfg, shards), dtype=np.uint8)
+    check(lib().aeon_b200_pack_expert_shards(ctypes.byref(cfg), shards, *[a.ctypes.data for a in arrays],
+                                             payload.ctypes.data))
+    return payload
+
+
+def unpack_expert_shards(cfg: MoeConfig, shards: int, payload):
+    """Inverse of pack_expert_shards: the six checkpoint-order arrays of the whole expert."""
+    import numpy as np
+    payload = np.ascontiguousarray(payload, dtype=np.uint8)
+    if payload.size != shards * expert_shard_bytes(cfg, shards):
+        raise AeonError(1, "unpack_expert_shards: payload size does not match shards * shard bytes")
+    out = [np.empty(shape, dtype=dtype)
+           for shape, dtype in zip(source_shapes(cfg), (np.uint32, np.uint16) * 3)]
+    check(lib().aeon_b200_unpack_expert_shards(ctypes.byref(cfg), shards, payload.ctypes.data,
+                                               *[a.ctypes.data for a in out]))
+    return out
+
+
+def expert_rank_slice(cfg: MoeConfig, shards: int, tp: int, rank: int):
+    """(offset, length) in bytes, inside one payload, of the shards rank `rank` of `tp` reads."""
+    off, length = c_uint64(), c_uint64()
+    check(lib().aeon_b200_expert_rank_slice(ctypes.byref(cfg), shards, tp, rank, ctypes.byref(off),
+                                            ctypes.byref(length)))
+    return off.value, length.value
+
+
+def merge_expert_shards(cfg_slice: MoeConfig, shards: int, slice_bytes):
+    """A rank's slice of `shards` shards -> one payload of width cfg_slice.intermediate."""
+    import numpy as np
+    slice_bytes = np.ascontiguousarray(slice_bytes, dtype=np.uint8)
+    if slice_bytes.size != shards * expert_shard_bytes(cfg_slice, shards):
+        raise AeonError(1, "merge_expert_shards: slice size does not match shards * shard bytes")
+    out = np.empty(expert_layout(cfg_slice).payload_bytes, dtype=np.uint8)
+    check(lib().aeon_b200_merge_expert_shards(ctypes.byref(cfg_slice), shards, slice_bytes.ctypes.data,
+                                              out.ctypes.data))
+    return out
 
 
 def _ptr(t):

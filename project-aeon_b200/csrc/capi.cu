@@ -99,8 +99,10 @@ inline uint32_t unpermute_word(uint32_t source) {
     return out;
 }
 
+}  // namespace
+
 // Walks every 16-byte atom once; `forward` copies checkpoint order -> swizzled order.
-void relayout(const uint32_t* src_packed, const uint16_t* src_scale, uint32_t* dst_packed,
+void relayout_w4a16(const uint32_t* src_packed, const uint16_t* src_scale, uint32_t* dst_packed,
               uint16_t* dst_scale, int N, int K, int rpw, int lpr, int group, bool forward) {
     const int atoms_per_row = K / 32;
     const int iters = atoms_per_row / lpr;
@@ -125,6 +127,8 @@ void relayout(const uint32_t* src_packed, const uint16_t* src_scale, uint32_t* d
         }
     }
 }
+
+namespace {
 
 template <class T>
 T* device_alloc(size_t count, uint64_t& total) {
@@ -226,7 +230,7 @@ int aeon_b200_swizzle_w4a16(const uint32_t* sp, const uint16_t* ss, uint32_t* dp
     return guarded([&] {
         require(sp && ss && dp && ds, "aeon_b200_swizzle_w4a16: null pointer argument");
         check_swizzle_args(N, K, rpw, lpr, group);
-        relayout(sp, ss, dp, ds, N, K, rpw, lpr, group, true);
+        relayout_w4a16(sp, ss, dp, ds, N, K, rpw, lpr, group, true);
     });
 }
 
@@ -235,7 +239,7 @@ int aeon_b200_unswizzle_w4a16(const uint32_t* sp, const uint16_t* ss, uint32_t* 
     return guarded([&] {
         require(sp && ss && dp && ds, "aeon_b200_unswizzle_w4a16: null pointer argument");
         check_swizzle_args(N, K, rpw, lpr, group);
-        relayout(sp, ss, dp, ds, N, K, rpw, lpr, group, false);
+        relayout_w4a16(sp, ss, dp, ds, N, K, rpw, lpr, group, false);
     });
 }
 

@@ -73,6 +73,9 @@ struct ExpertGeom {
 
 ExpertGeom make_geom(const aeon_b200_moe_config& cfg);
 void validate_config(const aeon_b200_moe_config& cfg);
+// Host re-layout of one matrix between checkpoint order and swizzled order (capi.cu).
+void relayout_w4a16(const uint32_t* src_packed, const uint16_t* src_scale, uint32_t* dst_packed,
+                    uint16_t* dst_scale, int N, int K, int rpw, int lpr, int group, bool forward);
 
 // Device error flag values (ctx->d_error).
 enum : int {

@@ -14,8 +14,10 @@
 //   ExpertRegistry              src/infrastructure/expert/residency/expert_registry.hpp:26-1064
 //                               (the HBM-resident subset: hot hits, cold misses into free or
 //                               least-recently-used unleased slots, leases, invariant audit)
-//   AeonExpertContainer         the expert half of AeonModelLoader,
-//                               src/infrastructure/artifact/aeon_loader.hpp:145-166,318-441
+//   AeonModelLoader             src/infrastructure/artifact/aeon_loader.hpp:41-166: AeonExpertContainer
+//                               (the expert index + payload file, :145-166,318-441, in version 2
+//                               and in the planned shard-aware version 3 with rank_slice) and
+//                               AeonDenseContainer (the dense file, :243-316,441-479)
 //   V4RoutedExpertExecutor      src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:32-112
 //   V4TieredExpertExecutor      src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:178-634
 //   dispatch_router             src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:124-159
@@ -23,6 +25,11 @@
 #pragma once
 
 #include "aeon_b200.h"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <cstdint>
@@ -234,11 +241,20 @@ struct ExpertFormatDescriptor {
     uint32_t num_layers{0};
     uint32_t experts_per_layer{0};
     size_t payload_bytes{0};
+    // Shard-aware payloads (version 3): shard_count self-contained shards of the intermediate
+    // dimension, shard-major. Version 2 means {1, payload_bytes}; shard_bytes 0 is read as that.
+    uint32_t shard_count{1};
+    size_t shard_bytes{0};
 
     uint64_t total_experts() const noexcept { return static_cast<uint64_t>(num_layers) * experts_per_layer; }
+    size_t bytes_per_shard() const noexcept { return shard_bytes != 0 ? shard_bytes : payload_bytes; }
     void validate_payload() const {
         if (payload_bytes == 0 || sector_size == 0 || payload_bytes % sector_size != 0)
             throw std::invalid_argument("ExpertFormatDescriptor: payload must be a positive multiple of the sector size");
+        if (shard_count == 0 || static_cast<uint64_t>(shard_count) * bytes_per_shard() != payload_bytes)
+            throw std::invalid_argument("ExpertFormatDescriptor: shard_count x shard_bytes must equal the payload size");
+        if (bytes_per_shard() % sector_size != 0)
+            throw std::invalid_argument("ExpertFormatDescriptor: shard_bytes must be a multiple of the sector size");
     }
     void validate_catalog() const {
         validate_payload();
@@ -247,11 +263,19 @@ struct ExpertFormatDescriptor {
     }
 };
 
-inline ExpertFormatDescriptor make_swizzled_expert_format(const aeon_b200_moe_config& cfg, uint32_t layers) {
-    aeon_b200_expert_layout lay{};
-    check_status(aeon_b200_expert_layout_of(&cfg, &lay));
-    return ExpertFormatDescriptor{ExpertFormatKind::SWIZZLED_W4A16, 2, 4096, layers,
-                                  static_cast<uint32_t>(cfg.experts), static_cast<size_t>(lay.payload_bytes)};
+inline ExpertFormatDescriptor make_swizzled_expert_format(const aeon_b200_moe_config& cfg, uint32_t layers,
+                                                          uint32_t shard_count = 1) {
+    uint64_t shard_bytes = 0;
+    check_status(aeon_b200_expert_shard_bytes(&cfg, static_cast<int>(shard_count), &shard_bytes));
+    ExpertFormatDescriptor f;
+    f.kind = ExpertFormatKind::SWIZZLED_W4A16;
+    f.version = shard_count > 1 ? 3 : 2;
+    f.num_layers = layers;
+    f.experts_per_layer = static_cast<uint32_t>(cfg.experts);
+    f.payload_bytes = static_cast<size_t>(shard_bytes) * shard_count;
+    f.shard_count = shard_count;
+    f.shard_bytes = static_cast<size_t>(shard_bytes);
+    return f;
 }
 
 // One device slab of slots x payload_bytes; a slot is a byte-identical expert payload.
@@ -548,13 +572,60 @@ public:
 };
 
 // ---------------------------------------------------------------------------------------------
+// Read-only memory mapping of a file (the loader maps both containers, aeon_loader.hpp:243-270).
+// ---------------------------------------------------------------------------------------------
+class MappedFile {
+public:
+    MappedFile() = default;
+    MappedFile(const MappedFile&) = delete;
+    MappedFile& operator=(const MappedFile&) = delete;
+    ~MappedFile() { close(); }
+
+    void open(const std::string& path, const char* what) {
+        close();
+        fd_ = ::open(path.c_str(), O_RDONLY);
+        if (fd_ < 0) throw std::runtime_error(std::string("AeonModelLoader: Failed to open ") + what + ": " + path);
+        struct stat st;
+        if (::fstat(fd_, &st) != 0) {
+            close();
+            throw std::runtime_error(std::string("AeonModelLoader: Failed to stat ") + what + ": " + path);
+        }
+        size_ = static_cast<size_t>(st.st_size);
+        if (size_ != 0) {
+            void* m = ::mmap(nullptr, size_, PROT_READ, MAP_SHARED, fd_, 0);
+            if (m == MAP_FAILED) {
+                close();
+                throw std::runtime_error(std::string("AeonModelLoader: Failed to mmap ") + what + ": " + path);
+            }
+            base_ = static_cast<const uint8_t*>(m);
+        }
+    }
+    void close() noexcept {
+        if (base_) ::munmap(const_cast<uint8_t*>(base_), size_);
+        if (fd_ >= 0) ::close(fd_);
+        base_ = nullptr; size_ = 0; fd_ = -1;
+    }
+    const uint8_t* data() const noexcept { return base_; }
+    size_t size() const noexcept { return size_; }
+
+private:
+    int fd_{-1};
+    const uint8_t* base_{nullptr};
+    size_t size_{0};
+};
+
+// ---------------------------------------------------------------------------------------------
 // Expert container: `.index` = magic "AEON_EXPERTS", u32 version, u32 layers, u32 experts per
-// layer, u64 expert bytes, then (u64 offset, u64 length) per expert; payloads in a second file.
+// layer, u64 payload bytes (version 2: 32 bytes), then for version 3 u32 shard count, u32 zero,
+// u64 shard bytes (48 bytes), then (u64 offset, u64 length) per expert; payloads in a second,
+// memory-mapped file. Version 3 is the shard-aware layout the reference plans
+// (plans-and-docs/execution/active/MULTI_GPU_EXECUTION_PLAN.md:151-181).
 // ---------------------------------------------------------------------------------------------
 class AeonExpertContainer {
 public:
     struct Location { uint64_t offset; uint64_t length; };
 
+    // expected_version 0 accepts 2 and 3; expected_payload_bytes 0 accepts any size.
     void open(const std::string& index_path, const std::string& experts_path, uint32_t expected_version,
               size_t expected_payload_bytes) {
         std::ifstream idx(index_path, std::ios::binary);
@@ -569,48 +640,99 @@ public:
         std::memcpy(&layers, buf.data() + 16, 4);
         std::memcpy(&experts, buf.data() + 20, 4);
         std::memcpy(&expert_bytes, buf.data() + 24, 8);
-        if (version != expected_version)
+        if (expected_version != 0 ? version != expected_version : (version != 2 && version != 3))
             throw std::runtime_error("AeonModelLoader: Unexpected expert index version " + std::to_string(version) +
-                                     ", expected " + std::to_string(expected_version));
+                                     ", expected " + (expected_version ? std::to_string(expected_version) : "2 or 3"));
         if (expected_payload_bytes != 0 && expert_bytes != expected_payload_bytes)
             throw std::runtime_error("AeonModelLoader: Expert payload size does not match the artifact specification");
-        format_ = ExpertFormatDescriptor{ExpertFormatKind::SWIZZLED_W4A16, version, 4096, layers, experts,
-                                         static_cast<size_t>(expert_bytes)};
-        format_.validate_catalog();
-        const uint64_t total = format_.total_experts();
-        if (buf.size() < 32 + total * 16) throw std::runtime_error("AeonModelLoader: Expert index has incomplete entries!");
-        locations_.resize(total);
+        size_t head = 32;
+        uint32_t shard_count = 1;
+        uint64_t shard_bytes = expert_bytes;
+        if (version == 3) {
+            if (buf.size() < 48) throw std::runtime_error("AeonModelLoader: Expert index too small for header!");
+            std::memcpy(&shard_count, buf.data() + 32, 4);
+            std::memcpy(&shard_bytes, buf.data() + 40, 8);
+            head = 48;
+        }
+        ExpertFormatDescriptor f;
+        f.kind = ExpertFormatKind::SWIZZLED_W4A16;
+        f.version = version;
+        f.num_layers = layers;
+        f.experts_per_layer = experts;
+        f.payload_bytes = static_cast<size_t>(expert_bytes);
+        f.shard_count = shard_count;
+        f.shard_bytes = static_cast<size_t>(shard_bytes);
+        try {
+            f.validate_catalog();
+        } catch (const std::invalid_argument& e) {
+            throw std::runtime_error(std::string("AeonModelLoader: ") + e.what());
+        }
+        const uint64_t total = f.total_experts();
+        if (buf.size() < head + total * 16) throw std::runtime_error("AeonModelLoader: Expert index has incomplete entries!");
+        std::vector<Location> locations(total);
         for (uint64_t i = 0; i < total; ++i) {
             uint64_t off, len;
-            std::memcpy(&off, buf.data() + 32 + i * 16, 8);
-            std::memcpy(&len, buf.data() + 32 + i * 16 + 8, 8);
-            if (len != expert_bytes || off % format_.sector_size != 0)
+            std::memcpy(&off, buf.data() + head + i * 16, 8);
+            std::memcpy(&len, buf.data() + head + i * 16 + 8, 8);
+            if (len != expert_bytes || off % f.sector_size != 0)
                 throw std::runtime_error("AeonModelLoader: Expert index contains an invalid payload entry");
-            locations_[i] = Location{off, len};
+            locations[i] = Location{off, len};
         }
-        std::ifstream exp(experts_path, std::ios::binary | std::ios::ate);
-        if (!exp) throw std::runtime_error("AeonModelLoader: Failed to open experts file: " + experts_path);
-        const uint64_t size = static_cast<uint64_t>(exp.tellg());
-        for (const Location& l : locations_)
-            if (l.offset + l.length > size)
+        file_.open(experts_path, "experts file");
+        for (const Location& l : locations)
+            if (l.offset + l.length > file_.size()) {
+                file_.close();
                 throw std::runtime_error("AeonModelLoader: Expert payload lies outside the experts file");
-        exp.seekg(0);
-        data_.resize(size);
-        exp.read(reinterpret_cast<char*>(data_.data()), static_cast<std::streamsize>(size));
+            }
+        format_ = f;
+        locations_ = std::move(locations);
     }
 
     const ExpertFormatDescriptor& format() const noexcept { return format_; }
     Location get_expert_location(uint32_t layer, uint32_t expert) const { return locations_.at(index_of(layer, expert)); }
     const uint8_t* get_expert_data(uint32_t layer, uint32_t expert) const {
-        return data_.data() + locations_.at(index_of(layer, expert)).offset;
+        return file_.data() + locations_.at(index_of(layer, expert)).offset;
+    }
+
+    // What rank `rank` of a tensor-parallel group of degree `tp` reads of one expert: one
+    // contiguous, sector-aligned range, offset + rank * (shards / tp) * shard_bytes, payload / tp
+    // long. tp must divide the artifact's shard count (its maximum tensor-parallel degree).
+    Location rank_slice(uint32_t layer, uint32_t expert, uint32_t tp, uint32_t rank) const {
+        const Location whole = get_expert_location(layer, expert);
+        if (tp == 0 || format_.shard_count % tp != 0)
+            throw std::invalid_argument("AeonModelLoader: tensor_parallel=" + std::to_string(tp) +
+                                        " does not divide the artifact's max tensor-parallel degree " +
+                                        std::to_string(format_.shard_count));
+        if (rank >= tp) throw std::out_of_range("AeonModelLoader: tensor-parallel rank out of range");
+        const uint64_t per_rank = static_cast<uint64_t>(format_.shard_count / tp) * format_.bytes_per_shard();
+        return Location{whole.offset + rank * per_rank, per_rank};
+    }
+
+    // The payload rank `rank` uploads into its pool: its slice with the slice's shards merged
+    // into one swizzled payload of width cfg.intermediate / tp. `cfg` describes the whole expert.
+    std::vector<uint8_t> read_rank_payload(const aeon_b200_moe_config& cfg, uint32_t layer, uint32_t expert,
+                                           uint32_t tp, uint32_t rank) const {
+        const Location slice = rank_slice(layer, expert, tp, rank);
+        aeon_b200_moe_config rank_cfg = cfg;
+        rank_cfg.intermediate = cfg.intermediate / static_cast<int32_t>(tp);
+        aeon_b200_expert_layout lay{};
+        check_status(aeon_b200_expert_layout_of(&rank_cfg, &lay));
+        std::vector<uint8_t> out(lay.payload_bytes);
+        check_status(aeon_b200_merge_expert_shards(&rank_cfg, static_cast<int>(format_.shard_count / tp),
+                                                   file_.data() + slice.offset, out.data()));
+        return out;
     }
 
     // Writer used by tools and tests: payloads in (layer, expert) order, sector-aligned.
+    // shard_count > 1 writes the version-3 header (the payloads must already be shard-major,
+    // aeon_b200_pack_expert_shards).
     static void write(const std::string& index_path, const std::string& experts_path, uint32_t version,
                       uint32_t layers, uint32_t experts, uint64_t expert_bytes,
-                      const std::vector<const uint8_t*>& payloads) {
+                      const std::vector<const uint8_t*>& payloads, uint32_t shard_count = 1) {
         if (payloads.size() != static_cast<size_t>(layers) * experts)
             throw std::invalid_argument("AeonExpertContainer::write: payload count does not match the catalog");
+        if (shard_count == 0 || expert_bytes % shard_count != 0 || (version < 3 && shard_count != 1))
+            throw std::invalid_argument("AeonExpertContainer::write: shard count does not fit the version or the payload size");
         std::ofstream idx(index_path, std::ios::binary), exp(experts_path, std::ios::binary);
         if (!idx || !exp) throw std::runtime_error("AeonExpertContainer::write: cannot create the output files");
         idx.write("AEON_EXPERTS", 12);
@@ -618,6 +740,13 @@ public:
         idx.write(reinterpret_cast<const char*>(&layers), 4);
         idx.write(reinterpret_cast<const char*>(&experts), 4);
         idx.write(reinterpret_cast<const char*>(&expert_bytes), 8);
+        if (version >= 3) {
+            const uint32_t zero = 0;
+            const uint64_t shard_bytes = expert_bytes / shard_count;
+            idx.write(reinterpret_cast<const char*>(&shard_count), 4);
+            idx.write(reinterpret_cast<const char*>(&zero), 4);
+            idx.write(reinterpret_cast<const char*>(&shard_bytes), 8);
+        }
         uint64_t offset = 0;
         for (const uint8_t* payload : payloads) {
             idx.write(reinterpret_cast<const char*>(&offset), 8);
@@ -635,7 +764,231 @@ private:
     }
     ExpertFormatDescriptor format_{};
     std::vector<Location> locations_;
-    std::vector<uint8_t> data_;
+    MappedFile file_;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Dense container: "AEON_DENSE\0\0", u32 version, u32 tensor count, u64 directory length, a
+// JSON directory [{name, offset, size, dtype, shape}], tensor bytes from the next 4 KiB
+// boundary (src/infrastructure/artifact/aeon_loader.hpp:243-316,441-479). The router gate and
+// the shared expert of every layer live here
+// (src/architecture/deepseek_v4/spec/v4_dense_weight_binding.hpp:123-137).
+// ---------------------------------------------------------------------------------------------
+struct LoadedTensor {
+    const uint8_t* data{nullptr};
+    int64_t byte_size{0};
+    std::string dtype;
+    std::vector<int64_t> shape;
+};
+
+namespace detail {
+
+// The few JSON forms the directory uses: an array of flat objects whose values are strings,
+// integers or arrays of integers. Anything else is refused.
+class DirectoryParser {
+public:
+    explicit DirectoryParser(const std::string& text) : s_(text) {}
+
+    template <class F>   // F(name, offset, size, dtype, shape)
+    size_t parse(F&& emit) {
+        size_t count = 0;
+        skip();
+        expect('[');
+        skip();
+        if (peek() == ']') { ++i_; end(); return 0; }
+        for (;;) {
+            std::string name, dtype;
+            int64_t offset = -1, size = -1;
+            std::vector<int64_t> shape;
+            bool has_name = false, has_dtype = false, has_offset = false, has_size = false, has_shape = false;
+            skip();
+            expect('{');
+            for (;;) {
+                skip();
+                const std::string key = string();
+                skip();
+                expect(':');
+                skip();
+                if (key == "name") { name = string(); has_name = true; }
+                else if (key == "dtype") { dtype = string(); has_dtype = true; }
+                else if (key == "offset") { offset = integer(); has_offset = true; }
+                else if (key == "size") { size = integer(); has_size = true; }
+                else if (key == "shape") {
+                    expect('[');
+                    skip();
+                    if (peek() == ']') ++i_;
+                    else
+                        for (;;) {
+                            skip();
+                            shape.push_back(integer());
+                            skip();
+                            if (peek() == ',') { ++i_; continue; }
+                            expect(']');
+                            break;
+                        }
+                    has_shape = true;
+                } else {
+                    fail("unknown key \"" + key + "\"");
+                }
+                skip();
+                if (peek() == ',') { ++i_; continue; }
+                expect('}');
+                break;
+            }
+            if (!(has_name && has_dtype && has_offset && has_size && has_shape)) fail("entry lacks a field");
+            emit(name, offset, size, dtype, shape);
+            ++count;
+            skip();
+            if (peek() == ',') { ++i_; continue; }
+            expect(']');
+            break;
+        }
+        end();
+        return count;
+    }
+
+private:
+    void end() { skip(); if (i_ != s_.size()) fail("text after the directory"); }
+    [[noreturn]] void fail(const std::string& why) const {
+        throw std::runtime_error("AeonModelLoader: Malformed dense directory (" + why + " at byte " + std::to_string(i_) + ")");
+    }
+    char peek() const { return i_ < s_.size() ? s_[i_] : '\0'; }
+    void skip() { while (i_ < s_.size() && (s_[i_] == ' ' || s_[i_] == '\n' || s_[i_] == '\t' || s_[i_] == '\r')) ++i_; }
+    void expect(char c) { if (peek() != c) fail(std::string("expected '") + c + "'"); ++i_; }
+    std::string string() {
+        expect('"');
+        std::string out;
+        while (i_ < s_.size() && s_[i_] != '"') {
+            if (s_[i_] == '\\') {
+                if (i_ + 1 >= s_.size()) fail("dangling escape");
+                const char e = s_[i_ + 1];
+                if (e == '"' || e == '\\' || e == '/') out.push_back(e);
+                else fail("unsupported escape");
+                i_ += 2;
+            } else {
+                out.push_back(s_[i_++]);
+            }
+        }
+        expect('"');
+        return out;
+    }
+    int64_t integer() {
+        const size_t start = i_;
+        bool negative = false;
+        if (peek() == '-') { negative = true; ++i_; }
+        if (peek() < '0' || peek() > '9') fail("expected an integer");
+        int64_t v = 0;
+        while (peek() >= '0' && peek() <= '9') {
+            if (v > (INT64_MAX - 9) / 10) fail("integer too large");
+            v = v * 10 + (s_[i_++] - '0');
+        }
+        if (peek() == '.' || peek() == 'e' || peek() == 'E') { i_ = start; fail("expected an integer"); }
+        return negative ? -v : v;
+    }
+    const std::string& s_;
+    size_t i_{0};
+};
+
+}  // namespace detail
+
+class AeonDenseContainer {
+public:
+    void open(const std::string& path, uint32_t expected_version = 1) {
+        file_.open(path, "dense file");
+        tensors_.clear();
+        if (file_.size() < 28) throw std::runtime_error("AeonModelLoader: Dense file too small for header: " + path);
+        if (std::memcmp(file_.data(), "AEON_DENSE\0\0", 12) != 0)
+            throw std::runtime_error("AeonModelLoader: Invalid dense magic in " + path);
+        uint32_t version, count;
+        uint64_t dir_len;
+        std::memcpy(&version, file_.data() + 12, 4);
+        std::memcpy(&count, file_.data() + 16, 4);
+        std::memcpy(&dir_len, file_.data() + 20, 8);
+        if (version != expected_version)
+            throw std::runtime_error("AeonModelLoader: Unexpected dense format version " + std::to_string(version) +
+                                     ", expected " + std::to_string(expected_version));
+        if (dir_len > file_.size() - 28) throw std::runtime_error("AeonModelLoader: Directory length exceeds file size!");
+        const std::string dir(reinterpret_cast<const char*>(file_.data() + 28), static_cast<size_t>(dir_len));
+        size_t start = 28 + static_cast<size_t>(dir_len);
+        start += (4096 - start % 4096) % 4096;
+        if (start > file_.size()) throw std::runtime_error("AeonModelLoader: Dense payload starts beyond file size");
+        const uint64_t room = file_.size() - start;
+        const uint8_t* base = file_.data() + start;
+        detail::DirectoryParser parser(dir);
+        const size_t parsed = parser.parse([&](const std::string& name, int64_t offset, int64_t size,
+                                               const std::string& dtype, const std::vector<int64_t>& shape) {
+            if (offset < 0 || size < 0) throw std::runtime_error("AeonModelLoader: Dense directory contains a negative range");
+            if (static_cast<uint64_t>(offset) > room || static_cast<uint64_t>(size) > room - static_cast<uint64_t>(offset))
+                throw std::runtime_error("AeonModelLoader: Dense tensor range exceeds payload");
+            for (int64_t d : shape)
+                if (d < 0) throw std::runtime_error("AeonModelLoader: Dense tensor shape is negative");
+            LoadedTensor t;
+            t.data = base + offset;
+            t.byte_size = size;
+            t.dtype = dtype;
+            t.shape = shape;
+            if (!tensors_.emplace(name, std::move(t)).second)
+                throw std::runtime_error("AeonModelLoader: Duplicate dense tensor: " + name);
+        });
+        if (parsed != count) throw std::runtime_error("AeonModelLoader: Dense directory count does not match its header");
+    }
+
+    bool has_tensor(const std::string& name) const { return tensors_.count(name) != 0; }
+    const LoadedTensor& get_tensor(const std::string& name) const {
+        const auto it = tensors_.find(name);
+        if (it == tensors_.end()) throw std::runtime_error("AeonModelLoader: Missing dense tensor: " + name);
+        return it->second;
+    }
+    size_t tensor_count() const noexcept { return tensors_.size(); }
+
+private:
+    MappedFile file_;
+    std::unordered_map<std::string, LoadedTensor> tensors_;
+};
+
+// The reference's loader surface for this path (src/infrastructure/artifact/aeon_loader.hpp:
+// 41-166): one model directory, dense tensors by name, experts by (layer, expert), plus the
+// planned rank_slice.
+class AeonModelLoader {
+public:
+    struct Artifact {
+        std::string dense_filename{"model_dense.aeon"};
+        std::string experts_filename{"model_experts_swizzled.aeon"};
+        std::string index_filename{"model_experts_swizzled.index"};
+        uint32_t expected_dense_version{1};
+        uint32_t expected_expert_version{0};    // 0: version 2 or 3
+        size_t expected_payload_bytes{0};       // 0: any
+    };
+
+    void open_model(const std::string& model_dir) { open_model(model_dir, Artifact{}); }
+    void open_model(const std::string& model_dir, const Artifact& artifact) {
+        if (artifact.dense_filename.empty() || artifact.experts_filename.empty() || artifact.index_filename.empty())
+            throw std::invalid_argument("AeonModelLoader: artifact file names must not be empty");
+        dense_.open(model_dir + "/" + artifact.dense_filename, artifact.expected_dense_version);
+        experts_.open(model_dir + "/" + artifact.index_filename, model_dir + "/" + artifact.experts_filename,
+                      artifact.expected_expert_version, artifact.expected_payload_bytes);
+        model_dir_ = model_dir;
+    }
+
+    const std::string& model_dir() const noexcept { return model_dir_; }
+    bool has_tensor(const std::string& name) const { return dense_.has_tensor(name); }
+    const LoadedTensor& get_tensor(const std::string& name) const { return dense_.get_tensor(name); }
+    const ExpertFormatDescriptor& expert_format() const noexcept { return experts_.format(); }
+    uint32_t max_tensor_parallel() const noexcept { return experts_.format().shard_count; }
+    AeonExpertContainer::Location get_expert_location(uint32_t layer, uint32_t expert) const {
+        return experts_.get_expert_location(layer, expert);
+    }
+    const uint8_t* get_expert_data(uint32_t layer, uint32_t expert) const { return experts_.get_expert_data(layer, expert); }
+    AeonExpertContainer::Location rank_slice(uint32_t layer, uint32_t expert, uint32_t tp, uint32_t rank) const {
+        return experts_.rank_slice(layer, expert, tp, rank);
+    }
+    const AeonExpertContainer& experts() const noexcept { return experts_; }
+    const AeonDenseContainer& dense() const noexcept { return dense_; }
+
+private:
+    std::string model_dir_;
+    AeonDenseContainer dense_;
+    AeonExpertContainer experts_;
 };
 
 // ---------------------------------------------------------------------------------------------

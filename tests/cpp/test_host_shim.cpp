@@ -2,8 +2,9 @@
 // the cases of the reference's tests/test_parallel_topology.cpp:83-256 (stage-major mapping,
 // 43-layer splits, refusals, parser), the registry's reservation / lease / eviction state
 // machine with the invariant audit after every step
-// (tests/test_expert_registry_warm_state.cpp), and the expert container round trip
-// (index header + entries, the loader contract of aeon_loader.hpp:345-405).
+// (tests/test_expert_registry_warm_state.cpp), the expert container round trip
+// (index header + entries, the loader contract of aeon_loader.hpp:345-405), the shard-aware
+// version 3 of it with rank slices, and the dense container behind AeonModelLoader.
 #include "aeon_b200_host.hpp"
 
 #include <cstdio>
@@ -153,6 +154,158 @@ int main(int argc, char** argv) {
         { std::ofstream t(idx, std::ios::binary | std::ios::trunc); std::vector<char> z(64, 0); t.write(z.data(), 64); }
         check("container: bad magic refused", throws<std::runtime_error>([&] { bad.open(idx, exp, 2, bytes); }, "magic"));
         std::remove(idx.c_str()); std::remove(exp.c_str());
+    }
+    // ---- shard-aware (version 3) expert container, dense container, loader ----
+    {
+        aeon_b200_moe_config cfg = moe_config_preset("baseline");
+        cfg.hidden = 256; cfg.intermediate = 2048; cfg.experts = 32; cfg.top_k = 4;
+        const uint32_t D = 8, layers = 1;
+        const size_t H = cfg.hidden, I = cfg.intermediate, G = cfg.group_size;
+        struct Source { std::vector<uint32_t> w1p, w2p, w3p; std::vector<uint16_t> w1s, w2s, w3s; };
+        auto make_source = [&](uint32_t seed) {
+            Source s;
+            uint64_t state = 0x9E3779B97F4A7C15ull * (seed + 1);
+            auto next = [&] { state ^= state << 13; state ^= state >> 7; state ^= state << 17; return state; };
+            s.w1p.resize(I * H / 8); s.w3p.resize(I * H / 8); s.w2p.resize(H * I / 8);
+            s.w1s.resize(I * H / G); s.w3s.resize(I * H / G); s.w2s.resize(H * I / G);
+            for (auto* v : {&s.w1p, &s.w2p, &s.w3p}) for (auto& w : *v) w = static_cast<uint32_t>(next());
+            for (auto* v : {&s.w1s, &s.w2s, &s.w3s}) for (auto& w : *v) w = static_cast<uint16_t>(0x2000 + next() % 0x800);
+            return s;
+        };
+        const ExpertFormatDescriptor f3 = make_swizzled_expert_format(cfg, layers, D);
+        check("v3 format: 8 shards, shard_bytes x 8 = payload, version 3",
+              f3.version == 3 && f3.shard_count == D && f3.shard_bytes * D == f3.payload_bytes);
+        std::vector<std::vector<uint8_t>> payloads(cfg.experts, std::vector<uint8_t>(f3.payload_bytes));
+        std::vector<const uint8_t*> ptrs;
+        for (int e = 0; e < cfg.experts; ++e) {
+            const Source s = make_source(e);
+            check_status(aeon_b200_pack_expert_shards(&cfg, D, s.w1p.data(), s.w1s.data(), s.w2p.data(), s.w2s.data(),
+                                                      s.w3p.data(), s.w3s.data(), payloads[e].data()));
+            ptrs.push_back(payloads[e].data());
+        }
+        const std::string dir = tmp;
+        const std::string idx = dir + "/model_experts_swizzled.index", exp = dir + "/model_experts_swizzled.aeon";
+        AeonExpertContainer::write(idx, exp, 3, layers, cfg.experts, f3.payload_bytes, ptrs, D);
+        AeonExpertContainer c;
+        c.open(idx, exp, 0, 0);
+        check("v3 container: header fields read back", c.format().version == 3 && c.format().shard_count == D &&
+                                                          c.format().shard_bytes == f3.shard_bytes);
+        bool tiles = true;
+        for (uint32_t tp : {1u, 2u, 4u, 8u}) {
+            const auto whole = c.get_expert_location(0, 5);
+            uint64_t cursor = whole.offset;
+            for (uint32_t r = 0; r < tp; ++r) {
+                const auto sl = c.rank_slice(0, 5, tp, r);
+                tiles &= sl.offset == cursor && sl.offset % 4096 == 0 && sl.length == whole.length / tp;
+                cursor += sl.length;
+            }
+            tiles &= cursor == whole.offset + whole.length;
+        }
+        check("rank slices: contiguous, sector-aligned, disjoint, cover the payload", tiles);
+        check("rank_slice: tp that does not divide the shard count refused",
+              throws<std::invalid_argument>([&] { c.rank_slice(0, 5, 3, 0); }, "does not divide"));
+        check("rank_slice: rank out of range", throws<std::out_of_range>([&] { c.rank_slice(0, 5, 2, 2); }));
+        {
+            // rank 1 of tp 2: its merged payload equals the payload packed from its half of the source
+            const Source s = make_source(5);
+            aeon_b200_moe_config half = cfg; half.intermediate = cfg.intermediate / 2;
+            const size_t Ih = half.intermediate;
+            Source h;
+            h.w1p.assign(s.w1p.begin() + Ih * H / 8, s.w1p.end()); h.w1s.assign(s.w1s.begin() + Ih * H / G, s.w1s.end());
+            h.w3p.assign(s.w3p.begin() + Ih * H / 8, s.w3p.end()); h.w3s.assign(s.w3s.begin() + Ih * H / G, s.w3s.end());
+            for (size_t r = 0; r < H; ++r) {
+                h.w2p.insert(h.w2p.end(), s.w2p.begin() + r * I / 8 + Ih / 8, s.w2p.begin() + (r + 1) * I / 8);
+                h.w2s.insert(h.w2s.end(), s.w2s.begin() + r * I / G + Ih / G, s.w2s.begin() + (r + 1) * I / G);
+            }
+            aeon_b200_expert_layout lay{};
+            check_status(aeon_b200_expert_layout_of(&half, &lay));
+            std::vector<uint8_t> direct(lay.payload_bytes);
+            check_status(aeon_b200_pack_expert_shards(&half, 1, h.w1p.data(), h.w1s.data(), h.w2p.data(), h.w2s.data(),
+                                                      h.w3p.data(), h.w3s.data(), direct.data()));
+            check("read_rank_payload(tp 2, rank 1) = payload packed from that half of the source",
+                  c.read_rank_payload(cfg, 0, 5, 2, 1) == direct);
+        }
+        AeonExpertContainer v2only;
+        check("v3 index refused when version 2 is demanded",
+              throws<std::runtime_error>([&] { v2only.open(idx, exp, 2, 0); }, "version"));
+        check("write: shards need version 3",
+              throws<std::invalid_argument>([&] { AeonExpertContainer::write(idx + ".x", exp + ".x", 2, layers, cfg.experts, f3.payload_bytes, ptrs, D); }));
+        std::remove((idx + ".x").c_str()); std::remove((exp + ".x").c_str());
+
+        // dense container written by hand: header, JSON directory, 4 KiB-aligned payload
+        const std::string dense_path = dir + "/model_dense.aeon";
+        std::vector<uint16_t> gate(static_cast<size_t>(cfg.experts) * H);
+        for (size_t i = 0; i < gate.size(); ++i) gate[i] = static_cast<uint16_t>(i * 7 + 1);
+        std::vector<float> bias(cfg.experts);
+        for (size_t i = 0; i < bias.size(); ++i) bias[i] = 0.25f * static_cast<float>(i);
+        auto write_dense = [&](const std::string& directory, uint32_t version, uint32_t count) {
+            std::ofstream out(dense_path, std::ios::binary | std::ios::trunc);
+            const uint64_t dir_len = directory.size();
+            out.write("AEON_DENSE\0\0", 12);
+            out.write(reinterpret_cast<const char*>(&version), 4);
+            out.write(reinterpret_cast<const char*>(&count), 4);
+            out.write(reinterpret_cast<const char*>(&dir_len), 8);
+            out.write(directory.data(), static_cast<std::streamsize>(directory.size()));
+            const size_t pre = 28 + directory.size();
+            std::vector<char> pad((4096 - pre % 4096) % 4096, 0);
+            out.write(pad.data(), static_cast<std::streamsize>(pad.size()));
+            out.write(reinterpret_cast<const char*>(gate.data()), static_cast<std::streamsize>(gate.size() * 2));
+            out.write(reinterpret_cast<const char*>(bias.data()), static_cast<std::streamsize>(bias.size() * 4));
+        };
+        const std::string directory =
+            "[\n  {\"name\": \"layers.0.ffn.gate.weight\", \"offset\": 0, \"size\": " + std::to_string(gate.size() * 2) +
+            ", \"dtype\": \"BF16\", \"shape\": [" + std::to_string(cfg.experts) + ", " + std::to_string(H) + "]},\n"
+            "  {\"name\": \"layers.0.ffn.gate.bias\", \"offset\": " + std::to_string(gate.size() * 2) +
+            ", \"size\": " + std::to_string(bias.size() * 4) + ", \"dtype\": \"F32\", \"shape\": [" +
+            std::to_string(cfg.experts) + "]}\n]";
+        write_dense(directory, 1, 2);
+        AeonModelLoader loader;
+        loader.open_model(dir);
+        const LoadedTensor& g = loader.get_tensor("layers.0.ffn.gate.weight");
+        const LoadedTensor& b = loader.get_tensor("layers.0.ffn.gate.bias");
+        check("loader: dense tensors by name (bytes, dtype, shape)",
+              g.byte_size == static_cast<int64_t>(gate.size() * 2) && g.dtype == "BF16" && g.shape.size() == 2 &&
+                  g.shape[0] == cfg.experts && std::memcmp(g.data, gate.data(), gate.size() * 2) == 0 &&
+                  b.dtype == "F32" && std::memcmp(b.data, bias.data(), bias.size() * 4) == 0 &&
+                  (reinterpret_cast<uintptr_t>(g.data) - reinterpret_cast<uintptr_t>(loader.dense().get_tensor("layers.0.ffn.gate.weight").data)) == 0);
+        check("loader: experts, max tensor-parallel degree and rank slices through one object",
+              loader.max_tensor_parallel() == D && loader.expert_format().payload_bytes == f3.payload_bytes &&
+                  std::memcmp(loader.get_expert_data(0, 31), payloads[31].data(), f3.payload_bytes) == 0 &&
+                  loader.rank_slice(0, 31, 8, 7).offset == loader.get_expert_location(0, 31).offset + 7 * f3.shard_bytes);
+        check("loader: missing tensor", !loader.has_tensor("layers.0.ffn.gate.tid2eid") &&
+                                             throws<std::runtime_error>([&] { loader.get_tensor("layers.0.ffn.gate.tid2eid"); }, "Missing"));
+        AeonDenseContainer bad;
+        write_dense(directory, 2, 2);
+        check("dense: version mismatch refused", throws<std::runtime_error>([&] { bad.open(dense_path); }, "version"));
+        write_dense(directory, 1, 3);
+        check("dense: count mismatch refused", throws<std::runtime_error>([&] { bad.open(dense_path); }, "count"));
+        write_dense("[{\"name\": \"a\", \"offset\": 0, \"size\": 99999999, \"dtype\": \"U8\", \"shape\": [1]}]", 1, 1);
+        check("dense: range beyond the payload refused", throws<std::runtime_error>([&] { bad.open(dense_path); }, "exceeds payload"));
+        write_dense("[{\"name\": \"a\", \"offset\": 0, \"size\": 8, \"dtype\": \"U8\"}]", 1, 1);
+        check("dense: entry without a shape refused", throws<std::runtime_error>([&] { bad.open(dense_path); }, "Malformed"));
+        write_dense(directory + "x", 1, 2);
+        check("dense: text after the directory refused", throws<std::runtime_error>([&] { bad.open(dense_path); }, "Malformed"));
+        std::remove(idx.c_str()); std::remove(exp.c_str()); std::remove(dense_path.c_str());
+    }
+    // ---- a model directory written by the Python converter (argv[2]), read by this loader ----
+    if (argc > 2) {
+        const std::string model_dir = argv[2];
+        std::ifstream expect_file(model_dir + "/expected.txt");
+        uint64_t shard_count = 0, payload_bytes = 0, expert_hash = 0, gate_hash = 0, slice_offset = 0;
+        expect_file >> shard_count >> payload_bytes >> expert_hash >> gate_hash >> slice_offset;
+        auto fnv = [](const uint8_t* p, size_t n) {
+            uint64_t h = 0xcbf29ce484222325ull;
+            for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 0x100000001b3ull; }
+            return h;
+        };
+        AeonModelLoader loader;
+        loader.open_model(model_dir);
+        check("python-written artifact: header fields", loader.max_tensor_parallel() == shard_count &&
+                                                          loader.expert_format().payload_bytes == payload_bytes);
+        check("python-written artifact: expert (0,3) bytes", fnv(loader.get_expert_data(0, 3), payload_bytes) == expert_hash);
+        const LoadedTensor& g = loader.get_tensor("layers.0.ffn.gate.weight");
+        check("python-written artifact: gate tensor bytes", fnv(g.data, static_cast<size_t>(g.byte_size)) == gate_hash);
+        check("python-written artifact: rank slice (tp 2, rank 1) offset", loader.rank_slice(0, 3, 2, 1).offset == slice_offset);
     }
     // ---- format / presets through the C ABI ----
     {

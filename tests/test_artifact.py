@@ -1,0 +1,288 @@
+"""CPU checks of the artifact files either side of the path: the expert container in the
+reference's version 2 and in the shard-aware version 3 it plans
+(plans-and-docs/execution/active/MULTI_GPU_EXECUTION_PLAN.md:151-181 — "rank slices are
+contiguous, 4 KiB-aligned and disjoint, and together cover the payload exactly; v2 still loads
+as D = 1; per-shard unswizzle round-trip is bit-exact and reassembling the shards reproduces the
+source tensor exactly"), and the dense container that carries the gate and the shared expert."""
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import aeon_b200
+from aeon_b200 import artifact
+
+
+def small_cfg(**changes):
+    # the smallest shapes the configuration rules admit with 8 intermediate shards
+    return aeon_b200.preset("baseline").copy(hidden=256, intermediate=2048, experts=32, top_k=4, **changes)
+
+
+def source_tensors(cfg, layer, expert):
+    """Seeded checkpoint-order tensors (words of eight nibbles, fp16 scale bits)."""
+    rng = np.random.default_rng([layer, expert, cfg.group_size])
+    out = []
+    for shape, dtype in zip(aeon_b200.source_shapes(cfg), (np.uint32, np.uint16) * 3):
+        if dtype == np.uint32:
+            out.append(rng.integers(0, 2 ** 32, size=shape, dtype=np.uint64).astype(np.uint32))
+        else:
+            out.append(np.abs(rng.standard_normal(shape) * 0.02 + 1e-4).astype(np.float16).view(np.uint16))
+    return out
+
+
+def slice_source(cfg, src, first, count):
+    G = cfg.group_size
+    rows = slice(first, first + count)
+    return [src[0][rows], src[1][rows], src[2][:, first // 8:(first + count) // 8],
+            src[3][:, first // G:(first + count) // G], src[4][rows], src[5][rows]]
+
+
+@pytest.mark.parametrize("group", [32, 128])
+def test_one_shard_is_the_v2_payload_and_shards_round_trip(group, oracle):
+    cfg = small_cfg(group_size=group)
+    src = source_tensors(cfg, 0, 0)
+    lay = aeon_b200.expert_layout(cfg)
+    whole = aeon_b200.pack_expert_shards(cfg, 1, src)
+    assert whole.size == lay.payload_bytes
+    # region by region the same bytes as the per-matrix swizzle, and as the oracle's own
+    # restatement of the reference swizzle
+    la = oracle.layout_args(cfg)
+    want = np.zeros(lay.payload_bytes, dtype=np.uint8)
+    for kind, (p, s) in enumerate(((src[0], src[1]), (src[2], src[3]), (src[4], src[5]))):
+        oracle.swizzle_from_source(la, kind, p, s, want)
+    assert np.array_equal(whole, want)
+    for shards in (2, 4, 8):
+        sharded = aeon_b200.pack_expert_shards(cfg, shards, src)
+        assert sharded.size == shards * aeon_b200.expert_shard_bytes(cfg, shards)
+        back = aeon_b200.unpack_expert_shards(cfg, shards, sharded)
+        assert all(np.array_equal(a, b) for a, b in zip(src, back))
+        # W1/W3 shards are row-block ranges of the whole matrix: their packed regions,
+        # concatenated, are the whole matrix's packed region
+        unit = aeon_b200.expert_layout(cfg.copy(intermediate=cfg.intermediate // shards))
+        sb = aeon_b200.expert_shard_bytes(cfg, shards)
+        for name in ("w1", "w3"):
+            off = getattr(unit, f"{name}_packed_offset")
+            cat = np.concatenate([sharded[s * sb + off:s * sb + off + unit.w13_packed_bytes] for s in range(shards)])
+            woff = getattr(lay, f"{name}_packed_offset")
+            assert np.array_equal(cat, whole[woff:woff + lay.w13_packed_bytes])
+
+
+def test_shard_is_decoded_by_the_oracle_as_the_slice_of_the_whole(oracle):
+    """The oracle's independent swizzled reader, pointed at one shard, sees exactly the rows
+    (W1, W3) and columns (W2) of the whole expert; the shards' FFN partials sum to the whole
+    expert's output (the shard gates of tests/test_expert_shard_equivalence.cpp:403-517)."""
+    cfg = small_cfg()
+    shards = 4
+    src = source_tensors(cfg, 1, 5)
+    whole = aeon_b200.pack_expert_shards(cfg, 1, src)
+    sharded = aeon_b200.pack_expert_shards(cfg, shards, src)
+    cfg_s = cfg.copy(intermediate=cfg.intermediate // shards)
+    la, la_s = oracle.layout_args(cfg), oracle.layout_args(cfg_s)
+    sb = aeon_b200.expert_shard_bytes(cfg, shards)
+    Is = cfg_s.intermediate
+    w = [oracle.decode_matrix(la, kind, whole) for kind in range(3)]      # W1, W2, W3
+    x = np.random.default_rng(3).standard_normal(cfg.hidden)
+    total = np.zeros(cfg.hidden)
+    for s in range(shards):
+        piece = np.ascontiguousarray(sharded[s * sb:(s + 1) * sb])
+        assert np.array_equal(oracle.decode_matrix(la_s, 0, piece), w[0][s * Is:(s + 1) * Is])
+        assert np.array_equal(oracle.decode_matrix(la_s, 2, piece), w[2][s * Is:(s + 1) * Is])
+        assert np.array_equal(oracle.decode_matrix(la_s, 1, piece), w[1][:, s * Is:(s + 1) * Is])
+        total += oracle.expert_ffn(la_s, piece, x)
+    want = oracle.expert_ffn(la, whole, x)
+    stats = oracle.compare(want, total)
+    assert stats["rel_l2"] < 1e-12
+
+
+def test_rank_slices_are_contiguous_aligned_disjoint_and_cover_the_payload():
+    cfg = small_cfg()
+    for shards in (1, 2, 4, 8):
+        sb = aeon_b200.expert_shard_bytes(cfg, shards)
+        assert sb % 4096 == 0
+        for tp in (1, 2, 4, 8):
+            if shards % tp:
+                with pytest.raises(aeon_b200.AeonError) as e:
+                    aeon_b200.expert_rank_slice(cfg, shards, tp, 0)
+                assert e.value.status == 1 and "does not divide" in str(e.value)
+                continue
+            cursor = 0
+            for rank in range(tp):
+                off, length = aeon_b200.expert_rank_slice(cfg, shards, tp, rank)
+                assert off == cursor and off % 4096 == 0 and length == shards * sb // tp
+                cursor += length
+            assert cursor == shards * sb
+            with pytest.raises(aeon_b200.AeonError) as e:
+                aeon_b200.expert_rank_slice(cfg, shards, tp, tp)
+            assert e.value.status == 4
+    with pytest.raises(aeon_b200.AeonError):
+        aeon_b200.expert_shard_bytes(cfg, 3)            # 2048 / 3 is not whole
+    with pytest.raises(aeon_b200.AeonError):
+        aeon_b200.expert_shard_bytes(cfg, 16)           # shards of 128 columns are too narrow
+
+
+def test_sharding_adds_no_padding_at_the_model_shapes():
+    """Each region of a shard stays a multiple of 4 KiB at the reference's and the benchmark's
+    shapes, so a version-3 payload is exactly as large as the version-2 one."""
+    for name, want in (("ref_dsv4", 14155776), ("baseline", 22708224)):
+        cfg = aeon_b200.preset(name)
+        for shards in (1, 2, 4, 8):
+            assert shards * aeon_b200.expert_shard_bytes(cfg, shards) == want
+
+
+def test_rank_slice_merges_into_the_payload_of_the_rank():
+    cfg = small_cfg()
+    src = source_tensors(cfg, 0, 9)
+    sharded = aeon_b200.pack_expert_shards(cfg, 8, src)
+    for tp in (1, 2, 4, 8):
+        cfg_r = cfg.copy(intermediate=cfg.intermediate // tp)
+        for rank in range(tp):
+            off, length = aeon_b200.expert_rank_slice(cfg, 8, tp, rank)
+            merged = aeon_b200.merge_expert_shards(cfg_r, 8 // tp, sharded[off:off + length])
+            direct = aeon_b200.pack_expert_shards(
+                cfg_r, 1, slice_source(cfg, src, rank * cfg_r.intermediate, cfg_r.intermediate))
+            assert np.array_equal(merged, direct), (tp, rank)
+
+
+@pytest.mark.parametrize("max_tp", [1, 8])
+def test_expert_container_files(tmp_path, max_tp):
+    cfg = small_cfg()
+    layers = 2
+    source_of = lambda layer, expert: source_tensors(cfg, layer, expert)
+    fmt = artifact.write_expert_artifact(str(tmp_path), cfg, layers, source_of, max_tensor_parallel=max_tp)
+    assert fmt.version == (3 if max_tp > 1 else 2)
+    # header bytes as the reference packs them ("<12sIIIQ", scripts/convert_safetensors_to_aeon.py:310)
+    raw = open(tmp_path / artifact.INDEX_FILENAME, "rb").read()
+    magic, version, n_layers, n_experts, payload = struct.unpack_from("<12sIIIQ", raw, 0)
+    assert (magic, version, n_layers, n_experts, payload) == (
+        b"AEON_EXPERTS", fmt.version, layers, cfg.experts, max_tp * aeon_b200.expert_shard_bytes(cfg, max_tp))
+    assert len(raw) == (32 if max_tp == 1 else 48) + 16 * layers * cfg.experts
+    manifest = json.load(open(tmp_path / artifact.MANIFEST_FILENAME))
+    assert manifest["max_tensor_parallel"] == max_tp and manifest["artifact"]["expert_shard_count"] == max_tp
+
+    art = artifact.ExpertArtifact(str(tmp_path), expected_payload_bytes=payload)
+    assert (art.format.shard_count, art.format.shard_bytes) == (max_tp, payload // max_tp)
+    off, length = art.expert_location(1, 7)
+    assert off == (cfg.experts + 7) * payload and length == payload
+    want = aeon_b200.pack_expert_shards(cfg, max_tp, source_of(1, 7))
+    assert np.array_equal(np.asarray(art.expert_data(1, 7)), want)
+    assert artifact.verify_conversion(str(tmp_path), cfg, source_of, sample=[(0, 0), (1, 31)]) == 2
+    with pytest.raises(IndexError):
+        art.expert_location(2, 0)
+    with pytest.raises(ValueError):
+        artifact.ExpertArtifact(str(tmp_path), expected_payload_bytes=payload + 4096)
+
+    # rank slices of one expert tile the expert's byte range; what a rank uploads equals the
+    # payload built directly from its slice of the source
+    for tp in (1, 2, 4, 8):
+        if max_tp % tp:
+            with pytest.raises(ValueError):
+                art.rank_slice(0, 3, tp, 0)
+            continue
+        base, _ = art.expert_location(0, 3)
+        cursor = base
+        for rank in range(tp):
+            o, n = art.rank_slice(0, 3, tp, rank)
+            assert o == cursor and o % 4096 == 0
+            cursor += n
+        assert cursor == base + payload
+        cfg_r = cfg.copy(intermediate=cfg.intermediate // tp)
+        got = art.rank_payload(cfg, 0, 3, tp, tp - 1)
+        direct = aeon_b200.pack_expert_shards(
+            cfg_r, 1, slice_source(cfg, source_of(0, 3), (tp - 1) * cfg_r.intermediate, cfg_r.intermediate))
+        assert np.array_equal(got, direct)
+
+
+def test_reshard_v2_artifact_into_v3(tmp_path):
+    cfg = small_cfg()
+    source_of = lambda layer, expert: source_tensors(cfg, layer, expert)
+    v2, v3 = str(tmp_path / "v2"), str(tmp_path / "v3")
+    artifact.write_expert_artifact(v2, cfg, 1, source_of, max_tensor_parallel=1)
+    fmt = artifact.reshard_expert_artifact(v2, v3, cfg, 4)
+    assert (fmt.version, fmt.shard_count) == (3, 4)
+    assert artifact.verify_conversion(v3, cfg, source_of, sample=[(0, 0), (0, 17)]) == 2
+    with pytest.raises(ValueError, match="shapes do not match"):
+        artifact.reshard_expert_artifact(v2, str(tmp_path / "bad"), cfg.copy(hidden=512), 4)
+
+
+def test_reshard_command_line_round_trip(tmp_path, monkeypatch):
+    cfg = small_cfg()
+    source_of = lambda layer, expert: source_tensors(cfg, layer, expert)
+    v2, v3, again = str(tmp_path / "v2"), str(tmp_path / "v3"), str(tmp_path / "again")
+    artifact.write_expert_artifact(v2, cfg, 1, source_of, max_tensor_parallel=1)
+    monkeypatch.setattr(aeon_b200, "preset", lambda name: cfg)
+    assert artifact._main([v2, v3, "--max-tensor-parallel", "8"]) == 0
+    assert artifact._main([v3, again, "--max-tensor-parallel", "1"]) == 0
+    for name in (artifact.INDEX_FILENAME, artifact.EXPERTS_FILENAME):
+        assert open(os.path.join(v2, name), "rb").read() == open(os.path.join(again, name), "rb").read()
+
+
+def test_corrupt_or_truncated_expert_container_is_refused(tmp_path):
+    cfg = small_cfg()
+    source_of = lambda layer, expert: source_tensors(cfg, layer, expert)
+    artifact.write_expert_artifact(str(tmp_path), cfg, 1, source_of, max_tensor_parallel=2)
+    index = tmp_path / artifact.INDEX_FILENAME
+    good = index.read_bytes()
+    # flipped payload byte: the round-trip verification notices
+    data = tmp_path / artifact.EXPERTS_FILENAME
+    blob = bytearray(data.read_bytes())
+    blob[12345] ^= 0x10
+    data.write_bytes(bytes(blob))
+    with pytest.raises(ValueError, match="does not round-trip"):
+        artifact.verify_conversion(str(tmp_path), cfg, source_of, sample=[(0, 0)])
+    for bad, message in (
+        (b"AEON_EXPERTZ" + good[12:], "magic"),
+        (good[:40], "too small"),
+        (good[:-8], "incomplete"),
+        (good[:12] + struct.pack("<I", 4) + good[16:], "unsupported version"),
+        (good[:32] + struct.pack("<IIQ", 3, 0, struct.unpack_from("<Q", good, 40)[0]) + good[48:], "shard_count"),
+        (good[:48] + struct.pack("<QQ", 100, struct.unpack_from("<Q", good, 56)[0]) + good[64:], "invalid payload entry"),
+    ):
+        index.write_bytes(bad)
+        with pytest.raises(ValueError, match=message):
+            artifact.ExpertArtifact(str(tmp_path))
+    index.write_bytes(good)
+    data.write_bytes(bytes(blob[:-4096]))
+    with pytest.raises(ValueError, match="outside the experts file"):
+        artifact.ExpertArtifact(str(tmp_path))
+
+
+def test_dense_container_round_trip_and_refusals(tmp_path):
+    cfg = small_cfg()
+    rng = np.random.default_rng(0)
+    names = artifact.moe_layer_tensor_names(3)
+    tensors = [
+        (names["gate"], "BF16", rng.integers(0, 2 ** 16, size=(cfg.experts, cfg.hidden), dtype=np.uint16)),
+        (names["gate_bias"], "F32", rng.standard_normal(cfg.experts).astype(np.float32)),
+        (names["shared_w1"], "BF16", rng.integers(0, 2 ** 16, size=(cfg.intermediate, cfg.hidden), dtype=np.uint16)),
+        (names["shared_w2"], "BF16", rng.integers(0, 2 ** 16, size=(cfg.hidden, cfg.intermediate), dtype=np.uint16)),
+        (names["shared_w3"], "BF16", rng.integers(0, 2 ** 16, size=(cfg.intermediate, cfg.hidden), dtype=np.uint16)),
+        (artifact.moe_layer_tensor_names(0, hash_layer=True)["tid2eid"], "I64",
+         rng.integers(0, cfg.experts, size=(64, cfg.top_k), dtype=np.int64)),
+    ]
+    path = str(tmp_path / artifact.DENSE_FILENAME)
+    artifact.write_dense_container(path, tensors)
+    raw = open(path, "rb").read()
+    magic, version, count, dir_len = struct.unpack_from("<12sIIQ", raw, 0)
+    assert (magic, version, count) == (b"AEON_DENSE\x00\x00", 1, len(tensors))
+    data_start = (28 + dir_len + 4095) // 4096 * 4096
+    assert raw[data_start:data_start + 8] == tensors[0][2].tobytes()[:8]
+    dense = artifact.DenseContainer(path)
+    assert set(dense.names()) == {t[0] for t in tensors}
+    for name, dtype, array in tensors:
+        assert dense.has_tensor(name) and dense.dtype_of(name) == dtype
+        assert np.array_equal(dense.get_tensor(name), array)
+    assert not dense.has_tensor("layers.3.ffn.gate.missing")
+    with pytest.raises(KeyError):
+        dense.get_tensor("layers.3.ffn.gate.missing")
+    for bad, message in (
+        (b"AEON_DENSF\x00\x00" + raw[12:], "magic"),
+        (raw[:12] + struct.pack("<I", 7) + raw[16:], "version"),
+        (raw[:16] + struct.pack("<I", count + 1) + raw[20:], "count"),
+        (raw[:20] + struct.pack("<Q", len(raw)) + raw[28:], "Directory length"),
+        (raw[:data_start + 100], "exceeds payload"),
+    ):
+        open(path, "wb").write(bad)
+        with pytest.raises(ValueError, match=message):
+            artifact.DenseContainer(path)
