@@ -41,9 +41,9 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tc5.cuh"
+#include "tensor_map.cuh"
 
 #include <algorithm>
-#include <mutex>
 
 namespace aeon_b200 {
 
@@ -433,42 +433,6 @@ __global__ void moe_accumulate_prefill_kernel(float* __restrict__ accum, int64_t
     }
 }
 
-// ---- host side --------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                   CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    });
-    if (!fn) throw StatusError(AEON_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    return fn;
-}
-
-// Row-major fp16 matrix [rows, cols]; box = 64 columns (128 B) x 64 rows, 128-byte swizzle.
-CUtensorMap make_act_map(const void* base, uint64_t rows, uint64_t cols) {
-    CUtensorMap map;
-    const cuuint64_t gdim[2] = {cols, rows};
-    const cuuint64_t gstride[1] = {cols * 2};
-    const cuuint32_t box[2] = {kTileK, 64};
-    const cuuint32_t estride[2] = {1, 1};
-    const CUresult rc = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim,
-                                       gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS)
-        throw StatusError(AEON_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(rc));
-    return map;
-}
-
 }  // namespace
 
 struct PrefillScratch {
@@ -521,8 +485,8 @@ static PrefillScratch* ensure_scratch(aeon_b200_ctx* ctx, int tokens) {
     alloc(s->entries, cfg.experts + draws / 8 + 1);
     AEON_CUDA_CHECK(cudaMemset(s->xg, 0, (draws + 64) * cfg.hidden * sizeof(__half)));
     AEON_CUDA_CHECK(cudaMemset(s->hidden, 0, (draws + 64) * cfg.intermediate * sizeof(__half)));
-    s->x_map = make_act_map(s->xg, draws + 64, cfg.hidden);
-    s->h_map = make_act_map(s->hidden, draws + 64, cfg.intermediate);
+    s->x_map = make_rowmajor16_map(s->xg, draws + 64, cfg.hidden, cfg.hidden);
+    s->h_map = make_rowmajor16_map(s->hidden, draws + 64, cfg.intermediate, cfg.intermediate);
     s->max_tokens = tokens;
     return s;
 }

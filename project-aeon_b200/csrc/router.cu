@@ -43,7 +43,15 @@ __device__ __forceinline__ void widen8(const uint4& v, float (&out)[8]) {
     }
 }
 
-template <bool kBf16>
+// One warp per expert, kTok tokens per CTA pass. A lane walks its vectors (lane, lane + 32, ...)
+// in ascending order in batches of kLogitBatch: the batch's gate vectors are all loaded
+// before the first is used, then each token's activation vectors likewise, so a warp keeps
+// kLogitBatch 16-byte loads in flight instead of one (there is no branch between a load and the
+// next: a token index past the end is clamped to the last token and its result dropped).
+// The order of the fused multiply-adds into each accumulator is the defined one.
+constexpr int kLogitBatch = 8;
+
+template <bool kBf16, int kTok>
 __global__ void __launch_bounds__(kLogitWarps * 32)
 router_logits_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
                      const uint16_t* __restrict__ gate, int tokens, int experts, int hidden,
@@ -51,36 +59,49 @@ router_logits_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int e = blockIdx.x * kLogitWarps + warp;
-    const int t0 = blockIdx.y * kLogitTokens;
+    const int t0 = blockIdx.y * kTok;
     if (e >= experts) return;
-    const int nt = min(kLogitTokens, tokens - t0);
 
-    float acc[kLogitTokens];
+    float acc[kTok];
 #pragma unroll
-    for (int j = 0; j < kLogitTokens; ++j) acc[j] = 0.f;
+    for (int j = 0; j < kTok; ++j) acc[j] = 0.f;
 
     const uint4* grow = reinterpret_cast<const uint4*>(gate + static_cast<size_t>(e) * hidden);
-    const int vectors = hidden / 8;
-#pragma unroll 8
-    for (int v = lane; v < vectors; v += 32) {
-        float gv[8];
-        widen8<kBf16>(__ldg(grow + v), gv);
+    const int vectors = hidden / 8;      // a multiple of 32: a batch slot is live for the whole warp or not at all
+    for (int v0 = lane; v0 < vectors; v0 += 32 * kLogitBatch) {
+        uint4 gq[kLogitBatch];
 #pragma unroll
-        for (int j = 0; j < kLogitTokens; ++j) {
-            if (j < nt) {
-                float xv[8];
-                widen8<kBf16>(__ldg(reinterpret_cast<const uint4*>(
-                                        x + static_cast<size_t>(t0 + j) * x_stride) + v), xv);
+        for (int u = 0; u < kLogitBatch; ++u) {
+            const int v = v0 + 32 * u;
+            gq[u] = v < vectors ? __ldg(grow + v) : make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[j] = fmaf(gv[i], xv[i], acc[j]);
+        for (int j = 0; j < kTok; ++j) {
+            const uint4* xrow = reinterpret_cast<const uint4*>(
+                x + static_cast<size_t>(min(t0 + j, tokens - 1)) * x_stride);
+            uint4 xq[kLogitBatch];
+#pragma unroll
+            for (int u = 0; u < kLogitBatch; ++u) {
+                const int v = v0 + 32 * u;
+                xq[u] = v < vectors ? __ldg(xrow + v) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < kLogitBatch; ++u) {
+                if (v0 + 32 * u < vectors) {
+                    float gv[8], xv[8];
+                    widen8<kBf16>(gq[u], gv);
+                    widen8<kBf16>(xq[u], xv);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[j] = fmaf(gv[i], xv[i], acc[j]);
+                }
             }
         }
     }
 #pragma unroll
-    for (int j = 0; j < kLogitTokens; ++j) {
+    for (int j = 0; j < kTok; ++j) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc[j] += __shfl_xor_sync(0xFFFFFFFFu, acc[j], off);
-        if (lane == 0 && j < nt) logits[static_cast<size_t>(t0 + j) * experts + e] = acc[j];
+        if (lane == 0 && t0 + j < tokens) logits[static_cast<size_t>(t0 + j) * experts + e] = acc[j];
     }
 }
 
@@ -155,6 +176,30 @@ router_select_kernel(const float* __restrict__ logits, const float* __restrict__
     }
 }
 
+template <bool kBf16>
+void launch_logits_dtype(const aeon_b200_moe_config& cfg, const void* x, int64_t x_stride, const void* gate,
+                         int tokens, float* logits, cudaStream_t stream) {
+    const int expert_ctas = (cfg.experts + kLogitWarps - 1) / kLogitWarps;
+    const uint16_t* xs = static_cast<const uint16_t*>(x);
+    const uint16_t* gs = static_cast<const uint16_t*>(gate);
+    if (tokens < kLogitTokens) {
+        // one token per CTA pass: no clamped duplicates at the smallest batches
+        router_logits_kernel<kBf16, 1><<<dim3(expert_ctas, tokens), kLogitWarps * 32, 0, stream>>>(
+            xs, x_stride, gs, tokens, cfg.experts, cfg.hidden, logits);
+    } else {
+        router_logits_kernel<kBf16, kLogitTokens>
+            <<<dim3(expert_ctas, (tokens + kLogitTokens - 1) / kLogitTokens), kLogitWarps * 32, 0, stream>>>(
+                xs, x_stride, gs, tokens, cfg.experts, cfg.hidden, logits);
+    }
+    AEON_CUDA_CHECK(cudaGetLastError());
+}
+
+void launch_logits(const aeon_b200_moe_config& cfg, const void* x, int64_t x_stride, const void* gate,
+                   int tokens, float* logits, cudaStream_t stream) {
+    if (cfg.act_dtype == AEON_B200_BF16) launch_logits_dtype<true>(cfg, x, x_stride, gate, tokens, logits, stream);
+    else launch_logits_dtype<false>(cfg, x, x_stride, gate, tokens, logits, stream);
+}
+
 }  // namespace
 
 void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const void* gate,
@@ -171,18 +216,7 @@ void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const vo
     require(cfg.top_k <= 32, "aeon_b200_router_topk: top_k above 32 is not supported");
     float* logits = logits_out != nullptr ? logits_out : ctx->d_logits;
 
-    const dim3 grid((cfg.experts + kLogitWarps - 1) / kLogitWarps,
-                    (tokens + kLogitTokens - 1) / kLogitTokens);
-    if (cfg.act_dtype == AEON_B200_BF16) {
-        router_logits_kernel<true><<<grid, kLogitWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
-            cfg.experts, cfg.hidden, logits);
-    } else {
-        router_logits_kernel<false><<<grid, kLogitWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
-            cfg.experts, cfg.hidden, logits);
-    }
-    AEON_CUDA_CHECK(cudaGetLastError());
+    launch_logits(cfg, x, x_stride, gate, tokens, logits, stream);
     const size_t smem = static_cast<size_t>(kSelectWarps) * cfg.experts * sizeof(float);
     router_select_kernel<<<(tokens + kSelectWarps - 1) / kSelectWarps, kSelectWarps * 32, smem, stream>>>(
         logits, bias, hash_table, token_ids, tokens, cfg.experts, cfg.top_k, cfg.score_fn,
@@ -242,18 +276,7 @@ void launch_router_noalloc(const aeon_b200_moe_config& cfg, const void* x, int64
             "aeon_b200_router_topk_noalloc: x_stride must be >= hidden and a multiple of 8");
     float* logits = noalloc_scratch_for_current_device();
 
-    const dim3 grid((cfg.experts + kLogitWarps - 1) / kLogitWarps,
-                    (tokens + kLogitTokens - 1) / kLogitTokens);
-    if (cfg.act_dtype == AEON_B200_BF16) {
-        router_logits_kernel<true><<<grid, kLogitWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
-            cfg.experts, cfg.hidden, logits);
-    } else {
-        router_logits_kernel<false><<<grid, kLogitWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(x), x_stride, static_cast<const uint16_t*>(gate), tokens,
-            cfg.experts, cfg.hidden, logits);
-    }
-    AEON_CUDA_CHECK(cudaGetLastError());
+    launch_logits(cfg, x, x_stride, gate, tokens, logits, stream);
     const size_t smem = static_cast<size_t>(kSelectWarps) * cfg.experts * sizeof(float);
     router_select_kernel<<<(tokens + kSelectWarps - 1) / kSelectWarps, kSelectWarps * 32, smem, stream>>>(
         logits, bias, nullptr, nullptr, tokens, cfg.experts, cfg.top_k, cfg.score_fn, cfg.renormalize,

@@ -10,7 +10,10 @@
 // Both phases stream the row-major weights once with 128-bit loads straight into MMA
 // operand registers (weight rows are the M operand, tokens the N operand; the four lanes of
 // a row read 64 contiguous bytes). A CTA owns 16 weight rows (of W1 and W3 together in
-// phase 1) and splits K over its 16 warps; the partial sums meet in shared memory.
+// phase 1) and a group of 8, 16 or 32 tokens, and splits K over its warps; the partial sums
+// meet in shared memory. Every token group streams the weights again (from L2 after the first),
+// so larger batches use the 32-token form: 8 warps x 4 MMA N tiles, which halves that traffic
+// against the 16-token form at the same shared-memory footprint.
 // Products of two 16-bit floats are exact in the fp32 accumulator. The fp32 hidden vector
 // is handed to phase 2 as three 16-bit pieces (hi + mid + lo), so no precision is lost
 // between the phases.
@@ -21,9 +24,8 @@ namespace aeon_b200 {
 
 namespace {
 
-constexpr int kWarps = 16;
-constexpr int kTokGroup = 16;   // tokens per CTA pass: 2 MMA N tiles
-constexpr int kNT = kTokGroup / 8;
+// Instances <warps, N tiles>: <16, 1> up to 8 tokens, <16, 2> up to 16, <8, 4> beyond
+// (32 tokens per CTA pass). The reduction buffer stays within 32 KB of static shared memory.
 
 template <bool kBf16>
 __device__ __forceinline__ void mma16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -53,7 +55,7 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 }
 
 // Phase 1: hidden[t, r] = swiglu(W1[r,:] . x[t,:], W3[r,:] . x[t,:]) as three 16-bit pieces.
-template <bool kBf16>
+template <bool kBf16, int kWarps, int kNT>
 __global__ void __launch_bounds__(kWarps * 32)
 shared_gate_up_kernel(const uint16_t* __restrict__ w1, const uint16_t* __restrict__ w3,
                       const uint16_t* __restrict__ x, int64_t x_stride, int tokens, int H, int I,
@@ -63,7 +65,7 @@ shared_gate_up_kernel(const uint16_t* __restrict__ w1, const uint16_t* __restric
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * 16;
-    const int tok0 = blockIdx.y * kTokGroup;
+    const int tok0 = blockIdx.y * (kNT * 8);
     const int kspan = H / kWarps;
     const int kbeg = warp * kspan;
 
@@ -133,7 +135,7 @@ shared_gate_up_kernel(const uint16_t* __restrict__ w1, const uint16_t* __restric
 }
 
 // Phase 2: out[t, r] = W2[r,:] . hidden[t,:]  (written, not added).
-template <bool kBf16>
+template <bool kBf16, int kWarps, int kNT>
 __global__ void __launch_bounds__(kWarps * 32)
 shared_down_kernel(const uint16_t* __restrict__ w2, const uint16_t* __restrict__ hid_hi,
                    const uint16_t* __restrict__ hid_mid, const uint16_t* __restrict__ hid_lo,
@@ -142,7 +144,7 @@ shared_down_kernel(const uint16_t* __restrict__ w2, const uint16_t* __restrict__
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * 16;
-    const int tok0 = blockIdx.y * kTokGroup;
+    const int tok0 = blockIdx.y * (kNT * 8);
     const int kspan = I / kWarps;
     const int kbeg = warp * kspan;
 
@@ -195,6 +197,38 @@ shared_down_kernel(const uint16_t* __restrict__ w2, const uint16_t* __restrict__
     }
 }
 
+template <bool kBf16, int kWarps, int kNT>
+void launch_shared_instance(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
+                            const void* x, int64_t x_stride, int tokens, float* moe_accum,
+                            int64_t accum_stride, cudaStream_t stream) {
+    const aeon_b200_moe_config& cfg = ctx->cfg;
+    const int groups = (tokens + kNT * 8 - 1) / (kNT * 8);
+    uint16_t* hi = reinterpret_cast<uint16_t*>(ctx->d_sh_hi);
+    uint16_t* mid = reinterpret_cast<uint16_t*>(ctx->d_sh_mid);
+    uint16_t* lo = reinterpret_cast<uint16_t*>(ctx->d_sh_lo);
+    const dim3 grid1(cfg.intermediate / 16, groups), grid2(cfg.hidden / 16, groups);
+    shared_gate_up_kernel<kBf16, kWarps, kNT><<<grid1, kWarps * 32, 0, stream>>>(
+        static_cast<const uint16_t*>(w1), static_cast<const uint16_t*>(w3), static_cast<const uint16_t*>(x),
+        x_stride, tokens, cfg.hidden, cfg.intermediate, cfg.swiglu_limit, hi, mid, lo);
+    AEON_CUDA_CHECK(cudaGetLastError());
+    shared_down_kernel<kBf16, kWarps, kNT><<<grid2, kWarps * 32, 0, stream>>>(
+        static_cast<const uint16_t*>(w2), hi, mid, lo, tokens, cfg.hidden, cfg.intermediate, moe_accum,
+        accum_stride);
+    AEON_CUDA_CHECK(cudaGetLastError());
+}
+
+template <bool kBf16>
+void launch_shared_dtype(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
+                         const void* x, int64_t x_stride, int tokens, float* moe_accum,
+                         int64_t accum_stride, cudaStream_t stream) {
+    if (tokens <= 8)
+        launch_shared_instance<kBf16, 16, 1>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
+    else if (tokens <= 16)
+        launch_shared_instance<kBf16, 16, 2>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
+    else
+        launch_shared_instance<kBf16, 8, 4>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
+}
+
 }  // namespace
 
 void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
@@ -206,33 +240,12 @@ void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, co
             "aeon_b200_shared_expert: tokens must be in [1, max_tokens of the context]");
     require(x_stride >= cfg.hidden && x_stride % 8 == 0 && accum_stride >= cfg.hidden,
             "aeon_b200_shared_expert: bad row stride");
-    require(cfg.hidden % (kWarps * 32) == 0 && cfg.intermediate % (kWarps * 32) == 0,
+    require(cfg.hidden % 512 == 0 && cfg.intermediate % 512 == 0,
             "aeon_b200_shared_expert: hidden and intermediate must be multiples of 512");
-    const int groups = (tokens + kTokGroup - 1) / kTokGroup;
-    uint16_t* hi = reinterpret_cast<uint16_t*>(ctx->d_sh_hi);
-    uint16_t* mid = reinterpret_cast<uint16_t*>(ctx->d_sh_mid);
-    uint16_t* lo = reinterpret_cast<uint16_t*>(ctx->d_sh_lo);
-    const dim3 grid1(cfg.intermediate / 16, groups), grid2(cfg.hidden / 16, groups);
-    if (cfg.act_dtype == AEON_B200_BF16) {
-        shared_gate_up_kernel<true><<<grid1, kWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(w1), static_cast<const uint16_t*>(w3),
-            static_cast<const uint16_t*>(x), x_stride, tokens, cfg.hidden, cfg.intermediate,
-            cfg.swiglu_limit, hi, mid, lo);
-        AEON_CUDA_CHECK(cudaGetLastError());
-        shared_down_kernel<true><<<grid2, kWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(w2), hi, mid, lo, tokens, cfg.hidden, cfg.intermediate,
-            moe_accum, accum_stride);
-    } else {
-        shared_gate_up_kernel<false><<<grid1, kWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(w1), static_cast<const uint16_t*>(w3),
-            static_cast<const uint16_t*>(x), x_stride, tokens, cfg.hidden, cfg.intermediate,
-            cfg.swiglu_limit, hi, mid, lo);
-        AEON_CUDA_CHECK(cudaGetLastError());
-        shared_down_kernel<false><<<grid2, kWarps * 32, 0, stream>>>(
-            static_cast<const uint16_t*>(w2), hi, mid, lo, tokens, cfg.hidden, cfg.intermediate,
-            moe_accum, accum_stride);
-    }
-    AEON_CUDA_CHECK(cudaGetLastError());
+    if (cfg.act_dtype == AEON_B200_BF16)
+        launch_shared_dtype<true>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
+    else
+        launch_shared_dtype<false>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
     ctx->launches += 2;
 }
 

@@ -8,7 +8,7 @@ import gpu_support as gs
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("preset,tokens", [("baseline", 1), ("baseline", 19), ("ref_dsv4", 5)])
+@pytest.mark.parametrize("preset,tokens", [("baseline", 1), ("baseline", 12), ("baseline", 19), ("ref_dsv4", 5), ("ref_dsv4", 45)])
 def test_shared_expert_matches_dense_oracle(oracle, preset, tokens):
     import torch
     cfg = aeon_b200.preset(preset)
