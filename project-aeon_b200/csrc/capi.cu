@@ -159,6 +159,7 @@ void free_ctx_buffers(aeon_b200_ctx* c) {
     for (void* b : bufs)
         if (b) (void)cudaFree(b);
     free_prefill_scratch(c);
+    free_shared_tc_scratch(c);
     if (c->timing_events) {
         for (cudaEvent_t e : *c->timing_events) (void)cudaEventDestroy(e);
         delete c->timing_events;

@@ -130,6 +130,7 @@ struct aeon_b200_ctx {
     __half* d_sh_hi;        // [max_tokens, I] (hi/mid/lo split of the fp32 hidden)
     __half* d_sh_mid;
     __half* d_sh_lo;
+    void* shared_tc;        // split-K partial sums of the tensor-core form, allocated on first use
 };
 
 namespace aeon_b200 {
@@ -164,6 +165,12 @@ void launch_ep_combine(float* out, int64_t out_stride, const float* partials, in
 void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
                           const void* x, int64_t x_stride, int tokens, float* moe_accum,
                           int64_t accum_stride, cudaStream_t stream);
+// tensor-core form of the shared expert (shared_expert_tc.cu), used at larger batches
+bool shared_expert_tc_supports(const aeon_b200_moe_config& cfg, int64_t accum_stride);
+void launch_shared_expert_tc(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
+                             const void* x, int64_t x_stride, int tokens, float* moe_accum,
+                             int64_t accum_stride, cudaStream_t stream);
+void free_shared_tc_scratch(aeon_b200_ctx* ctx);
 void launch_synth_experts(const aeon_b200_moe_config& cfg, void* pool_base, uint32_t first_slot,
                           uint32_t count, uint64_t seed, uint32_t layer, uint32_t first_expert,
                           const uint16_t* scale_table, uint32_t table_n, cudaStream_t stream);

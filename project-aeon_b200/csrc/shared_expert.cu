@@ -24,6 +24,12 @@ namespace aeon_b200 {
 
 namespace {
 
+// Above this many tokens the tensor-core form (shared_expert_tc.cu) takes over. Its time is
+// nearly flat in the token count (it is bound by feeding the weight operand), while the kernels
+// here stream the weights once per group of 32 tokens; measured on B200 the two meet between two
+// and three groups (batch 32: 983 vs 1057 us per layer; batch 128: 1741 vs 1706 us).
+constexpr int kTensorCoreFrom = 64;
+
 // Instances <warps, N tiles>: <16, 1> up to 8 tokens, <16, 2> up to 16, <8, 4> beyond
 // (32 tokens per CTA pass). The reduction buffer stays within 32 KB of static shared memory.
 
@@ -242,6 +248,11 @@ void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, co
             "aeon_b200_shared_expert: bad row stride");
     require(cfg.hidden % 512 == 0 && cfg.intermediate % 512 == 0,
             "aeon_b200_shared_expert: hidden and intermediate must be multiples of 512");
+    if (tokens > kTensorCoreFrom && shared_expert_tc_supports(cfg, accum_stride)) {
+        // a dense contraction from here on: tensor-core form
+        launch_shared_expert_tc(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
+        return;
+    }
     if (cfg.act_dtype == AEON_B200_BF16)
         launch_shared_dtype<true>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
     else

@@ -59,6 +59,12 @@ __device__ __forceinline__ uint32_t idesc_f16(uint32_t m, uint32_t n) {
     return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// The same with the operand type selectable: A / B format 0 = fp16, 1 = bf16.
+__device__ __forceinline__ uint32_t idesc_16bit(uint32_t m, uint32_t n, bool bf16) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]^T, one CTA, issued by a single thread.
 __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                            uint32_t idesc, uint32_t accumulate) {

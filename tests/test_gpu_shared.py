@@ -8,7 +8,9 @@ import gpu_support as gs
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("preset,tokens", [("baseline", 1), ("baseline", 12), ("baseline", 19), ("ref_dsv4", 5), ("ref_dsv4", 45)])
+@pytest.mark.parametrize("preset,tokens", [("baseline", 1), ("baseline", 12), ("baseline", 19), ("ref_dsv4", 5), ("ref_dsv4", 45),
+                                           # above 64 tokens: the tensor-core form
+                                           ("baseline", 100), ("ref_dsv4", 77)])
 def test_shared_expert_matches_dense_oracle(oracle, preset, tokens):
     import torch
     cfg = aeon_b200.preset(preset)
@@ -22,6 +24,6 @@ def test_shared_expert_matches_dense_oracle(oracle, preset, tokens):
     got = out.cpu().numpy().astype(np.float64)
     x = synth.from_bits16(x_bits, cfg.act_dtype)
     w1, w3, w2 = layer.shared_bits(oracle)
-    for t in sorted({0, tokens // 2, tokens - 1}):
+    for t in sorted({0, tokens // 2, tokens - 1, min(tokens - 1, 64)}):
         want = oracle.dense_ffn(w1, w3, w2, cfg.act_dtype, x[t], cfg.swiglu_limit)
         s = gs.assert_close(oracle, want, got[t], f"{preset} token {t}", tol_abs=1e-3, tol_l2=1e-5)
