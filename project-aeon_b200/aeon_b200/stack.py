@@ -152,6 +152,9 @@ class MoeStack:
             self.partial = torch.empty(max_tokens, H, dtype=torch.float32, device=dev)
             self.recv = torch.empty(world, max_tokens // world, H, dtype=torch.float32, device=dev)
         self._extra_launches = 0
+        # False: the shared expert runs on the caller's stream ahead of the router, so that no
+        # other kernel is resident while the routed kernels run (used to time them alone)
+        self.overlap_shared = True
         self._side = torch.cuda.Stream(device=dev)
         self._fork = torch.cuda.Event()
         self._join = torch.cuda.Event()
@@ -202,7 +205,13 @@ class MoeStack:
         w = self.weights[l]
         ctx = self.ctx
         ops = _DeviceOps(ctx, w)
-        if self.world == 1:
+        if self.world == 1 and not self.overlap_shared:
+            ops.shared(x, out)
+            weights, ids = ops.router(x)
+            ctx.moe_decode(w.pool.base, w.slot_of, x, ids, weights, out, defer_accumulate=True)
+            ctx.moe_accumulate(w.slot_of, ids, out)
+            tokens_seen = x.shape[0]
+        elif self.world == 1:
             # The shared expert (88 MB of dense weights, no dependence on the routing) runs on
             # a side stream while the main stream does router -> permutation -> routed experts;
             # the two meet at the slot-order accumulate, whose initial value it produces.
