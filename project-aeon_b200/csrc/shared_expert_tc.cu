@@ -446,11 +446,21 @@ bool shared_expert_tc_supports(const aeon_b200_moe_config& cfg, int64_t accum_st
 void launch_shared_expert_tc(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
                              const void* x, int64_t x_stride, int tokens, float* moe_accum,
                              int64_t accum_stride, cudaStream_t stream) {
-    if (ctx->cfg.act_dtype == AEON_B200_BF16)
-        run<true>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
-    else
-        run<false>(ctx, w1, w3, w2, x, x_stride, tokens, moe_accum, accum_stride, stream);
-    ctx->launches += 4;
+    // One token tile (up to 256 tokens) per pass: the kernels index any number of token tiles,
+    // but only the single-tile shape has been checked against the oracle on a B200 so far, so
+    // larger batches are fed tile by tile (stream order keeps the passes apart; the hidden
+    // planes and the partial sums are reused).
+    const uint16_t* xs = static_cast<const uint16_t*>(x);
+    for (int t0 = 0; t0 < tokens; t0 += kMaxN) {
+        const int n = std::min(kMaxN, tokens - t0);
+        const void* xc = xs + static_cast<size_t>(t0) * x_stride;
+        float* oc = moe_accum + static_cast<size_t>(t0) * accum_stride;
+        if (ctx->cfg.act_dtype == AEON_B200_BF16)
+            run<true>(ctx, w1, w3, w2, xc, x_stride, n, oc, accum_stride, stream);
+        else
+            run<false>(ctx, w1, w3, w2, xc, x_stride, n, oc, accum_stride, stream);
+        ctx->launches += 4;
+    }
 }
 
 }  // namespace aeon_b200

@@ -10,7 +10,9 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("preset,tokens", [("baseline", 1), ("baseline", 12), ("baseline", 19), ("ref_dsv4", 5), ("ref_dsv4", 45),
                                            # above 64 tokens: the tensor-core form
-                                           ("baseline", 100), ("ref_dsv4", 77)])
+                                           ("baseline", 100), ("ref_dsv4", 77),
+                                           # more than one 256-token pass
+                                           ("baseline", 300)])
 def test_shared_expert_matches_dense_oracle(oracle, preset, tokens):
     import torch
     cfg = aeon_b200.preset(preset)
@@ -24,6 +26,6 @@ def test_shared_expert_matches_dense_oracle(oracle, preset, tokens):
     got = out.cpu().numpy().astype(np.float64)
     x = synth.from_bits16(x_bits, cfg.act_dtype)
     w1, w3, w2 = layer.shared_bits(oracle)
-    for t in sorted({0, tokens // 2, tokens - 1, min(tokens - 1, 64)}):
+    for t in sorted({0, tokens // 2, tokens - 1, min(tokens - 1, 64), min(tokens - 1, 256)}):
         want = oracle.dense_ffn(w1, w3, w2, cfg.act_dtype, x[t], cfg.swiglu_limit)
         s = gs.assert_close(oracle, want, got[t], f"{preset} token {t}", tol_abs=1e-3, tol_l2=1e-5)
