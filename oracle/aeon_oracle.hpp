@@ -685,6 +685,173 @@ inline std::vector<double> moe_combine(const std::vector<std::vector<double>>& e
 }
 
 // ---------------------------------------------------------------------------
+// The steps either side of the MoE FFN in a layer: hyper-connection pre-mix of the four
+// residual streams, FFN RMSNorm, and the post expansion back to four streams
+// (the caller of the path, src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:204-312).
+// ---------------------------------------------------------------------------
+
+// out[i] = x[i] * rsqrt(mean(x^2) + eps) * weight[i].
+// Follows src/architecture/deepseek_v4/reference/dsv4_oracle.hpp:146-158.
+inline std::vector<double> rmsnorm(const std::vector<double>& x, const std::vector<double>& weight,
+                                   double eps) {
+    double sum_sq = 0.0;
+    for (double v : x) sum_sq += v * v;
+    const double inv_rms = 1.0 / std::sqrt(sum_sq / static_cast<double>(x.size()) + eps);
+    std::vector<double> out(x.size());
+    for (size_t i = 0; i < x.size(); ++i) out[i] = x[i] * inv_rms * weight[i];
+    return out;
+}
+
+// Weightless form, dsv4_oracle.hpp:160-169.
+inline std::vector<double> rmsnorm_unit(const std::vector<double>& x, double eps) {
+    double sum_sq = 0.0;
+    for (double v : x) sum_sq += v * v;
+    const double inv_rms = 1.0 / std::sqrt(sum_sq / static_cast<double>(x.size()) + eps);
+    std::vector<double> out(x.size());
+    for (size_t i = 0; i < x.size(); ++i) out[i] = x[i] * inv_rms;
+    return out;
+}
+
+// Constants of the hyper-connection mixes, dsv4_oracle.hpp:489-495.
+struct HcParams {
+    double rms_eps{1e-6};
+    double pre_eps{1e-6};
+    double sinkhorn_eps{1e-6};
+    double post_mult{2.0};
+    int sinkhorn_iters{20};
+};
+
+struct HcPreResult {
+    std::vector<double> mixes;      // [3 * hc] for hc = 4 streams: 4 pre, 4 post, 16 comb logits
+    std::vector<double> pre_mix;    // [hc]
+    std::vector<double> post_mix;   // [hc]
+    std::vector<double> comb;       // [hc * hc], C[contraction * hc + output]
+};
+
+// mixes[m] = (residual . fn[m]) * rsqrt(mean(residual^2) + rms_eps) over the flattened
+// hc x hidden residual; fn is fp32 [mixes, hc * hidden] row-major.
+// Follows dsv4_oracle.hpp:510-524.
+inline std::vector<double> hc_mixes(const std::vector<double>& residual, size_t n_mixes, const float* fn,
+                                    double rms_eps) {
+    const size_t dim = residual.size();
+    double sum_sq = 0.0;
+    for (double v : residual) sum_sq += v * v;
+    const double inv_rms = 1.0 / std::sqrt(sum_sq / static_cast<double>(dim) + rms_eps);
+    std::vector<double> mixes(n_mixes, 0.0);
+    for (size_t m = 0; m < n_mixes; ++m) {
+        double dot = 0.0;
+        for (size_t k = 0; k < dim; ++k) dot += residual[k] * static_cast<double>(fn[m * dim + k]);
+        mixes[m] = dot * inv_rms;
+    }
+    return mixes;
+}
+
+// Scale/base transform, sigmoid gates, softmax over the output axis and the Sinkhorn
+// normalisations of the comb (every denominator carries sinkhorn_eps; only the pre gate
+// carries pre_eps). Follows dsv4_oracle.hpp:529-591.
+inline void hc_sinkhorn(const std::vector<double>& mixes, const std::vector<double>& scale3,
+                        const std::vector<double>& base, size_t hc, const HcParams& p, HcPreResult& out) {
+    auto sigmoid = [](double x) { return 1.0 / (1.0 + std::exp(-x)); };
+    out.pre_mix.resize(hc);
+    for (size_t j = 0; j < hc; ++j) out.pre_mix[j] = sigmoid(mixes[j] * scale3[0] + base[j]) + p.pre_eps;
+    out.post_mix.resize(hc);
+    for (size_t j = 0; j < hc; ++j)
+        out.post_mix[j] = sigmoid(mixes[j + hc] * scale3[1] + base[j + hc]) * p.post_mult;
+    std::vector<double>& C = out.comb;
+    C.assign(hc * hc, 0.0);
+    for (size_t i = 0; i < hc; ++i)
+        for (size_t j = 0; j < hc; ++j) {
+            const size_t idx = 2 * hc + i * hc + j;
+            C[i * hc + j] = mixes[idx] * scale3[2] + base[idx];
+        }
+    for (size_t i = 0; i < hc; ++i) {          // softmax over j, the output axis
+        double max_v = C[i * hc];
+        for (size_t j = 1; j < hc; ++j) max_v = std::fmax(max_v, C[i * hc + j]);
+        double sum_e = 0.0;
+        for (size_t j = 0; j < hc; ++j) {
+            const double e = std::exp(C[i * hc + j] - max_v);
+            C[i * hc + j] = e;
+            sum_e += e;
+        }
+        for (size_t j = 0; j < hc; ++j) C[i * hc + j] = C[i * hc + j] / sum_e + p.sinkhorn_eps;
+    }
+    auto normalize_over_i = [&]() {              // the contraction axis
+        for (size_t j = 0; j < hc; ++j) {
+            double col = 0.0;
+            for (size_t i = 0; i < hc; ++i) col += C[i * hc + j];
+            const double inv = 1.0 / (col + p.sinkhorn_eps);
+            for (size_t i = 0; i < hc; ++i) C[i * hc + j] *= inv;
+        }
+    };
+    auto normalize_over_j = [&]() {
+        for (size_t i = 0; i < hc; ++i) {
+            double row = 0.0;
+            for (size_t j = 0; j < hc; ++j) row += C[i * hc + j];
+            const double inv = 1.0 / (row + p.sinkhorn_eps);
+            for (size_t j = 0; j < hc; ++j) C[i * hc + j] *= inv;
+        }
+    };
+    normalize_over_i();
+    for (int it = 0; it < p.sinkhorn_iters - 1; ++it) {
+        normalize_over_j();
+        normalize_over_i();
+    }
+}
+
+// layer_input[h] = sum_j pre_mix[j] * residual[j][h]. Follows dsv4_oracle.hpp:595-607.
+inline std::vector<double> hc_pre_combine(const std::vector<double>& residual,
+                                          const std::vector<double>& pre_mix, size_t hidden) {
+    const size_t hc = pre_mix.size();
+    std::vector<double> out(hidden, 0.0);
+    for (size_t h = 0; h < hidden; ++h) {
+        double acc = 0.0;
+        for (size_t j = 0; j < hc; ++j) acc += pre_mix[j] * residual[j * hidden + h];
+        out[h] = acc;
+    }
+    return out;
+}
+
+// out[j][h] = post_mix[j] * layer_out[h] + sum_i C[i][j] * residual[i][h]; transpose_comb is the
+// wrong-reading control of the reference. Follows dsv4_oracle.hpp:613-631.
+inline std::vector<double> hc_post(const std::vector<double>& layer_out, const std::vector<double>& residual,
+                                   const std::vector<double>& post_mix, const std::vector<double>& C,
+                                   size_t hidden, bool transpose_comb = false) {
+    const size_t hc = post_mix.size();
+    std::vector<double> out(hc * hidden, 0.0);
+    for (size_t j = 0; j < hc; ++j)
+        for (size_t h = 0; h < hidden; ++h) {
+            double acc = post_mix[j] * layer_out[h];
+            for (size_t i = 0; i < hc; ++i) {
+                const double c = transpose_comb ? C[j * hc + i] : C[i * hc + j];
+                acc += c * residual[i * hidden + h];
+            }
+            out[j * hidden + h] = acc;
+        }
+    return out;
+}
+
+// The FFN half's front: residual streams -> (mix coefficients, FFN input after RMSNorm).
+// Follows the composition at dsv4_oracle.hpp:2446-2467.
+struct FfnFront {
+    HcPreResult hc;
+    std::vector<double> ffn_pre;    // [hidden]
+    std::vector<double> ffn_norm;   // [hidden], the activation the router and the experts read
+};
+inline FfnFront ffn_front(const std::vector<double>& res_mid, size_t hidden, const float* hc_fn,
+                          const float* hc_base, const float* hc_scale3,
+                          const std::vector<double>& norm_weight, double norm_eps, const HcParams& p) {
+    const size_t hc = res_mid.size() / hidden;
+    FfnFront out;
+    out.hc.mixes = hc_mixes(res_mid, hc * (hc + 2), hc_fn, p.rms_eps);
+    const std::vector<double> scale(hc_scale3, hc_scale3 + 3);
+    const std::vector<double> base(hc_base, hc_base + hc * (hc + 2));
+    hc_sinkhorn(out.hc.mixes, scale, base, hc, p, out.hc);
+    out.ffn_pre = hc_pre_combine(res_mid, out.hc.pre_mix, hidden);
+    out.ffn_norm = rmsnorm(out.ffn_pre, norm_weight, norm_eps);
+    return out;
+}
+
+// ---------------------------------------------------------------------------
 // Counter-based synthetic tensors shared with the CUDA library's fill kernels,
 // so the device pool and this oracle hold byte-identical payloads without the
 // pool ever crossing the bus. A value depends only on (seed, stream, index):

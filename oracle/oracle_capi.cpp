@@ -356,4 +356,39 @@ int ao_dense_ffn_f64(const double* w1, const double* w3, const double* w2, int i
     });
 }
 
+// Front of the FFN half of a layer: residual streams [hc, hidden] -> mix coefficients and
+// the normalised FFN input. mixes_out [hc*(hc+2)], pre_out / post_out [hc], comb_out [hc*hc],
+// ffn_pre_out / ffn_norm_out [hidden]; norm_weight may be null (weightless RMSNorm).
+int ao_ffn_front(const double* res_mid, int hidden, int hc, const float* hc_fn, const float* hc_base,
+                 const float* hc_scale3, const double* norm_weight, double norm_eps, double* mixes_out,
+                 double* pre_out, double* post_out, double* comb_out, double* ffn_pre_out,
+                 double* ffn_norm_out) {
+    return guarded([&] {
+        const size_t H = static_cast<size_t>(hidden), S = static_cast<size_t>(hc);
+        const std::vector<double> res(res_mid, res_mid + S * H);
+        const std::vector<double> w = norm_weight ? std::vector<double>(norm_weight, norm_weight + H)
+                                                  : std::vector<double>(H, 1.0);
+        const FfnFront f = ffn_front(res, H, hc_fn, hc_base, hc_scale3, w, norm_eps, HcParams{});
+        std::memcpy(mixes_out, f.hc.mixes.data(), f.hc.mixes.size() * sizeof(double));
+        std::memcpy(pre_out, f.hc.pre_mix.data(), S * sizeof(double));
+        std::memcpy(post_out, f.hc.post_mix.data(), S * sizeof(double));
+        std::memcpy(comb_out, f.hc.comb.data(), S * S * sizeof(double));
+        std::memcpy(ffn_pre_out, f.ffn_pre.data(), H * sizeof(double));
+        std::memcpy(ffn_norm_out, f.ffn_norm.data(), H * sizeof(double));
+    });
+}
+
+// out[hc, hidden] = post expansion of the layer output back to the residual streams.
+int ao_hc_post(const double* layer_out, const double* residual, const double* post_mix, const double* comb,
+               int hidden, int hc, int transpose_comb, double* out) {
+    return guarded([&] {
+        const size_t H = static_cast<size_t>(hidden), S = static_cast<size_t>(hc);
+        const std::vector<double> y = hc_post(std::vector<double>(layer_out, layer_out + H),
+                                              std::vector<double>(residual, residual + S * H),
+                                              std::vector<double>(post_mix, post_mix + S),
+                                              std::vector<double>(comb, comb + S * S), H, transpose_comb != 0);
+        std::memcpy(out, y.data(), S * H * sizeof(double));
+    });
+}
+
 }  // extern "C"

@@ -299,6 +299,61 @@ int main(int argc, char** argv) {
                   a.max_abs_index == b.max_abs_index);
     }
 
+    // --- hyper-connection pre-mix, FFN RMSNorm, post expansion (the caller of the path) ---
+    std::vector<double> hc_golden_front, hc_golden_post;
+    {
+        const size_t hidden = 192, hc = 4, n_mix = hc * (hc + 2);
+        ref::Rng g(0x4C0FFEEull);
+        const std::vector<double> res_mid = g.vector_filled(hc * hidden, 1.5);
+        std::vector<float> fn(n_mix * hc * hidden), base(n_mix), scale(3);
+        for (float& v : fn) v = static_cast<float>(g.symmetric(0.05));
+        for (float& v : base) v = static_cast<float>(g.symmetric(0.5));
+        for (float& v : scale) v = static_cast<float>(0.5 + g.uniform01());
+        const std::vector<double> norm_w = g.vector_filled(hidden, 1.0);
+        const std::vector<double> layer_out = g.vector_filled(hidden, 2.0);
+        ref::HcParams rp;
+        const std::vector<double> mixes_ref = ref::hc_mixes(
+            res_mid, n_mix, [&](size_t m, size_t k) { return static_cast<double>(fn[m * hc * hidden + k]); },
+            hc * hidden, rp.rms_eps);
+        ref::HcPreResult rh;
+        ref::hc_sinkhorn(mixes_ref, std::vector<double>(scale.begin(), scale.end()),
+                         std::vector<double>(base.begin(), base.end()), hc, rp, rh);
+        const std::vector<double> pre_ref = ref::hc_pre_combine(res_mid, rh.pre_mix, hidden);
+        const std::vector<double> norm_ref = ref::rmsnorm(pre_ref, norm_w, 1e-6);
+        const std::vector<double> post_ref = ref::hc_post(layer_out, res_mid, rh.post_mix, rh.comb, hidden);
+        const std::vector<double> post_t_ref = ref::hc_post(layer_out, res_mid, rh.post_mix, rh.comb, hidden, true);
+
+        ao::HcParams ap;
+        const ao::FfnFront front = ao::ffn_front(res_mid, hidden, fn.data(), base.data(), scale.data(), norm_w, 1e-6, ap);
+        check("hc_mixes + hc_sinkhorn (pre, post, comb): bit-identical",
+              bit_equal(front.hc.mixes, mixes_ref) && bit_equal(front.hc.pre_mix, rh.pre_mix) &&
+                  bit_equal(front.hc.post_mix, rh.post_mix) && bit_equal(front.hc.comb, rh.comb));
+        check("hc_pre_combine + rmsnorm (FFN input): bit-identical",
+              bit_equal(front.ffn_pre, pre_ref) && bit_equal(front.ffn_norm, norm_ref));
+        check("rmsnorm_unit: bit-identical", bit_equal(ao::rmsnorm_unit(pre_ref, 1e-6), ref::rmsnorm_unit(pre_ref, 1e-6)));
+        const std::vector<double> post_ao = ao::hc_post(layer_out, res_mid, front.hc.post_mix, front.hc.comb, hidden);
+        check("hc_post and its transposed-comb control: bit-identical",
+              bit_equal(post_ao, post_ref) &&
+                  bit_equal(ao::hc_post(layer_out, res_mid, front.hc.post_mix, front.hc.comb, hidden, true), post_t_ref));
+        // the control is a different answer, so the comb convention is pinned by the above
+        check("transposed comb differs from the correct reading by > 1e-2",
+              ref::compare(post_ref, post_t_ref).max_abs > 1e-2);
+        // comb is doubly stochastic up to the eps terms
+        bool stochastic = true;
+        for (size_t i = 0; i < hc; ++i) {
+            double row = 0.0, col = 0.0;
+            for (size_t j = 0; j < hc; ++j) { row += rh.comb[i * hc + j]; col += rh.comb[j * hc + i]; }
+            stochastic = stochastic && std::fabs(row - 1.0) < 1e-4 && std::fabs(col - 1.0) < 1e-4;
+        }
+        check("comb rows and columns sum to 1 within 1e-4", stochastic);
+        hc_golden_front = front.hc.pre_mix;
+        hc_golden_front.insert(hc_golden_front.end(), rh.post_mix.begin(), rh.post_mix.end());
+        hc_golden_front.insert(hc_golden_front.end(), rh.comb.begin(), rh.comb.end());
+        hc_golden_front.insert(hc_golden_front.end(), norm_ref.begin(), norm_ref.begin() + 16);
+        hc_golden_post.assign(post_ref.begin(), post_ref.begin() + 16);
+        hc_golden_post.insert(hc_golden_post.end(), post_ref.end() - 16, post_ref.end());
+    }
+
     if (golden_path != nullptr) {
         FILE* f = std::fopen(golden_path, "w");
         if (!f) { std::perror("golden"); return 2; }
@@ -315,7 +370,10 @@ int main(int argc, char** argv) {
         json_ints(f, "hash_ids", hash_ids);
         json_doubles(f, "hash_weights", hash_w);
         json_doubles(f, "swiglu_probe_grid", swiglu_out);
-        json_doubles(f, "dense_ffn", dense_out, true);
+        json_doubles(f, "dense_ffn", dense_out);
+        std::fprintf(f, "  \"hc_seed\": \"0x4C0FFEE\",\n");
+        json_doubles(f, "hc_pre_post_comb_norm16", hc_golden_front);
+        json_doubles(f, "hc_post_first16_last16", hc_golden_post, true);
         std::fprintf(f, "}\n");
         std::fclose(f);
         std::printf("  golden fixture written to %s\n", golden_path);

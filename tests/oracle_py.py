@@ -274,3 +274,37 @@ def dense_ffn_f64(w1, w3, w2, x, limit=10.0) -> np.ndarray:
                              w2.ctypes.data_as(c_void_p), I, H, x.ctypes.data_as(c_void_p),
                              c_double(limit), out.ctypes.data_as(c_void_p)))
     return out
+
+
+def ffn_front(res_mid, hc_fn, hc_base, hc_scale3, norm_weight=None, norm_eps=1e-6) -> dict:
+    """Hyper-connection pre-mix + FFN RMSNorm: res_mid [hc, hidden] fp64, hc_fn fp32
+    [hc*(hc+2), hc*hidden], hc_base fp32 [hc*(hc+2)], hc_scale3 fp32 [3]."""
+    res_mid = np.ascontiguousarray(res_mid, dtype=np.float64)
+    hc, hidden = res_mid.shape
+    fn = np.ascontiguousarray(hc_fn, dtype=np.float32)
+    base = np.ascontiguousarray(hc_base, dtype=np.float32)
+    scale = np.ascontiguousarray(hc_scale3, dtype=np.float32)
+    assert fn.shape == (hc * (hc + 2), hc * hidden) and base.shape == (hc * (hc + 2),) and scale.shape == (3,)
+    w = None if norm_weight is None else np.ascontiguousarray(norm_weight, dtype=np.float64)
+    out = dict(mixes=np.empty(hc * (hc + 2)), pre=np.empty(hc), post=np.empty(hc), comb=np.empty((hc, hc)),
+               ffn_pre=np.empty(hidden), ffn_norm=np.empty(hidden))
+    _chk(_L.ao_ffn_front(res_mid.ctypes.data_as(c_void_p), hidden, hc, fn.ctypes.data_as(c_void_p),
+                         base.ctypes.data_as(c_void_p), scale.ctypes.data_as(c_void_p),
+                         None if w is None else w.ctypes.data_as(c_void_p), c_double(norm_eps),
+                         *[out[k].ctypes.data_as(c_void_p)
+                           for k in ("mixes", "pre", "post", "comb", "ffn_pre", "ffn_norm")]))
+    return out
+
+
+def hc_post(layer_out, residual, post_mix, comb, transpose_comb=False) -> np.ndarray:
+    """out[j][h] = post_mix[j] * layer_out[h] + sum_i comb[i][j] * residual[i][h]."""
+    residual = np.ascontiguousarray(residual, dtype=np.float64)
+    hc, hidden = residual.shape
+    layer_out = np.ascontiguousarray(layer_out, dtype=np.float64)
+    post_mix = np.ascontiguousarray(post_mix, dtype=np.float64)
+    comb = np.ascontiguousarray(comb, dtype=np.float64)
+    out = np.empty((hc, hidden))
+    _chk(_L.ao_hc_post(layer_out.ctypes.data_as(c_void_p), residual.ctypes.data_as(c_void_p),
+                       post_mix.ctypes.data_as(c_void_p), comb.ctypes.data_as(c_void_p), hidden, hc,
+                       int(transpose_comb), out.ctypes.data_as(c_void_p)))
+    return out

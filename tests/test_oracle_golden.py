@@ -88,6 +88,41 @@ def test_swiglu_and_dense_fixture_bit_exact(oracle, golden):
     np.testing.assert_array_equal(y, hexfloats(golden["dense_ffn"]))
 
 
+def test_hyper_connection_front_and_post_bit_exact(oracle, golden):
+    """The steps either side of the MoE FFN (hyper-connection pre-mix with Sinkhorn comb, FFN
+    RMSNorm, post expansion) reproduce the reference's own outputs bit for bit; the inputs are
+    rebuilt from the reference's generator stream."""
+    hidden, hc = 192, 4
+    n_mix = hc * (hc + 2)
+    total = hc * hidden + n_mix * hc * hidden + n_mix + 3 + hidden + hidden
+    u01 = (oracle.rng_u64(0x4C0FFEE, total) >> np.uint64(11)).astype(np.float64) * (1.0 / 9007199254740992.0)
+    sym = u01 * 2.0 - 1.0
+    at = 0
+    def take(n):
+        nonlocal at
+        at += n
+        return slice(at - n, at)
+    res_mid = (sym[take(hc * hidden)] * 1.5).reshape(hc, hidden)
+    fn = (sym[take(n_mix * hc * hidden)] * 0.05).astype(np.float32).reshape(n_mix, hc * hidden)
+    base = (sym[take(n_mix)] * 0.5).astype(np.float32)
+    scale = (0.5 + u01[take(3)]).astype(np.float32)
+    norm_w = sym[take(hidden)] * 1.0
+    layer_out = sym[take(hidden)] * 2.0
+    front = oracle.ffn_front(res_mid, fn, base, scale, norm_w, 1e-6)
+    got = np.concatenate([front["pre"], front["post"], front["comb"].ravel(), front["ffn_norm"][:16]])
+    np.testing.assert_array_equal(got, hexfloats(golden["hc_pre_post_comb_norm16"]))
+    post = oracle.hc_post(layer_out, res_mid, front["post"], front["comb"]).ravel()
+    np.testing.assert_array_equal(np.concatenate([post[:16], post[-16:]]),
+                                  hexfloats(golden["hc_post_first16_last16"]))
+    # definitions, independently in numpy
+    np.testing.assert_allclose(front["ffn_pre"], front["pre"] @ res_mid, rtol=1e-13)
+    np.testing.assert_allclose(post.reshape(hc, hidden),
+                               np.outer(front["post"], layer_out) + front["comb"].T @ res_mid, rtol=1e-12)
+    assert np.abs(front["comb"].sum(axis=0) - 1).max() < 1e-4 and np.abs(front["comb"].sum(axis=1) - 1).max() < 1e-4
+    wrong = oracle.hc_post(layer_out, res_mid, front["post"], front["comb"], transpose_comb=True).ravel()
+    assert np.abs(wrong - post).max() > 1e-2
+
+
 def test_wrong_format_readings_are_far(oracle, ref_cfg):
     """The two plausible-but-wrong decodings differ materially (reference:
     tests/test_v4_expert_oracle.cpp section A: forks > 1e-1 apart)."""
