@@ -257,6 +257,42 @@ int aeon_b200_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32
                           const float* topk_weights, int tokens, float* moe_accum,
                           int64_t accum_stride, uint32_t flags, void* stream);
 
+/*
+ * The steps of a layer either side of the MoE FFN (the caller of the path,
+ * src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:204-312): the
+ * hyper-connection pre-mix of the four residual streams fused with the FFN
+ * RMSNorm, and the post expansion back to four streams. Replace
+ * hc_project_kernel + hc_sinkhorn_normalize_kernel + hc_pre_combine_kernel +
+ * the FFN norm, and hc_post_kernel
+ * (src/architecture/deepseek_v4/kernels/hc_sinkhorn.hpp:22-290). With these the
+ * activation the router and the experts read, the routing and the mix
+ * coefficients all stay on the device from residual in to residual out.
+ *
+ * res_mid / res_out: [tokens, 4, hidden] 16-bit (act_dtype), contiguous.
+ * hc_fn fp32 [24, 4*hidden], hc_base fp32 [24], hc_scale3 fp32 [3] (device).
+ * norm_weight [hidden] 16-bit. Outputs of the front: ffn_norm_out [tokens,
+ * out_stride] 16-bit, pre/post_mix_out fp32 [tokens, 4], comb_out fp32
+ * [tokens, 16] with comb[i*4 + j] contracting stream i into stream j.
+ * moe_out: the fp32 accumulator of the path (shared expert + routed experts).
+ */
+typedef struct aeon_b200_hc_params {
+    float rms_eps;         /* RMS of the flattened residual in the mixes */
+    float pre_eps;         /* added to the pre gate only */
+    float sinkhorn_eps;    /* in every Sinkhorn denominator and after the softmax */
+    float post_mult;       /* multiplies the post gate (2 in the reference model) */
+    float norm_eps;        /* FFN RMSNorm */
+    int32_t sinkhorn_iters;
+} aeon_b200_hc_params;
+int aeon_b200_hc_params_default(aeon_b200_hc_params* out_host);
+int aeon_b200_hc_ffn_front(aeon_b200_ctx* ctx, const void* res_mid, const float* hc_fn,
+                           const float* hc_base, const float* hc_scale3, const void* norm_weight,
+                           int tokens, const aeon_b200_hc_params* params_host, void* ffn_norm_out,
+                           int64_t out_stride, float* pre_mix_out, float* post_mix_out,
+                           float* comb_out, void* stream);
+int aeon_b200_hc_post(aeon_b200_ctx* ctx, const float* moe_out, int64_t moe_stride,
+                      const void* res_mid, const float* post_mix, const float* comb, int tokens,
+                      void* res_out, void* stream);
+
 /* Expert-parallel combine: out[t, :] += sum over r = 0..ranks-1, in rank order, of
  * partials[r, t, :] (fp32; partials is [ranks, tokens, hidden] dense, as an equal-split
  * all-to-all delivers it). The fixed order makes the result independent of arrival order.

@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_ep_combine", "aeon_b200_router_topk_noalloc", "aeon_b200_moe_prefill", "aeon_b200_moe_accumulate",
     "aeon_b200_expert_shard_bytes", "aeon_b200_pack_expert_shards", "aeon_b200_unpack_expert_shards",
     "aeon_b200_expert_rank_slice", "aeon_b200_merge_expert_shards",
+    "aeon_b200_hc_params_default", "aeon_b200_hc_ffn_front", "aeon_b200_hc_post",
 ]
 
 
@@ -59,6 +60,11 @@ class MoeConfig(ctypes.Structure):
         for key, value in changes.items():
             setattr(out, key, value)
         return out
+
+
+class HcParams(ctypes.Structure):
+    _fields_ = [("rms_eps", c_float), ("pre_eps", c_float), ("sinkhorn_eps", c_float),
+                ("post_mult", c_float), ("norm_eps", c_float), ("sinkhorn_iters", c_int32)]
 
 
 class ExpertLayout(ctypes.Structure):
@@ -123,6 +129,12 @@ def lib() -> ctypes.CDLL:
     L.aeon_b200_moe_accumulate.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                                            c_uint32, c_void_p]
     L.aeon_b200_ep_combine.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]
+    L.aeon_b200_hc_params_default.argtypes = [POINTER(HcParams)]
+    L.aeon_b200_hc_ffn_front.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                         POINTER(HcParams), c_void_p, c_int64, c_void_p, c_void_p,
+                                         c_void_p, c_void_p]
+    L.aeon_b200_hc_post.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                    c_void_p, c_void_p]
     L.aeon_b200_synth_fill_experts.argtypes = [POINTER(MoeConfig), c_void_p, c_uint32, c_uint32,
                                                c_uint64, c_uint32, c_uint32, c_void_p, c_uint32,
                                                c_void_p]
@@ -363,6 +375,36 @@ class Context:
                                              DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
 
 
+def hc_params_default() -> HcParams:
+    out = HcParams()
+    check(lib().aeon_b200_hc_params_default(ctypes.byref(out)))
+    return out
+
+
+def _hc_ffn_front(self, res_mid, hc_fn, hc_base, hc_scale3, norm_weight, params: HcParams | None = None):
+    """res_mid [T, 4, H] 16-bit -> (ffn_norm [T, H] 16-bit, pre [T, 4], post [T, 4], comb [T, 16])."""
+    import torch
+    T, H = res_mid.shape[0], res_mid.shape[2]
+    params = params or hc_params_default()
+    ffn_norm = torch.empty(T, H, dtype=res_mid.dtype, device=res_mid.device)
+    pre = torch.empty(T, 4, dtype=torch.float32, device=res_mid.device)
+    post = torch.empty_like(pre)
+    comb = torch.empty(T, 16, dtype=torch.float32, device=res_mid.device)
+    check(lib().aeon_b200_hc_ffn_front(self._h, _ptr(res_mid), _ptr(hc_fn), _ptr(hc_base), _ptr(hc_scale3),
+                                       _ptr(norm_weight), T, ctypes.byref(params), _ptr(ffn_norm),
+                                       ffn_norm.stride(0), _ptr(pre), _ptr(post), _ptr(comb), _stream()))
+    return ffn_norm, pre, post, comb
+
+
+def _hc_post(self, moe_out, res_mid, post, comb):
+    """res_out [T, 4, H] 16-bit = post * moe_out + comb^T . res_mid."""
+    import torch
+    res_out = torch.empty_like(res_mid)
+    check(lib().aeon_b200_hc_post(self._h, _ptr(moe_out), moe_out.stride(0), _ptr(res_mid), _ptr(post),
+                                  _ptr(comb), res_mid.shape[0], _ptr(res_out), _stream()))
+    return res_out
+
+
 def _moe_prefill(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum,
                  skip_absent: bool = False):
     check(lib().aeon_b200_moe_prefill(self._h, c_void_p(pool_base), _ptr(slot_of_expert), _ptr(x),
@@ -372,6 +414,8 @@ def _moe_prefill(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accu
 
 
 Context.moe_prefill = _moe_prefill
+Context.hc_ffn_front = _hc_ffn_front
+Context.hc_post = _hc_post
 
 
 def router_topk_noalloc(cfg: MoeConfig, x, gate, weights_out, ids_out, bias=None) -> None:

@@ -81,6 +81,31 @@ def tp_layer_forward(ops, dist, world, x, out_local, partial):
     return weights, ids
 
 
+def layer_body_moe(ctx, w, hc, res_mid, prefill: bool = False):
+    """The FFN half of a layer around the path, all on the device: residual streams
+    res_mid [T, 4, H] 16-bit -> pre-mix + FFN RMSNorm -> router -> shared expert -> routed
+    experts -> post expansion -> res_out [T, 4, H]. Stands in for
+    run_layer_body_moe_router + run_layer_body_moe_and_post
+    (src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:124-312) with the routing kept on
+    the device (the reference copies it to the host per token, :188-192).
+
+    `w` carries gate / shared / pool / slot_of (MoeLayerWeights); `hc` is a dict with the
+    layer's hc_ffn_fn [24, 4H] fp32, hc_ffn_base [24], hc_ffn_scale [3] and ffn_norm weight [H].
+    Returns (res_out, ffn_norm, weights, ids, moe_out)."""
+    import torch
+    ffn_norm, _pre, post, comb = ctx.hc_ffn_front(res_mid, hc["fn"], hc["base"], hc["scale"], hc["norm"])
+    T, H = ffn_norm.shape
+    moe_out = torch.empty(T, H, dtype=torch.float32, device=ffn_norm.device)
+    ctx.shared_expert(w.shared[0], w.shared[1], w.shared[2], ffn_norm, moe_out)
+    weights, ids = ctx.router_topk(ffn_norm, w.gate)
+    if prefill:
+        ctx.moe_prefill(w.pool.base, w.slot_of, ffn_norm, ids, weights, moe_out)
+    else:
+        ctx.moe_decode(w.pool.base, w.slot_of, ffn_norm, ids, weights, moe_out)
+    res_out = ctx.hc_post(moe_out, res_mid, post, comb)
+    return res_out, ffn_norm, weights, ids, moe_out
+
+
 class _DeviceOps:
     """The library's kernels behind the four calls ep_layer_forward needs."""
 

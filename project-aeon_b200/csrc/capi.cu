@@ -490,6 +490,35 @@ int aeon_b200_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32
     });
 }
 
+int aeon_b200_hc_params_default(aeon_b200_hc_params* out) {
+    return guarded([&] {
+        require(out != nullptr, "aeon_b200_hc_params_default: null argument");
+        // src/architecture/deepseek_v4/reference/dsv4_oracle.hpp:489-495; spec/config.hpp:66-70
+        *out = aeon_b200_hc_params{1e-6f, 1e-6f, 1e-6f, 2.0f, 1e-6f, 20};
+    });
+}
+
+int aeon_b200_hc_ffn_front(aeon_b200_ctx* ctx, const void* res_mid, const float* hc_fn, const float* hc_base,
+                           const float* hc_scale3, const void* norm_weight, int tokens,
+                           const aeon_b200_hc_params* params, void* ffn_norm_out, int64_t out_stride,
+                           float* pre_mix_out, float* post_mix_out, float* comb_out, void* stream) {
+    return guarded([&] {
+        require(ctx != nullptr && params != nullptr, "aeon_b200_hc_ffn_front: null context or parameters");
+        DeviceGuard guard(ctx->device);
+        launch_hc_ffn_front(ctx, res_mid, hc_fn, hc_base, hc_scale3, norm_weight, tokens, *params, ffn_norm_out,
+                            out_stride, pre_mix_out, post_mix_out, comb_out, as_stream(stream));
+    });
+}
+
+int aeon_b200_hc_post(aeon_b200_ctx* ctx, const float* moe_out, int64_t moe_stride, const void* res_mid,
+                      const float* post_mix, const float* comb, int tokens, void* res_out, void* stream) {
+    return guarded([&] {
+        require(ctx != nullptr, "aeon_b200_hc_post: null context");
+        DeviceGuard guard(ctx->device);
+        launch_hc_post(ctx, moe_out, moe_stride, res_mid, post_mix, comb, tokens, res_out, as_stream(stream));
+    });
+}
+
 int aeon_b200_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks, int tokens,
                          int hidden, void* stream) {
     return guarded([&] {

@@ -171,6 +171,12 @@ void launch_shared_expert_tc(aeon_b200_ctx* ctx, const void* w1, const void* w3,
                              const void* x, int64_t x_stride, int tokens, float* moe_accum,
                              int64_t accum_stride, cudaStream_t stream);
 void free_shared_tc_scratch(aeon_b200_ctx* ctx);
+void launch_hc_ffn_front(aeon_b200_ctx* ctx, const void* res_mid, const float* hc_fn, const float* hc_base,
+                         const float* hc_scale3, const void* norm_weight, int tokens,
+                         const aeon_b200_hc_params& hp, void* ffn_norm, int64_t out_stride, float* pre_mix,
+                         float* post_mix, float* comb, cudaStream_t stream);
+void launch_hc_post(aeon_b200_ctx* ctx, const float* layer_out, int64_t layer_stride, const void* res_mid,
+                    const float* post_mix, const float* comb, int tokens, void* res_out, cudaStream_t stream);
 void launch_synth_experts(const aeon_b200_moe_config& cfg, void* pool_base, uint32_t first_slot,
                           uint32_t count, uint64_t seed, uint32_t layer, uint32_t first_expert,
                           const uint16_t* scale_table, uint32_t table_n, cudaStream_t stream);
