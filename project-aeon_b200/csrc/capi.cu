@@ -155,7 +155,7 @@ struct DeviceGuard {
 void free_ctx_buffers(aeon_b200_ctx* c) {
     void* bufs[] = {c->d_xperm, c->d_logits, c->d_offsets, c->d_token_idx, c->d_draw_idx, c->d_wpos,
                     c->d_entries, c->d_counts, c->d_hidden_hi, c->d_hidden_lo, c->d_contrib,
-                    c->d_tile_done, c->d_error, c->d_sh_hi, c->d_sh_mid, c->d_sh_lo};
+                    c->d_error, c->d_sh_hi, c->d_sh_mid, c->d_sh_lo};
     for (void* b : bufs)
         if (b) (void)cudaFree(b);
     free_prefill_scratch(c);
@@ -284,7 +284,6 @@ int aeon_b200_ctx_create(const aeon_b200_moe_config* cfg, int device, int max_to
             c->d_hidden_hi = device_alloc<__half>(draws * cfg->intermediate, total);
             c->d_hidden_lo = device_alloc<__half>(draws * cfg->intermediate, total);
             c->d_contrib = device_alloc<float>(draws * cfg->hidden, total);
-            c->d_tile_done = device_alloc<int32_t>(cfg->hidden / 16, total);
             c->d_error = device_alloc<int32_t>(1, total);
             c->d_sh_hi = device_alloc<__half>(T * cfg->intermediate, total);
             c->d_sh_mid = device_alloc<__half>(T * cfg->intermediate, total);

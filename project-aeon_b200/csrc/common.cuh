@@ -114,7 +114,6 @@ struct aeon_b200_ctx {
     __half* d_hidden_hi;    // [max_tokens * k, I]
     __half* d_hidden_lo;    // [max_tokens * k, I]
     float* d_contrib;       // [max_tokens * k, H]
-    int32_t* d_tile_done;   // per output row tile arrival counters
     int32_t* d_error;       // device error flag
     // optional per-kernel timing (events recorded on the caller's stream)
     int timing_enabled;

@@ -51,8 +51,7 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
                           int32_t* __restrict__ token_idx, int32_t* __restrict__ draw_idx,
                           const float* __restrict__ weights, float* __restrict__ wpos,
                           const int32_t* __restrict__ slot_of, WorkEntry* __restrict__ entries,
-                          int32_t* __restrict__ counts, int32_t* __restrict__ tile_done,
-                          int tile_done_n, int skip_absent) {
+                          int32_t* __restrict__ counts, int skip_absent) {
     extern __shared__ int hist[];   // [walk_warps][experts]
     __shared__ int warp_sums[32];
     __shared__ int scan_total;
@@ -62,8 +61,6 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
     const int warp = tid >> 5;
 
     for (int i = tid; i < walk_warps * experts; i += kPermThreads) hist[i] = 0;
-    if (tile_done != nullptr)
-        for (int i = tid; i < tile_done_n; i += kPermThreads) tile_done[i] = 0;
     __syncthreads();
 
     // Chunk of draws per walking warp, a multiple of 32 so a warp step never straddles.
@@ -174,11 +171,9 @@ void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens,
     int walk_warps = std::min(32, std::max(1, (40 * 1024) / (experts * 4)));
     walk_warps = std::min(walk_warps, std::max(1, (draws + 31) / 32));
     const size_t smem = static_cast<size_t>(walk_warps) * experts * sizeof(int);
-    const int tiles = ctx->cfg.hidden / 16;
     expert_permutation_kernel<<<1, kPermThreads, smem, stream>>>(
         topk_ids, draws, slots, experts, walk_warps, expert_offsets, token_indices, draw_indices,
-        weights, weights_by_position, slot_of_expert, entries, counts,
-        entries != nullptr ? ctx->d_tile_done : nullptr, tiles, skip_absent ? 1 : 0);
+        weights, weights_by_position, slot_of_expert, entries, counts, skip_absent ? 1 : 0);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 1;
 }
