@@ -1,0 +1,111 @@
+"""The decode and prefill paths at the benchmark's full size (one layer, all 256 experts,
+batch 128 / 4096 tokens), where the fp64 oracle is too slow to cover every token: properties
+that hold at any size, plus the oracle on a sample of tokens.
+
+  * bit-reproducibility of two runs;
+  * homogeneity in the routing weights: doubling every weight doubles every output bit for
+    bit (one multiply by the weight per draw, fixed-order sums, powers of two are exact);
+  * the accumulator's initial value passes through: out(init) - out(0) == init up to fp32
+    rounding of the sums;
+  * a permutation of the tokens permutes the outputs;
+  * decode path and grouped (prefill) path agree within the tolerance on the same batch;
+  * sampled tokens against the fp64 oracle.
+
+Collected late: it runs after the per-kernel parity tests."""
+import numpy as np
+import pytest
+
+import aeon_b200
+import gpu_support as gs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def full_layer():
+    cfg = aeon_b200.preset("baseline")
+    return cfg, gs.SyntheticLayer(cfg, None, seed=4, layer=5, with_shared=False)
+
+
+def routed(ctx, layer, x, ids, w, init=None, prefill=False):
+    import torch
+    out = torch.zeros(x.shape[0], layer.cfg.hidden, dtype=torch.float32, device="cuda") if init is None \
+        else init.clone()
+    call = ctx.moe_prefill if prefill else ctx.moe_decode
+    call(layer.pool.base, layer.slot_of, x, ids, w, out)
+    ctx.check()
+    return out
+
+
+def test_decode_batch_128_properties(oracle, full_layer):
+    import torch
+    cfg, layer = full_layer
+    T = 128
+    x_bits = gs.activations(cfg, T, seed=21)
+    x = gs.torch_bits(x_bits, cfg.act_dtype)
+    ctx = aeon_b200.Context(cfg, max_tokens=T)
+    w, ids = ctx.router_topk(x, layer.gate)           # the benchmark's own routing (near-uniform load)
+    ids_h, w_h = ids.cpu().numpy(), w.cpu().numpy()
+    assert len(np.unique(ids_h)) > 200                 # the batch touches most of the 256 experts
+
+    base = routed(ctx, layer, x, ids, w)
+    again = routed(ctx, layer, x, ids, w)
+    assert torch.equal(base, again)
+
+    doubled = routed(ctx, layer, x, ids, w * 2.0)
+    assert torch.equal(doubled, base * 2.0)
+
+    init = torch.from_numpy(np.random.default_rng(2).standard_normal((T, cfg.hidden)).astype(np.float32)).cuda()
+    with_init = routed(ctx, layer, x, ids, w, init=init)
+    assert (with_init - base - init).abs().max().item() <= 2e-5 * max(1.0, base.abs().max().item())
+
+    perm = torch.from_numpy(np.random.default_rng(3).permutation(T)).cuda()
+    permuted = routed(ctx, layer, x[perm].contiguous(), ids[perm].contiguous(), w[perm].contiguous())
+    s = oracle.compare(base[perm].double().cpu().numpy(), permuted.double().cpu().numpy())
+    assert s["rel_l2"] <= 1e-6 and s["max_abs"] <= 1e-3, s
+
+    grouped = routed(ctx, layer, x, ids, w, prefill=True)
+    s = oracle.compare(base.double().cpu().numpy(), grouped.double().cpu().numpy())
+    print(f"\nbatch 128: decode vs grouped path max_abs={s['max_abs']:.3e} rel_l2={s['rel_l2']:.3e}")
+    assert s["rel_l2"] <= gs.TOL_REL_L2 and s["max_abs"] <= 2 * gs.TOL_MAX_ABS
+
+    sample = [0, 77, T - 1]
+    want = gs.oracle_routed(oracle, layer, x_bits, ids_h, w_h.astype(np.float64), sample)
+    for t in sample:
+        gs.assert_close(oracle, want[t], base[t].double().cpu().numpy(), f"batch 128 token {t}")
+
+
+def test_prefill_4096_tokens_properties(oracle, full_layer):
+    import torch
+    cfg, layer = full_layer
+    T = 4096
+    x_bits = gs.activations(cfg, T, seed=22)
+    x = gs.torch_bits(x_bits, cfg.act_dtype)
+    ctx = aeon_b200.Context(cfg, max_tokens=128)
+    # Zipf-like skew as in the benchmark's prefill configuration: a per-expert logit bias
+    rank = np.random.default_rng(5).permutation(cfg.experts)
+    bias = torch.from_numpy((0.3 * (1.0 / (1.0 + rank)) ** 1.1 * cfg.experts ** 0.5).astype(np.float32)).cuda()
+    logits = torch.empty(T, cfg.experts, dtype=torch.float32, device="cuda")
+    w, ids = ctx.router_topk(x, layer.gate, bias=bias, logits_out=logits)
+    counts = np.bincount(ids.cpu().numpy().ravel(), minlength=cfg.experts)
+    assert counts.max() > 256 and counts.min() >= 0     # ragged: some experts need several token tiles
+
+    base = routed(ctx, layer, x, ids, w, prefill=True)
+    again = routed(ctx, layer, x, ids, w, prefill=True)
+    assert torch.equal(base, again)
+    doubled = routed(ctx, layer, x, ids, w * 2.0, prefill=True)
+    assert torch.equal(doubled, base * 2.0)
+
+    # the same tokens in chunks of 128 through the decode path
+    ctx_d = aeon_b200.Context(cfg, max_tokens=128)
+    for t0 in (0, 1920, T - 128):
+        part = routed(ctx_d, layer, x[t0:t0 + 128], ids[t0:t0 + 128].contiguous(), w[t0:t0 + 128].contiguous())
+        s = oracle.compare(part.double().cpu().numpy(), base[t0:t0 + 128].double().cpu().numpy())
+        assert s["rel_l2"] <= gs.TOL_REL_L2 and s["max_abs"] <= 2 * gs.TOL_MAX_ABS, (t0, s)
+
+    sample = [0, T - 1]
+    want = gs.oracle_routed(oracle, layer, x_bits, ids.cpu().numpy(), w.cpu().numpy().astype(np.float64), sample)
+    for t in sample:
+        s = oracle.compare(want[t], base[t].double().cpu().numpy())
+        # grouped path: fp16 operand and hidden roundings against the exact oracle
+        assert s["rel_l2"] <= gs.TOL_REL_L2 and s["max_abs"] <= 2 * gs.TOL_MAX_ABS, (t, s)
