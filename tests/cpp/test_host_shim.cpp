@@ -155,6 +155,71 @@ int main(int argc, char** argv) {
         check("container: bad magic refused", throws<std::runtime_error>([&] { bad.open(idx, exp, 2, bytes); }, "magic"));
         std::remove(idx.c_str()); std::remove(exp.c_str());
     }
+    // ---- registry under random traffic against a shadow model ----
+    {
+        const uint32_t layers = 3, experts = 16, slots = 10;
+        ExpertRegistry reg(layers, experts, slots);
+        struct Shadow { int slot{-1}; bool published{false}; uint32_t leases{0}; uint64_t op{0}; };
+        std::vector<Shadow> shadow(layers * experts);
+        uint64_t state = 0x2545F4914F6CDD1Dull;
+        auto rnd = [&](uint32_t n) { state ^= state << 13; state ^= state >> 7; state ^= state << 17; return static_cast<uint32_t>(state % n); };
+        bool ok = true;
+        uint64_t refusals = 0, evictions = 0;
+        for (int step = 0; step < 20000 && ok; ++step) {
+            const uint32_t gid = rnd(layers * experts);
+            Shadow& sh = shadow[gid];
+            switch (rnd(4)) {
+                case 0: {   // request
+                    try {
+                        const ExpertRequestReservation r = reg.reserve_request(gid / experts, gid % experts);
+                        if (sh.slot >= 0 && sh.published) ok &= r.kind == ExpertRequestKind::HOT_HIT && r.vram_slot == sh.slot;
+                        else if (sh.slot >= 0) ok &= r.kind == ExpertRequestKind::PENDING && r.operation_id == sh.op;
+                        else {
+                            ok &= r.kind == ExpertRequestKind::COLD_MISS && r.vram_slot >= 0;
+                            if (r.evicted_global_id >= 0) {
+                                Shadow& v = shadow[r.evicted_global_id];
+                                ok &= v.published && v.leases == 0 && v.slot == r.vram_slot;   // only idle residents lose slots
+                                v = Shadow{};
+                                ++evictions;
+                            }
+                            for (const Shadow& other : shadow) ok &= other.slot != r.vram_slot;      // the slot was really free
+                            sh.slot = r.vram_slot; sh.published = false; sh.op = r.operation_id;
+                        }
+                        ++sh.leases;
+                    } catch (const std::runtime_error&) {
+                        // legal only when no slot is free and every published resident is leased
+                        bool reclaimable = reg.free_vram_slot_count() > 0;
+                        for (const Shadow& o : shadow) reclaimable |= o.published && o.leases == 0;
+                        ok &= !reclaimable && sh.slot < 0;
+                        ++refusals;
+                    }
+                    break;
+                }
+                case 1:     // an upload finishes
+                    if (sh.slot >= 0 && !sh.published) { reg.complete_request(sh.op); sh.published = true; sh.op = 0; }
+                    break;
+                case 2: {   // a lease is returned: the next leased expert at or after the drawn id
+                    uint32_t g = gid;
+                    for (uint32_t i = 0; i < layers * experts && shadow[g].leases == 0; ++i) g = (g + 1) % (layers * experts);
+                    if (shadow[g].leases > 0) { reg.release_lease(g); --shadow[g].leases; }
+                    else ok &= throws<std::logic_error>([&] { reg.release_lease(gid); });
+                    break;
+                }
+                case 3:     // an upload fails (rare)
+                    if (sh.slot >= 0 && !sh.published && rnd(4) == 0) { reg.fail_request(sh.op); sh = Shadow{}; }
+                    break;
+            }
+            ok &= reg.invariants_hold();
+            if (step % 97 == 0)
+                for (uint32_t g = 0; g < layers * experts; ++g)
+                    ok &= reg.slot_of(g / experts, g % experts) == ((shadow[g].published) ? shadow[g].slot : -1) &&
+                          reg.lease_count(g) == shadow[g].leases;
+        }
+        check("20000 random requests / completions / releases / failures agree with a shadow model", ok);
+        std::printf("  (evictions %llu, refusals %llu)\n", static_cast<unsigned long long>(evictions),
+                    static_cast<unsigned long long>(refusals));
+        check("the traffic exercised evictions and full-pool refusals", evictions > 100 && refusals > 0);
+    }
     // ---- shard-aware (version 3) expert container, dense container, loader ----
     {
         aeon_b200_moe_config cfg = moe_config_preset("baseline");

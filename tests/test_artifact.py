@@ -286,3 +286,45 @@ def test_dense_container_round_trip_and_refusals(tmp_path):
         open(path, "wb").write(bad)
         with pytest.raises(ValueError, match=message):
             artifact.DenseContainer(path)
+
+
+def test_shard_packing_properties_over_random_shapes():
+    """Random legal shapes: packing into D shards then unpacking is the identity, every rank's
+    merged slice equals the payload packed from its slice of the source, and the payload bytes of
+    different ranks never overlap."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=25, deadline=None)
+    @given(hidden=st.sampled_from([256, 512, 768]), inter_blocks=st.sampled_from([1, 2, 4, 8]),
+           group=st.sampled_from([32, 128]), shards=st.sampled_from([1, 2, 4, 8]),
+           tp=st.sampled_from([1, 2, 4, 8]), seed=st.integers(0, 2 ** 16))
+    def run(hidden, inter_blocks, group, shards, tp, seed):
+        cfg = aeon_b200.preset("baseline").copy(hidden=hidden, intermediate=256 * inter_blocks, experts=32,
+                                                top_k=4, group_size=group)
+        if inter_blocks % shards:
+            with pytest.raises(aeon_b200.AeonError):
+                aeon_b200.expert_shard_bytes(cfg, shards)
+            return
+        rng = np.random.default_rng(seed)
+        src = [rng.integers(0, 2 ** 32, size=shape, dtype=np.uint64).astype(np.uint32) if i % 2 == 0
+               else rng.integers(0, 2 ** 16, size=shape, dtype=np.uint32).astype(np.uint16)
+               for i, shape in enumerate(aeon_b200.source_shapes(cfg))]
+        payload = aeon_b200.pack_expert_shards(cfg, shards, src)
+        back = aeon_b200.unpack_expert_shards(cfg, shards, payload)
+        assert all(np.array_equal(a, b) for a, b in zip(src, back))
+        if shards % tp:
+            with pytest.raises(aeon_b200.AeonError):
+                aeon_b200.expert_rank_slice(cfg, shards, tp, 0)
+            return
+        cfg_r = cfg.copy(intermediate=cfg.intermediate // tp)
+        covered = np.zeros(payload.size, dtype=np.uint8)
+        for rank in range(tp):
+            off, length = aeon_b200.expert_rank_slice(cfg, shards, tp, rank)
+            covered[off:off + length] += 1
+            merged = aeon_b200.merge_expert_shards(cfg_r, shards // tp, payload[off:off + length])
+            direct = aeon_b200.pack_expert_shards(
+                cfg_r, 1, slice_source(cfg, src, rank * cfg_r.intermediate, cfg_r.intermediate))
+            assert np.array_equal(merged, direct)
+        assert np.all(covered == 1)
+
+    run()
