@@ -350,6 +350,32 @@ int main(int argc, char** argv) {
         check("dense: entry without a shape refused", throws<std::runtime_error>([&] { bad.open(dense_path); }, "Malformed"));
         write_dense(directory + "x", 1, 2);
         check("dense: text after the directory refused", throws<std::runtime_error>([&] { bad.open(dense_path); }, "Malformed"));
+        {
+            // damaged directories: every outcome is either a clean open or a runtime_error
+            uint64_t state = 0x9E3779B97F4A7C15ull;
+            auto rnd = [&](uint32_t n) { state ^= state << 13; state ^= state >> 7; state ^= state << 17; return static_cast<uint32_t>(state % n); };
+            bool contained = true;
+            int opened = 0, refused = 0;
+            for (int trial = 0; trial < 400 && contained; ++trial) {
+                std::string d = directory;
+                const int edits = 1 + static_cast<int>(rnd(3));
+                for (int e = 0; e < edits; ++e) {
+                    const size_t at = rnd(static_cast<uint32_t>(d.size()));
+                    switch (rnd(3)) {
+                        case 0: d[at] = static_cast<char>(32 + rnd(95)); break;
+                        case 1: d.erase(at, 1 + rnd(4)); break;
+                        default: d.insert(at, 1, "[]{}\",:-0123456789"[rnd(19)]); break;
+                    }
+                    if (d.empty()) d = "[";
+                }
+                write_dense(d, 1, 2);
+                try { bad.open(dense_path); ++opened; }
+                catch (const std::runtime_error&) { ++refused; }
+                catch (...) { contained = false; }
+            }
+            std::printf("  (damaged directories: %d opened, %d refused)\n", opened, refused);
+            check("dense: 400 damaged directories are opened or refused, nothing else", contained && refused > 100);
+        }
         std::remove(idx.c_str()); std::remove(exp.c_str()); std::remove(dense_path.c_str());
     }
     // ---- a model directory written by the Python converter (argv[2]), read by this loader ----
