@@ -62,7 +62,9 @@ def test_decode_batch_128_properties(oracle, full_layer):
     perm = torch.from_numpy(np.random.default_rng(3).permutation(T)).cuda()
     permuted = routed(ctx, layer, x[perm].contiguous(), ids[perm].contiguous(), w[perm].contiguous())
     s = oracle.compare(base[perm].double().cpu().numpy(), permuted.double().cpu().numpy())
-    assert s["rel_l2"] <= 1e-6 and s["max_abs"] <= 1e-3, s
+    # not bit-identical: which tokens share a work entry decides whether the hi and lo planes of
+    # the hidden vector meet before or after the K-split sum (fp32 reassociation only)
+    assert s["rel_l2"] <= 5e-6 and s["max_abs"] <= 1e-3, s
 
     grouped = routed(ctx, layer, x, ids, w, prefill=True)
     s = oracle.compare(base.double().cpu().numpy(), grouped.double().cpu().numpy())
