@@ -2,8 +2,8 @@
 post expansion) against the fp64 oracle that is pinned bit-exactly to the reference's
 (oracle/ref_check.cpp), and the whole FFN half of a layer composed on the device.
 
-Collected late on purpose: these kernels were written after the last GPU session of the build
-that added them, so they run after the checks of everything else."""
+Collected late: the composition builds on the router, the shared expert and the routed path, so
+it runs after their own checks."""
 import numpy as np
 import pytest
 
