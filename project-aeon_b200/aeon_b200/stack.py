@@ -35,7 +35,7 @@ def _torch_bits(bits: np.ndarray, dtype: int, device):
     return t.view(torch.bfloat16 if dtype == aeon_b200.BF16 else torch.float16)
 
 
-def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv):
+def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv, group=None):
     """One expert-parallel MoE layer on this rank (the protocol of the module docstring).
 
     `ops` supplies the compute: router(x) -> (weights, ids); shared(x, out) writes the shared
@@ -43,16 +43,78 @@ def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv)
     contributions; combine(out, recv) adds recv[r] for r = 0..world-1 in that order. The
     collectives are `dist`'s (NCCL on GPUs; gloo in the CPU tests of the protocol).
     Returns the (replicated) routing of the whole batch."""
-    dist.all_gather_into_tensor(x_all, x_local)                 # dispatch
+    scope = {} if group is None else {"group": group}          # the ranks of one pipeline stage
+    dist.all_gather_into_tensor(x_all, x_local, **scope)        # dispatch
     weights, ids = ops.router(x_all)                            # replicated, identical inputs
     ops.shared(x_local, out_local)
     partial.zero_()
     ops.routed(x_all, ids, weights, partial, skip_absent=True)
     if not recv.is_contiguous():
         raise ValueError("the receive buffer must be a dense [world, tokens_local, hidden] block")
-    dist.all_to_all_single(recv.view(-1, recv.shape[-1]), partial)   # combine: rows to owners
+    dist.all_to_all_single(recv.view(-1, recv.shape[-1]), partial, **scope)   # combine: rows to owners
     ops.combine(out_local, recv)
     return weights, ids
+
+
+class StageTopology:
+    """One process per GPU, `world` ranks as `pp` pipeline stages of world / pp ranks each
+    (expert- or tensor-parallel inside a stage). Stage-major like the reference's topology
+    (src/infrastructure/parallel/parallel_topology.hpp:166-199): global rank = stage *
+    ranks_per_stage + rank_in_stage; layers split contiguously, remainder to the earliest stages.
+    The peer of a rank in the next stage is the rank with the same index inside that stage, so a
+    hand-off moves each rank's own token rows and nothing else."""
+
+    def __init__(self, world: int, pp: int, layers: int):
+        if pp < 1 or world < 1 or world % pp:
+            raise ValueError(f"pipeline_parallel={pp} does not divide the {world} ranks")
+        if pp > layers:
+            raise ValueError(f"pipeline_parallel={pp} exceeds the {layers} model layers")
+        self.world, self.pp, self.layers = world, pp, layers
+        self.ranks_per_stage = world // pp
+        base, rem = divmod(layers, pp)
+        self._ranges, first = [], 0
+        for stage in range(pp):
+            count = base + (1 if stage < rem else 0)
+            self._ranges.append(range(first, first + count))
+            first += count
+
+    def stage_of_rank(self, rank: int) -> int:
+        return rank // self.ranks_per_stage
+
+    def rank_in_stage(self, rank: int) -> int:
+        return rank % self.ranks_per_stage
+
+    def stage_ranks(self, stage: int):
+        return list(range(stage * self.ranks_per_stage, (stage + 1) * self.ranks_per_stage))
+
+    def stage_layers(self, stage: int) -> range:
+        return self._ranges[stage]
+
+    def stage_of_layer(self, layer: int) -> int:
+        for stage, r in enumerate(self._ranges):
+            if layer in r:
+                return stage
+        raise IndexError("layer out of range")
+
+    def peer(self, rank: int, stage: int) -> int:
+        return stage * self.ranks_per_stage + self.rank_in_stage(rank)
+
+
+def pipeline_forward(topo: StageTopology, dist, rank: int, carry, run_layers):
+    """One pass of a pipelined stack on this rank: receive the carried rows from the previous
+    stage (a byte copy, as the reference's stage hand-off is,
+    src/architecture/deepseek_v4/runtime/v4_graph.hpp:454-513, so the pipelined result equals the
+    single-stage one bit for bit), run this stage's layers with `run_layers(carry, layers)`, and
+    send the result on. Returns the carry on the last stage, None elsewhere. The point-to-point
+    calls are `dist`'s (NCCL send/recv between the GPUs; gloo in the CPU tests)."""
+    stage = topo.stage_of_rank(rank)
+    if stage > 0:
+        dist.recv(carry, src=topo.peer(rank, stage - 1))
+    carry = run_layers(carry, topo.stage_layers(stage))
+    if stage + 1 < topo.pp:
+        dist.send(carry, dst=topo.peer(rank, stage + 1))
+        return None
+    return carry
 
 
 def tp_layer_forward(ops, dist, world, x, out_local, partial):

@@ -159,3 +159,98 @@ def test_combine_buffer_must_be_dense():
         stack.ep_layer_forward(moe, Dummy(), 1, x, torch.empty(T, H, dtype=torch.float64),
                                torch.empty(T, H, dtype=torch.float64),
                                torch.empty(T, H, dtype=torch.float64), recv)
+
+
+# ---- pipeline stages x expert parallel under one topology -------------------------------------
+LAYERS = 5
+
+
+class TinyLayer(TinyMoe):
+    """TinyMoe with per-layer weights (seeded by the layer id)."""
+
+    def __init__(self, layer, owned):
+        super().__init__(owned)
+        g = torch.Generator().manual_seed(100 + layer)
+        self.gate = torch.randn(E, H, generator=g, dtype=torch.float64)
+        self.w1 = torch.randn(E, I, H, generator=g, dtype=torch.float64) * 0.3
+        self.w3 = torch.randn(E, I, H, generator=g, dtype=torch.float64) * 0.3
+        self.w2 = torch.randn(E, H, I, generator=g, dtype=torch.float64) * 0.3
+        self.sw = torch.randn(H, H, generator=g, dtype=torch.float64) * 0.1
+
+
+def single_rank_stack(x):
+    routing = []
+    for layer in range(LAYERS):
+        moe = TinyLayer(layer, range(E))
+        w, ids = moe.router(x)
+        out = torch.empty(T, H, dtype=torch.float64)
+        moe.shared(x, out)
+        moe.routed(x, ids, w, out, skip_absent=False)
+        x = x + 0.1 * out
+        routing.append(ids)
+    return x, routing
+
+
+def pp_worker(rank, world, pp, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        topo = stack.StageTopology(world, pp, LAYERS)
+        # every rank creates every stage's group, in the same order (a collective call)
+        groups = [dist.new_group(topo.stage_ranks(s)) for s in range(pp)]
+        stage, r = topo.stage_of_rank(rank), topo.rank_in_stage(rank)
+        ep = topo.ranks_per_stage
+        tl, per = T // ep, E // ep
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(7), dtype=torch.float64)
+        carry = x[r * tl:(r + 1) * tl].contiguous() if stage == 0 else torch.empty(tl, H, dtype=torch.float64)
+        seen = []
+
+        def run_layers(rows, layers):
+            for layer in layers:
+                moe = TinyLayer(layer, range(r * per, (r + 1) * per))
+                out_local = torch.empty(tl, H, dtype=torch.float64)
+                x_all = torch.empty(T, H, dtype=torch.float64)
+                partial = torch.empty(T, H, dtype=torch.float64)
+                recv = torch.empty(ep, tl, H, dtype=torch.float64)
+                _, ids = stack.ep_layer_forward(moe, dist, ep, rows, out_local, x_all, partial, recv,
+                                                group=groups[stage])
+                rows = rows + 0.1 * out_local
+                seen.append((layer, ids))
+            return rows
+
+        final = stack.pipeline_forward(topo, dist, rank, carry, run_layers)
+        want, want_routing = single_rank_stack(x)
+        ok = all(torch.equal(ids, want_routing[layer]) for layer, ids in seen)
+        ok = ok and [layer for layer, _ in seen] == list(topo.stage_layers(stage))
+        if stage == pp - 1:
+            err = (final - want[r * tl:(r + 1) * tl]).abs().max().item()
+            ok = ok and err < 1e-12
+        else:
+            ok = ok and final is None
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,pp", [(2, 2), (4, 2), (4, 4)])
+def test_pipeline_stages_compose_with_expert_parallel(world, pp):
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(pp_worker, args=(world, pp, free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {rank: True for rank in range(world)}
+
+
+def test_stage_topology_rules():
+    topo = stack.StageTopology(8, 2, 43)
+    assert list(topo.stage_layers(0)) == list(range(22)) and list(topo.stage_layers(1)) == list(range(22, 43))
+    assert topo.stage_ranks(1) == [4, 5, 6, 7] and topo.peer(2, 1) == 6 and topo.stage_of_rank(5) == 1
+    assert topo.stage_of_layer(21) == 0 and topo.stage_of_layer(22) == 1
+    for pp in (1, 2, 3, 4):
+        t = stack.StageTopology(12, pp, 43)
+        counts = [len(t.stage_layers(s)) for s in range(pp)]
+        assert sum(counts) == 43 and counts == sorted(counts, reverse=True)
+    with pytest.raises(ValueError, match="does not divide"):
+        stack.StageTopology(8, 3, 43)
+    with pytest.raises(ValueError, match="exceeds"):
+        stack.StageTopology(64, 64, 43)
