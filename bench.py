@@ -42,12 +42,14 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/8/32/128 sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default="full", choices=["full", "small", "b1", "prefill_small", "tp"],
+    ap.add_argument("--case", default="full", choices=["full", "small", "small128", "b1", "prefill_small", "tp"],
                     help="small: one layer of 64 experts at batch 32 (1.45 GB of weights, larger "
                          "than L2), the case the ncu captures under profiles/ run; not a bench value")
     args = ap.parse_args()
     if args.case == "small":
         args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 32, True, True
+    if args.case == "small128":   # the same layer at batch 128: the shared expert takes its tensor-core form
+        args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 128, True, True
     if args.case == "prefill_small":   # 64 experts, 512 tokens through the grouped GEMMs (ncu captures)
         args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 8, True, True
     if args.case == "b1":      # configuration 1 at batch 1 over 8 layers (launch lists)
@@ -355,7 +357,7 @@ def main():
             print(json.dumps(line), flush=True)
         shutdown(dist)
         return
-    if args.case in ("small", "prefill_small"):
+    if args.case in ("small", "small128", "prefill_small"):
         cfg = cfg.copy(experts=64)
     model = stack.MoeStack(cfg, layers=args.layers, max_tokens=args.batch, seed=SEED,
                            device=local_rank, rank=rank, world=world, dist=dist)
