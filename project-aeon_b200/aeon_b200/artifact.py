@@ -311,6 +311,13 @@ class DenseContainer:
     def dtype_of(self, name: str) -> str:
         return self._tensors[name][2]
 
+    def raw(self, name: str) -> np.ndarray:
+        """The tensor's bytes, whatever its element type."""
+        if name not in self._tensors:
+            raise KeyError("AeonModelLoader: Missing dense tensor: " + name)
+        off, size, _, _ = self._tensors[name]
+        return self._data[off:off + size]
+
 
 def moe_layer_tensor_names(layer: int, hash_layer: bool = False) -> dict:
     """Names of the dense tensors the path reads for one layer."""
@@ -321,20 +328,183 @@ def moe_layer_tensor_names(layer: int, hash_layer: bool = False) -> dict:
     return names
 
 
+# ---------------------------------------------------------------------------------------------
+# Checkpoint front end: safetensors shards -> the two containers
+# ---------------------------------------------------------------------------------------------
+_ST_SIZES = {"BF16": 2, "F16": 2, "F32": 4, "F64": 8, "I64": 8, "I32": 4, "U32": 4, "I16": 2, "U16": 2,
+             "I8": 1, "U8": 1, "BOOL": 1, "F8_E4M3": 1, "F8_E5M2": 1}
+
+
+class SafetensorsFile:
+    """One safetensors shard, read without interpreting the element types (bf16 has no numpy
+    type): u64 header length, JSON header {name: {dtype, shape, data_offsets}}, then the bytes."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self._data = np.memmap(path, dtype=np.uint8, mode="r")
+        if self._data.size < 8:
+            raise ValueError("safetensors: file too small: " + path)
+        (n,) = struct.unpack("<Q", self._data[:8].tobytes())
+        if n > self._data.size - 8:
+            raise ValueError("safetensors: header length exceeds the file: " + path)
+        header = json.loads(self._data[8:8 + n].tobytes().decode("utf-8"))
+        self._base = 8 + n
+        self.tensors = {}
+        for name, meta in header.items():
+            if name == "__metadata__":
+                continue
+            start, end = meta["data_offsets"]
+            shape = tuple(int(d) for d in meta["shape"])
+            count = int(np.prod(shape)) if shape else 1
+            if meta["dtype"] not in _ST_SIZES or end - start != count * _ST_SIZES[meta["dtype"]]:
+                raise ValueError(f"safetensors: tensor {name} has an inconsistent size in {path}")
+            if end > self._data.size - self._base or start > end:
+                raise ValueError(f"safetensors: tensor {name} lies outside {path}")
+            self.tensors[name] = (meta["dtype"], shape, start, end)
+
+    def raw(self, name: str) -> np.ndarray:
+        _, _, start, end = self.tensors[name]
+        return self._data[self._base + start:self._base + end]
+
+
+class SafetensorsCheckpoint:
+    """A checkpoint directory: `model.safetensors.index.json` (weight_map: tensor -> shard) or a
+    single `model.safetensors` (the source side of scripts/convert_safetensors_to_aeon.py:196-260)."""
+
+    def __init__(self, model_dir: str):
+        self.model_dir = model_dir
+        index_path = os.path.join(model_dir, "model.safetensors.index.json")
+        self._files = {}
+        if os.path.exists(index_path):
+            with open(index_path, "r", encoding="utf-8") as f:
+                weight_map = json.load(f).get("weight_map", {})
+            self._where = dict(weight_map)
+        else:
+            single = os.path.join(model_dir, "model.safetensors")
+            if not os.path.exists(single):
+                raise FileNotFoundError("Missing Safetensors index: " + index_path)
+            self._where = {name: "model.safetensors" for name in self._file("model.safetensors").tensors}
+        for name, shard in self._where.items():
+            if name not in self._file(shard).tensors:
+                raise KeyError(f"Missing tensor in Safetensors: {name} (expected in {shard})")
+
+    def _file(self, shard: str) -> SafetensorsFile:
+        if shard not in self._files:
+            self._files[shard] = SafetensorsFile(os.path.join(self.model_dir, shard))
+        return self._files[shard]
+
+    def names(self):
+        return sorted(self._where)
+
+    def meta(self, name: str):
+        if name not in self._where:
+            raise KeyError("Missing tensor in Safetensors: " + name)
+        dtype, shape, _, _ = self._file(self._where[name]).tensors[name]
+        return dtype, shape
+
+    def raw(self, name: str) -> np.ndarray:
+        if name not in self._where:
+            raise KeyError("Missing tensor in Safetensors: " + name)
+        return self._file(self._where[name]).raw(name)
+
+
+def convert_checkpoint(source_dir: str, output_dir: str, cfg, max_tensor_parallel: int = 1,
+                       max_layers: int | None = None, verify: bool = True) -> ExpertFormat:
+    """safetensors checkpoint -> model_dense.aeon + model_experts_swizzled.{aeon,index} + manifest.
+
+    Routed experts are the tensors `layers.L.ffn.experts.E.{w1,w2,w3}.{weight_packed,weight_scale}`
+    (packed words [N, K/8], fp16 scales [N, K/group]; scripts/convert_safetensors_to_aeon.py:489-511);
+    every other tensor goes to the dense container byte for byte (:361-364). With
+    max_tensor_parallel > 1 the experts are written shard-aware (index version 3)."""
+    ckpt = SafetensorsCheckpoint(source_dir)
+    names = ckpt.names()
+    routed = [n for n in names if ".ffn.experts." in n and "shared_experts" not in n]
+    layer_ids = sorted({int(n.split(".")[1]) for n in routed})
+    if not layer_ids or layer_ids != list(range(len(layer_ids))):
+        raise ValueError("checkpoint: routed-expert layers must be numbered 0..L-1")
+    layers = len(layer_ids) if max_layers is None else min(max_layers, len(layer_ids))
+    shapes = aeon_b200.source_shapes(cfg)
+
+    def source_of(layer, expert):
+        out = []
+        for i, (w, t) in enumerate((("w1", "weight_packed"), ("w1", "weight_scale"), ("w2", "weight_packed"),
+                                    ("w2", "weight_scale"), ("w3", "weight_packed"), ("w3", "weight_scale"))):
+            key = f"layers.{layer}.ffn.experts.{expert}.{w}.{t}"
+            dtype, shape = ckpt.meta(key)
+            want = ("I32", "U32") if i % 2 == 0 else ("F16",)
+            if dtype not in want or tuple(shape) != shapes[i]:
+                raise ValueError(f"checkpoint: {key} is {dtype}{list(shape)}, expected {want[0]}{list(shapes[i])}")
+            out.append(np.asarray(ckpt.raw(key)).view(np.uint32 if i % 2 == 0 else np.uint16).reshape(shapes[i]))
+        return out
+
+    fmt = write_expert_artifact(output_dir, cfg, layers, source_of, max_tensor_parallel)
+
+    def keep(name):
+        if name in routed:
+            return False
+        if max_layers is not None and name.startswith("layers."):
+            return int(name.split(".")[1]) < max_layers
+        return True
+
+    dense = []
+    for name in names:
+        if keep(name):
+            dtype, shape = ckpt.meta(name)
+            dense.append((name, dtype, shape, ckpt.raw(name)))
+    _write_dense_raw(os.path.join(output_dir, DENSE_FILENAME), dense)
+    for aux in ("config.json", "generation_config.json", "tokenizer.json", "tokenizer_config.json"):
+        src = os.path.join(source_dir, aux)
+        if os.path.isfile(src):
+            with open(src, "rb") as fi, open(os.path.join(output_dir, aux), "wb") as fo:
+                fo.write(fi.read())
+    if verify:
+        verify_conversion(output_dir, cfg, source_of)
+        back = DenseContainer(os.path.join(output_dir, DENSE_FILENAME))
+        for name, dtype, shape, raw in dense:
+            if back.dtype_of(name) != dtype or back.raw(name).tobytes() != np.asarray(raw).tobytes():
+                raise ValueError("verify_conversion: dense tensor does not round-trip: " + name)
+    return fmt
+
+
+def _write_dense_raw(path: str, tensors) -> None:
+    """tensors: (name, dtype string, shape, raw uint8 bytes); any safetensors dtype passes through."""
+    directory, offset = [], 0
+    for name, dtype, shape, raw in tensors:
+        directory.append({"name": name, "offset": offset, "size": int(raw.size), "dtype": dtype,
+                          "shape": [int(d) for d in shape]})
+        offset += int(raw.size)
+    dir_json = json.dumps(directory, indent=2).encode("utf-8")
+    head = struct.pack("<12sIIQ", DENSE_MAGIC, DENSE_FORMAT_VERSION, len(directory), len(dir_json))
+    pad = (-(len(head) + len(dir_json))) % SECTOR_SIZE
+    with open(path, "wb") as f:
+        f.write(head)
+        f.write(dir_json)
+        f.write(b"\x00" * pad)
+        for _, _, _, raw in tensors:
+            f.write(np.asarray(raw).tobytes())
+
+
 def _main(argv=None) -> int:
     import argparse
     ap = argparse.ArgumentParser(
         prog="python -m aeon_b200.artifact",
-        description="Rewrite an expert container with shard-aware (version 3) payloads.")
+        description="Rewrite an expert container with shard-aware (version 3) payloads, or, with "
+                    "--from-safetensors, convert a safetensors checkpoint into the two containers.")
     ap.add_argument("source_dir")
     ap.add_argument("output_dir")
+    ap.add_argument("--from-safetensors", action="store_true")
+    ap.add_argument("--max-layers", type=int, default=None)
     ap.add_argument("--preset", default="ref_dsv4", help="shape preset of the experts (ref_dsv4, baseline)")
     ap.add_argument("--max-tensor-parallel", type=int, default=8, choices=(1, 2, 4, 8))
     ap.add_argument("--no-verify", action="store_true")
     args = ap.parse_args(argv)
     cfg = aeon_b200.preset(args.preset)
-    fmt = reshard_expert_artifact(args.source_dir, args.output_dir, cfg, args.max_tensor_parallel,
-                                  verify=not args.no_verify)
+    if args.from_safetensors:
+        fmt = convert_checkpoint(args.source_dir, args.output_dir, cfg, args.max_tensor_parallel,
+                                 max_layers=args.max_layers, verify=not args.no_verify)
+    else:
+        fmt = reshard_expert_artifact(args.source_dir, args.output_dir, cfg, args.max_tensor_parallel,
+                                      verify=not args.no_verify)
     print(f"wrote {fmt.num_layers} x {fmt.experts_per_layer} experts, version {fmt.version}, "
           f"{fmt.shard_count} shards of {fmt.shard_bytes} bytes")
     return 0

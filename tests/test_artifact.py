@@ -328,3 +328,92 @@ def test_shard_packing_properties_over_random_shapes():
         assert np.all(covered == 1)
 
     run()
+
+
+def write_safetensors(path, tensors):
+    """Minimal writer of the safetensors layout: u64 header length, JSON header, raw bytes."""
+    header, blobs, offset = {}, [], 0
+    for name, (dtype, array) in tensors.items():
+        raw = np.ascontiguousarray(array).tobytes()
+        header[name] = {"dtype": dtype, "shape": list(array.shape), "data_offsets": [offset, offset + len(raw)]}
+        blobs.append(raw)
+        offset += len(raw)
+    head = json.dumps(header).encode("utf-8")
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for raw in blobs:
+            f.write(raw)
+
+
+def test_safetensors_checkpoint_to_containers(tmp_path):
+    """A two-shard checkpoint with the reference's tensor names becomes the dense container, the
+    expert container (here shard-aware, D = 2) and a manifest; everything reads back bit-exactly
+    (the conversion the reference's scripts/convert_safetensors_to_aeon.py performs for version 2)."""
+    cfg = aeon_b200.preset("baseline").copy(hidden=256, intermediate=512, experts=32, top_k=4)
+    layers = 2
+    src_dir, out_dir = tmp_path / "hf", tmp_path / "aeon"
+    src_dir.mkdir()
+    rng = np.random.default_rng(17)
+    shards = [{}, {}]
+    weight_map = {}
+    sources = {}
+    names6 = (("w1", "weight_packed"), ("w1", "weight_scale"), ("w2", "weight_packed"), ("w2", "weight_scale"),
+              ("w3", "weight_packed"), ("w3", "weight_scale"))
+    for layer in range(layers):
+        for expert in range(cfg.experts):
+            src = source_tensors(cfg, layer, expert)
+            sources[(layer, expert)] = src
+            for (w, t), arr in zip(names6, src):
+                name = f"layers.{layer}.ffn.experts.{expert}.{w}.{t}"
+                shards[layer][name] = ("I32" if t == "weight_packed" else "F16", arr)
+                weight_map[name] = f"model-{layer}.safetensors"
+        dense = {
+            f"layers.{layer}.ffn.gate.weight": ("BF16", rng.integers(0, 2 ** 16, (cfg.experts, cfg.hidden), dtype=np.uint16)),
+            f"layers.{layer}.ffn.gate.bias": ("F32", rng.standard_normal(cfg.experts).astype(np.float32)),
+            f"layers.{layer}.ffn.shared_experts.w1.weight": ("BF16", rng.integers(0, 2 ** 16, (cfg.intermediate, cfg.hidden), dtype=np.uint16)),
+            f"layers.{layer}.ffn_norm.weight": ("BF16", rng.integers(0, 2 ** 16, (cfg.hidden,), dtype=np.uint16)),
+        }
+        for name, value in dense.items():
+            shards[layer][name] = value
+            weight_map[name] = f"model-{layer}.safetensors"
+    shards[0]["embed.weight"] = ("BF16", rng.integers(0, 2 ** 16, (64, cfg.hidden), dtype=np.uint16))
+    weight_map["embed.weight"] = "model-0.safetensors"
+    for i, tensors in enumerate(shards):
+        write_safetensors(src_dir / f"model-{i}.safetensors", tensors)
+    (src_dir / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    (src_dir / "config.json").write_text(json.dumps({"model_type": "deepseek_v4"}))
+
+    fmt = artifact.convert_checkpoint(str(src_dir), str(out_dir), cfg, max_tensor_parallel=2)
+    assert (fmt.version, fmt.num_layers, fmt.shard_count) == (3, layers, 2)
+    art = artifact.ExpertArtifact(str(out_dir))
+    for key in ((0, 0), (1, 31)):
+        back = aeon_b200.unpack_expert_shards(cfg, 2, np.asarray(art.expert_data(*key)))
+        assert all(np.array_equal(a, b) for a, b in zip(back, sources[key]))
+    dense = artifact.DenseContainer(str(out_dir / artifact.DENSE_FILENAME))
+    want_dense = {n for n in weight_map if ".ffn.experts." not in n}
+    assert set(dense.names()) == want_dense and "layers.1.ffn.shared_experts.w1.weight" in want_dense
+    for name in want_dense:
+        dtype, array = shards[0].get(name) or shards[1][name]
+        assert dense.dtype_of(name) == dtype and dense.raw(name).tobytes() == array.tobytes()
+    assert json.load(open(out_dir / "config.json"))["model_type"] == "deepseek_v4"
+    assert json.load(open(out_dir / artifact.MANIFEST_FILENAME))["max_tensor_parallel"] == 2
+
+    # the command-line form, first layer only
+    one = tmp_path / "one"
+    import unittest.mock as mock
+    with mock.patch.object(aeon_b200, "preset", lambda name: cfg):
+        assert artifact._main([str(src_dir), str(one), "--from-safetensors", "--max-tensor-parallel", "1",
+                               "--max-layers", "1"]) == 0
+    first = artifact.ExpertArtifact(str(one))
+    assert (first.format.version, first.format.num_layers) == (2, 1)
+    assert set(artifact.DenseContainer(str(one / artifact.DENSE_FILENAME)).names()) == \
+        {n for n in want_dense if not n.startswith("layers.1.")}
+
+    # refusals: a missing expert tensor, a wrong shape
+    del weight_map["layers.1.ffn.experts.7.w2.weight_scale"]
+    (src_dir / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    with pytest.raises(KeyError, match="Missing tensor"):
+        artifact.convert_checkpoint(str(src_dir), str(tmp_path / "bad"), cfg)
+    with pytest.raises(ValueError, match="expected"):
+        artifact.convert_checkpoint(str(src_dir), str(tmp_path / "bad2"), cfg.copy(hidden=512), max_layers=1)
