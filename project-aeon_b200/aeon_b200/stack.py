@@ -159,7 +159,7 @@ def layer_body_moe(ctx, w, hc, res_mid, prefill: bool = False):
     T, H = ffn_norm.shape
     moe_out = torch.empty(T, H, dtype=torch.float32, device=ffn_norm.device)
     ctx.shared_expert(w.shared[0], w.shared[1], w.shared[2], ffn_norm, moe_out)
-    weights, ids = ctx.router_topk(ffn_norm, w.gate)
+    weights, ids = ctx.router_topk(ffn_norm, w.gate, bias=getattr(w, "gate_bias", None))
     if prefill:
         ctx.moe_prefill(w.pool.base, w.slot_of, ffn_norm, ids, weights, moe_out)
     else:
@@ -210,6 +210,63 @@ class MoeLayerWeights:
             t = torch.empty(n, dtype=torch.int16, device=dev)
             aeon_b200.synth_fill_dense16(t, seed, layer, stream_id, dense_table)
             self.shared.append(t)
+
+
+class LoadedLayer:
+    """One layer's weights for the path, read from a model directory (the dense and the expert
+    container, aeon_b200.artifact) onto a device: gate (+ bias or hash table), shared expert,
+    the hyper-connection / norm tensors of the FFN half, and this rank's experts in a pool.
+    Takes the place of the per-layer uploads of
+    src/architecture/deepseek_v4/spec/v4_dense_weight_binding.hpp:86-137 and of the expert
+    supply's initial fill. `tp` > 1 loads the rank's slice of every expert through
+    rank_slice (the pool's configuration then has intermediate / tp); `experts` limits the
+    resident set (default: all)."""
+
+    def __init__(self, cfg, model_dir: str, layer: int, device: int = 0, experts=None, tp: int = 1,
+                 tp_rank: int = 0):
+        import os
+        import torch
+        from aeon_b200 import artifact
+        dev = f"cuda:{device}"
+        self.cfg = cfg
+        self.cfg_rank = cfg.copy(intermediate=cfg.intermediate // tp)
+        dense = artifact.DenseContainer(os.path.join(model_dir, artifact.DENSE_FILENAME))
+        art = artifact.ExpertArtifact(model_dir)
+        names = artifact.moe_layer_tensor_names(layer)
+        prefix = f"layers.{layer}."
+
+        def bits16(name):
+            want = "BF16" if cfg.act_dtype == aeon_b200.BF16 else "F16"
+            if dense.dtype_of(name) != want:
+                raise aeon_b200.AeonError(1, f"{name} is {dense.dtype_of(name)}, the configuration wants {want}")
+            raw = np.asarray(dense.raw(name)).view(np.uint16)
+            return raw, _torch_bits(raw, cfg.act_dtype, dev)
+
+        def f32(name):
+            return torch.from_numpy(np.asarray(dense.raw(name)).view(np.float32).copy()).to(dev)
+
+        self.gate_bits, self.gate = bits16(names["gate"])
+        self.gate_bits = self.gate_bits.reshape(cfg.experts, cfg.hidden)
+        self.gate = self.gate.reshape(cfg.experts, cfg.hidden)
+        self.gate_bias = f32(names["gate_bias"]) if dense.has_tensor(names["gate_bias"]) else None
+        self.shared_bits, self.shared = [], []
+        for key in ("shared_w1", "shared_w3", "shared_w2"):
+            b, t = bits16(names[key])
+            self.shared_bits.append(b)
+            self.shared.append(t.view(torch.int16))
+        self.hc = None
+        if dense.has_tensor(prefix + "hc_ffn_fn"):
+            norm_bits, norm = bits16(prefix + "ffn_norm.weight")
+            self.hc = dict(fn=f32(prefix + "hc_ffn_fn").reshape(24, 4 * cfg.hidden), base=f32(prefix + "hc_ffn_base"),
+                           scale=f32(prefix + "hc_ffn_scale"), norm=norm, norm_bits=norm_bits)
+        resident = list(range(cfg.experts)) if experts is None else list(experts)
+        self.pool = aeon_b200.ExpertPool(self.cfg_rank, len(resident), device)
+        slot_of = np.full(cfg.experts, -1, dtype=np.int32)
+        for slot, e in enumerate(resident):
+            self.pool.upload(slot, art.rank_payload(cfg, layer, e, tp, tp_rank))
+            slot_of[e] = slot
+        self.slot_of = torch.from_numpy(slot_of).to(dev)
+        self.artifact = art
 
 
 class MoeStack:

@@ -103,3 +103,70 @@ def test_ffn_half_of_a_layer_on_the_device(oracle):
         # one spacing of the 16-bit type plus the path's own tolerance scaled by the post gate
         bound = ulp16(want_out, cfg.act_dtype) + gs.TOL_MAX_ABS * np.abs(front["post"]).max()
         assert np.all(np.abs(got_out[t] - want_out) <= bound.reshape(4, H))
+
+
+def test_checkpoint_to_device_to_residual_out(tmp_path, oracle):
+    """The whole chain a deployment runs: a safetensors checkpoint with the reference's tensor
+    names -> the two containers (aeon_b200.artifact.convert_checkpoint) -> device weights
+    (stack.LoadedLayer) -> residual streams through the FFN half of the layer, against the
+    oracle evaluated on the checkpoint's own tensors. Small shapes through the grouped path."""
+    import json
+    import torch
+    from aeon_b200 import artifact
+    from test_artifact import source_tensors, write_safetensors
+    cfg = aeon_b200.preset("baseline").copy(hidden=1024, intermediate=512, experts=32, top_k=4)
+    H, I, tokens = cfg.hidden, cfg.intermediate, 6
+    rng = np.random.default_rng(31)
+    tensors = {}
+    names6 = (("w1", "weight_packed"), ("w1", "weight_scale"), ("w2", "weight_packed"), ("w2", "weight_scale"),
+              ("w3", "weight_packed"), ("w3", "weight_scale"))
+    for e in range(cfg.experts):
+        for (w, t), arr in zip(names6, source_tensors(cfg, 0, e)):
+            tensors[f"layers.0.ffn.experts.{e}.{w}.{t}"] = ("I32" if t == "weight_packed" else "F16", arr)
+    gate_bits = synth.normal_bits(rng, (cfg.experts, H), 0.05, cfg.act_dtype)
+    shared_bits = [synth.normal_bits(rng, shape, 0.02, cfg.act_dtype) for shape in ((I, H), (I, H), (H, I))]
+    fn = (rng.standard_normal((24, 4 * H)) * 0.02).astype(np.float32)
+    base = (rng.standard_normal(24) * 0.5).astype(np.float32)
+    scale = (0.5 + rng.random(3)).astype(np.float32)
+    norm_bits = synth.to_bits16(1.0 + 0.1 * rng.standard_normal(H), cfg.act_dtype)
+    tensors.update({
+        "layers.0.ffn.gate.weight": ("BF16", gate_bits),
+        "layers.0.ffn.shared_experts.w1.weight": ("BF16", shared_bits[0]),
+        "layers.0.ffn.shared_experts.w3.weight": ("BF16", shared_bits[1]),
+        "layers.0.ffn.shared_experts.w2.weight": ("BF16", shared_bits[2]),
+        "layers.0.hc_ffn_fn": ("F32", fn), "layers.0.hc_ffn_base": ("F32", base),
+        "layers.0.hc_ffn_scale": ("F32", scale), "layers.0.ffn_norm.weight": ("BF16", norm_bits),
+    })
+    src_dir, out_dir = tmp_path / "hf", tmp_path / "aeon"
+    src_dir.mkdir()
+    write_safetensors(src_dir / "model.safetensors", tensors)
+    artifact.convert_checkpoint(str(src_dir), str(out_dir), cfg)
+
+    layer = stack.LoadedLayer(cfg, str(out_dir), 0)
+    ctx = aeon_b200.Context(cfg, max_tokens=tokens)
+    res_bits = synth.normal_bits(rng, (tokens, 4, H), 1.0, cfg.act_dtype)
+    d_res = gs.torch_bits(res_bits.reshape(tokens, 4 * H), cfg.act_dtype).reshape(tokens, 4, H)
+    res_out, ffn_norm, weights, ids, moe_out = stack.layer_body_moe(ctx, layer, layer.hc, d_res, prefill=True)
+    ctx.check()
+
+    x_bits = ffn_norm.view(torch.int16).cpu().numpy().view(np.uint16)
+    ids_h, w_h = ids.cpu().numpy(), weights.cpu().numpy().astype(np.float64)
+    logits = oracle.router_logits_f32_ordered(gate_bits, cfg.act_dtype, x_bits, cfg.act_dtype)
+    want_ids, _, _ = oracle.router_topk(logits.astype(np.float64), None, cfg.top_k, cfg.routed_scaling, cfg.score_fn)
+    np.testing.assert_array_equal(ids_h, want_ids)
+    la = oracle.layout_args(cfg)
+    x = synth.from_bits16(x_bits, cfg.act_dtype)
+    res = synth.from_bits16(res_bits, cfg.act_dtype)
+    norm_w = synth.from_bits16(norm_bits, cfg.act_dtype)
+    got_out = synth.from_bits16(res_out.view(torch.int16).cpu().numpy().view(np.uint16), cfg.act_dtype)
+    for t in (0, tokens - 1):
+        front = oracle.ffn_front(res[t], fn, base, scale, norm_w, 1e-6)
+        assert np.all(np.abs(x[t] - front["ffn_norm"]) <= ulp16(front["ffn_norm"], cfg.act_dtype) + 1e-6)
+        eo = np.stack([oracle.expert_ffn(la, np.asarray(layer.artifact.expert_data(0, int(e))), x[t], cfg.swiglu_limit)
+                       for e in ids_h[t]])
+        want_moe = oracle.moe_combine(eo, w_h[t]) + oracle.dense_ffn(shared_bits[0], shared_bits[1], shared_bits[2],
+                                                                     cfg.act_dtype, x[t], cfg.swiglu_limit)
+        s = oracle.compare(want_moe, moe_out[t].double().cpu().numpy())
+        assert s["rel_l2"] <= 2e-3, s                   # grouped path: fp16 operand and hidden roundings
+        want_out = oracle.hc_post(moe_out[t].double().cpu().numpy(), res[t], front["post"], front["comb"])
+        assert np.all(np.abs(got_out[t] - want_out) <= ulp16(want_out, cfg.act_dtype) + 1e-4)
