@@ -521,19 +521,27 @@ def main():
         },
     }
 
+    # The sections below explain the headline; a failure in one of them is recorded in its place
+    # and never costs the line itself.
+    def section(key, fn):
+        try:
+            line[key] = fn()
+        except Exception as exc:
+            line[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
     if world == 1 and not args.no_sweep:
-        line["decode_sweep"] = model.batch_sweep([1, 8, 32, 128], x_dev, out_dev, peak_gbs,
-                                                 iters=max(10, args.steps))
-    if world == 1 and not args.no_sweep:
-        line["prefill"] = prefill_bench(model, cfg, peaks, iters=max(3, min(args.steps, 10)))
+        section("decode_sweep", lambda: model.batch_sweep([1, 8, 32, 128], x_dev, out_dev, peak_gbs,
+                                                          iters=max(10, args.steps)))
+        section("prefill", lambda: prefill_bench(model, cfg, peaks, iters=max(3, min(args.steps, 10))))
     if args.case == "prefill_small":
-        line["prefill"] = prefill_bench(model, cfg, peaks, tokens=512, iters=2)
+        section("prefill", lambda: prefill_bench(model, cfg, peaks, tokens=512, iters=2))
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
-        tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, 1)
-        line["cpu_baseline"] = {
-            "value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": (f"1 token through 1 layer (router + 8 routed experts + shared expert + combine) "
-                       f"= {sec:.3f} s on {cores} threads, scaled x{args.layers} layers; fp64 oracle")}
+        def cpu_section():
+            tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, 1)
+            return {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+                    "sample": (f"1 token through 1 layer (router + 8 routed experts + shared expert + combine) "
+                               f"= {sec:.3f} s on {cores} threads, scaled x{args.layers} layers; fp64 oracle")}
+        section("cpu_baseline", cpu_section)
     if rank == 0:
         print(json.dumps(line), flush=True)
     shutdown(dist)
