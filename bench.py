@@ -111,44 +111,106 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------
 # CPU oracle leg (reported baseline and the --impl reference arm)
 # ----------------------------------------------------------------------------------------
-def cpu_oracle_tokens_per_s(layers: int, repeats: int = 1):
-    """Times the CPU oracle on one token through one layer (router + 8 routed experts +
-    shared expert + combine) with every host thread it can use, and scales to the stack."""
+# The benchmark configuration's layer shape as literals: the CPU leg must not load the product
+# library (tests/test_bench_contract.py checks these against the library's "baseline" preset).
+BASELINE_SHAPE = dict(hidden=7168, intermediate=2048, experts=256, top_k=8, group_size=128, act_dtype=1,
+                      score_fn=1, renormalize=1, routed_scaling=1.0, swiglu_limit=10.0, w13_rpw=4,
+                      w13_lpr=8, w2_rpw=8, w2_lpr=4)
+F16, BF16 = 0, 1
+
+
+def load_synth():
+    """aeon_b200/synth.py by file path (pure numpy): the quantile tables and seeded small tensors
+    without importing the package, which would load the CUDA library."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "_aeon_synth_tables", os.path.join(ROOT, "project-aeon_b200", "aeon_b200", "synth.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_oracle():
+    """The CPU oracle with every host core: a launcher may export OMP_NUM_THREADS=1
+    (torch.distributed.run does), which would otherwise make this leg single-threaded."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import numpy as np
-    import aeon_b200
-    from aeon_b200 import synth
     import oracle_py as oracle
+    oracle.set_threads(os.cpu_count() or 1)
+    return oracle
 
-    cfg = aeon_b200.preset("baseline")
-    la = oracle.layout_args(cfg)
-    scale_table = synth.half_normal_table(0.02, 1e-4, 4096, dtype=aeon_b200.F16)
-    dense_table = synth.half_normal_table(0.02, 0.0, 4096, dtype=cfg.act_dtype)
-    rng = np.random.default_rng([SEED, 0, 0x6A7E])
-    gate_bits = synth.normal_bits(rng, (cfg.experts, cfg.hidden), 0.01, cfg.act_dtype)
-    x_bits = synth.normal_bits(np.random.default_rng([SEED, 0xAC7]), (1, cfg.hidden), 1.0, cfg.act_dtype)
-    n = cfg.hidden * cfg.intermediate
-    shared = [oracle.synth_dense16(n, SEED, 0, s, dense_table) for s in range(3)]
-    w1 = shared[0].reshape(cfg.intermediate, cfg.hidden)
-    w3 = shared[1].reshape(cfg.intermediate, cfg.hidden)
-    w2 = shared[2].reshape(cfg.hidden, cfg.intermediate)
-    x = synth.from_bits16(x_bits, cfg.act_dtype)[0]
-    # payload generation is input preparation, not the path: done before the clock starts
-    logits0 = oracle.router_logits_f64(gate_bits, cfg.act_dtype, x_bits, cfg.act_dtype)
-    ids0, _, _ = oracle.router_topk(logits0, None, cfg.top_k, cfg.routed_scaling, cfg.score_fn)
-    payloads = {int(e): oracle.synth_expert_payload(la, SEED, 0, int(e), scale_table) for e in ids0[0]}
 
+class OracleLayer:
+    """One seeded layer of the benchmark stack as the oracle sees it (same generators and seeds
+    as the device fill kernels): gate, shared expert, and expert payloads on demand."""
+
+    def __init__(self, oracle, synth, layer: int, experts: int = BASELINE_SHAPE["experts"]):
+        import numpy as np
+        from types import SimpleNamespace
+        self.oracle, self.synth, self.layer = oracle, synth, layer
+        self.cfg = cfg = SimpleNamespace(**dict(BASELINE_SHAPE, experts=experts))
+        self.la = oracle.layout_args(cfg)
+        self.scale_table = synth.half_normal_table(0.02, 1e-4, 4096, dtype=F16)
+        dense_table = synth.half_normal_table(0.02, 0.0, 4096, dtype=cfg.act_dtype)
+        rng = np.random.default_rng([SEED, layer, 0x6A7E])
+        self.gate_bits = synth.normal_bits(rng, (cfg.experts, cfg.hidden), 0.01, cfg.act_dtype)
+        n = cfg.hidden * cfg.intermediate
+        shared = [oracle.synth_dense16(n, SEED, layer, s, dense_table) for s in range(3)]
+        self.w1 = shared[0].reshape(cfg.intermediate, cfg.hidden)
+        self.w3 = shared[1].reshape(cfg.intermediate, cfg.hidden)
+        self.w2 = shared[2].reshape(cfg.hidden, cfg.intermediate)
+        self._payloads = {}
+
+    def payload(self, expert: int):
+        if expert not in self._payloads:
+            self._payloads[expert] = self.oracle.synth_expert_payload(self.la, SEED, self.layer, expert,
+                                                                      self.scale_table)
+        return self._payloads[expert]
+
+    def route(self, x_bits_row):
+        cfg, o = self.cfg, self.oracle
+        logits = o.router_logits_f64(self.gate_bits, cfg.act_dtype, x_bits_row.reshape(1, -1), cfg.act_dtype)
+        ids, w, _ = o.router_topk(logits, None, cfg.top_k, cfg.routed_scaling, cfg.score_fn)
+        return ids[0], w[0]
+
+    def token_output(self, x_bits_row, ids, weights):
+        """fp64 layer output of one token: shared expert + routed experts combined in slot order."""
+        import numpy as np
+        cfg, o = self.cfg, self.oracle
+        x = self.synth.from_bits16(x_bits_row, cfg.act_dtype)
+        outs = np.stack([o.expert_ffn(self.la, self.payload(int(e)), x, cfg.swiglu_limit) for e in ids])
+        sh = o.dense_ffn(self.w1, self.w3, self.w2, cfg.act_dtype, x, cfg.swiglu_limit)
+        return o.moe_combine(outs, np.asarray(weights, dtype=np.float64), sh)
+
+
+def stack_activation_bits(synth, layers: int, tokens: int):
+    """The benchmark's activation rows [layers, tokens, hidden] as 16-bit patterns (both arms)."""
+    import numpy as np
+    return synth.normal_bits(np.random.default_rng([SEED, 0xAC7]), (layers, tokens, BASELINE_SHAPE["hidden"]),
+                             1.0, BASELINE_SHAPE["act_dtype"])
+
+
+def cpu_oracle_tokens_per_s(layers: int, batch: int, repeats: int = 1):
+    """Times the CPU oracle on a bounded sample of the workload -- token 0 of layer 0 through
+    router + 8 routed experts + shared expert + combine -- with every host thread, and scales
+    the sample to the stack. Returns (tokens/s, seconds per token-layer, threads)."""
+    oracle, synth = load_oracle(), load_synth()
+    layer = OracleLayer(oracle, synth, 0)
+    x_row = stack_activation_bits(synth, 1, 1)[0, 0]
+    ids0, _ = layer.route(x_row)
+    for e in ids0:                      # payload generation is input preparation: before the clock
+        layer.payload(int(e))
     best = float("inf")
-    for _ in range(repeats):
+    for _ in range(max(1, repeats)):
         t0 = time.perf_counter()
-        logits = oracle.router_logits_f64(gate_bits, cfg.act_dtype, x_bits, cfg.act_dtype)
-        ids, w, _ = oracle.router_topk(logits, None, cfg.top_k, cfg.routed_scaling, cfg.score_fn)
-        outs = np.stack([oracle.expert_ffn(la, payloads[int(e)], x, cfg.swiglu_limit) for e in ids[0]])
-        sh = oracle.dense_ffn(w1, w3, w2, cfg.act_dtype, x, cfg.swiglu_limit)
-        oracle.moe_combine(outs, w[0], sh)
+        ids, w = layer.route(x_row)
+        layer.token_output(x_row, ids, w)
         best = min(best, time.perf_counter() - t0)
-    seconds_per_layer_token = best
-    return 1.0 / (seconds_per_layer_token * layers), seconds_per_layer_token, oracle.threads()
+    return 1.0 / (best * layers), best, oracle.threads()
+
+
+def sample_text(sec, cores, layers):
+    return (f"token 0 of layer 0 (router + 8 routed experts + shared expert + combine) = {sec:.3f} s on "
+            f"{cores} threads, scaled x{layers} layers; fp64 oracle")
 
 
 def run_reference_arm(args):
@@ -157,18 +219,21 @@ def run_reference_arm(args):
         return
     t0 = time.perf_counter()
     for _ in range(max(0, min(args.warmup, 1))):
-        cpu_oracle_tokens_per_s(args.layers, 1)
-    tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, max(1, min(args.steps, 3)))
-    sample = (f"1 token through 1 layer (router + 8 routed experts + shared expert + combine) "
-              f"= {sec:.3f} s on {cores} threads, scaled x{args.layers} layers; fp64 oracle")
+        cpu_oracle_tokens_per_s(args.layers, args.batch, 1)
+    tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, args.batch, max(1, min(args.steps, 3)))
     line = {
         "impl": "reference", "metric": "moe_decode_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sec * args.layers * args.batch * 1e3, "higher_is_better": True,
+        # a step of this arm is the bounded sample; the whole-stack step time is the sample scaled
+        # by layers x batch and is labelled as such
+        "ms_per_step": sec * args.layers * args.batch * 1e3,
+        "ms_per_step_is": "extrapolated: measured sample_ms x layers x batch (the sample is one token-layer)",
+        "sample_ms": sec * 1e3,
+        "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": workload_config(args, 1),
+        "config": workload_config(args, args.gpus),
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": sample},
+                         "sample": sample_text(sec, cores, args.layers)},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
     }
@@ -365,8 +430,8 @@ def main():
     if T % world:
         raise SystemExit("--batch must divide by the number of GPUs")
     TL = T // world          # tokens owned by this rank
-    x_bits = synth.normal_bits(np.random.default_rng([SEED, 0xAC7]), (args.layers, T, H), 1.0, cfg.act_dtype)
-    x_bits = np.ascontiguousarray(x_bits[:, rank * TL:(rank + 1) * TL])
+    x_bits_all = stack_activation_bits(synth, args.layers, T)
+    x_bits = np.ascontiguousarray(x_bits_all[:, rank * TL:(rank + 1) * TL])
     x_host = torch.from_numpy(x_bits.view(np.int16)).view(torch.bfloat16).pin_memory()
     x_dev = x_host.cuda(non_blocking=True)
     out_dev = torch.empty(args.layers, TL, H, dtype=torch.float32, device="cuda")
@@ -489,7 +554,7 @@ def main():
         "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int4 weights x fp16 scales, f16 MMA operands, f32 accumulate (W4A16)",
-        "data": "synthetic", "config": dict(workload_config(args, world), launch_mode=graph_note),
+        "data": "synthetic", "config": workload_config(args, world), "launch_mode": graph_note,
         "clocks": clocks,
         "e2e": {"value": e2e_tokens_per_s, "unit": "tokens/s",
                 "h2d_bytes_per_step": int(x_host.numel() * 2 * world),
@@ -537,23 +602,78 @@ def main():
         section("prefill", lambda: prefill_bench(model, cfg, peaks, tokens=512, iters=2))
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
         def cpu_section():
-            tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, 1)
+            tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, args.batch, 1)
             return {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
-                    "sample": (f"1 token through 1 layer (router + 8 routed experts + shared expert + combine) "
-                               f"= {sec:.3f} s on {cores} threads, scaled x{args.layers} layers; fp64 oracle")}
+                    "sample": sample_text(sec, cores, args.layers)}
         section("cpu_baseline", cpu_section)
+    # ---- self-check of the measured configuration, outside the timed region, at every N ------
+    parity = parity_check(args, model, cfg, dist, rank, world, x_dev, out_dev, x_bits_all)
+    line["parity"] = parity
+    if world > 1 and args.case == "full":
+        model.release_graph()
+        peaks_tp = dict(peaks)
+        section("tp", lambda: tp_bench(args, cfg, dist, rank, world, local_rank, peaks_tp))
     if rank == 0:
         print(json.dumps(line), flush=True)
+    model.release_graph()
     shutdown(dist)
+    if not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
+
+
+def parity_check(args, model, cfg, dist, rank, world, x_dev, out_dev, x_bits_all):
+    """Correctness of the run that was just timed, on the box that timed it:
+    (a) layer 0's top-k ids, hashed, must be equal on every rank (replicated routing);
+    (b) token 0 of layer 0 -- routed experts on whichever ranks own them, shared expert, combine --
+        against the fp64 CPU oracle within the benchmark's tolerance (max-abs 2e-2, rel-L2 1e-3),
+        and its ids against the oracle's own top-k."""
+    import zlib
+    import numpy as np
+    import torch
+    tol_abs, tol_l2 = 2e-2, 1e-3
+    weights, ids = model.forward_layer(0, x_dev[0], out_dev[0], return_routing=True)
+    torch.cuda.synchronize()
+    ids_h = ids.cpu().numpy()
+    digest = zlib.crc32(np.ascontiguousarray(ids_h).tobytes())
+    digests = [digest]
+    if dist is not None:
+        t = torch.tensor([digest], dtype=torch.int64, device="cuda")
+        gathered = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        digests = [int(g.item()) for g in gathered]
+    ids_equal = len(set(digests)) == 1
+    result = {"ids_equal": ids_equal, "ids_crc32": digests[0], "ranks": world, "token": 0, "layer": 0,
+              "tolerance": {"max_abs": tol_abs, "rel_l2": tol_l2}}
+    if rank == 0:          # token 0 is rank 0's first row at every N
+        oracle, synth = load_oracle(), load_synth()
+        layer = OracleLayer(oracle, synth, 0, cfg.experts)
+        x_row = x_bits_all[0, 0]
+        want_ids, _ = layer.route(x_row)
+        got_ids, got_w = ids_h[0], weights[0].cpu().numpy().astype(np.float64)
+        want = layer.token_output(x_row, got_ids, got_w)
+        got = out_dev[0, 0].double().cpu().numpy()
+        cmp = oracle.compare(want, got)
+        result.update(max_abs=float(cmp["max_abs"]), rel_l2=float(cmp["rel_l2"]),
+                      ids_match_oracle=bool(sorted(int(e) for e in got_ids) == sorted(int(e) for e in want_ids)))
+        ok = ids_equal and result["ids_match_oracle"] and cmp["max_abs"] <= tol_abs and cmp["rel_l2"] <= tol_l2
+    else:
+        ok = ids_equal
+    if dist is not None:   # every rank leaves with the same verdict
+        t = torch.tensor([1 if ok else 0], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = bool(t.item())
+    result["ok"] = ok
+    return result
 
 
 def shutdown(dist):
-    """Leaves the process group; a teardown that blocks must not keep the job alive."""
+    """Leaves the process group. A teardown that blocks must not keep the job alive, and must not
+    look like success either: the watchdog ends the process with a non-zero code."""
     if dist is None:
         return
     import threading
     sys.stdout.flush()
-    watchdog = threading.Timer(60.0, lambda: os._exit(0))
+    watchdog = threading.Timer(90.0, lambda: os._exit(3))
     watchdog.daemon = True
     watchdog.start()
     try:

@@ -228,7 +228,11 @@ enum {
     /* Stop after the per-draw slices are written; the caller finishes with
      * aeon_b200_moe_accumulate. Lets the shared expert (which produces moe_accum's initial
      * value) run on another stream while the routed experts stream their weights. */
-    AEON_B200_DECODE_DEFER_ACCUMULATE = 2
+    AEON_B200_DECODE_DEFER_ACCUMULATE = 2,
+    /* moe_accum[t,:] = the routed sum instead of += : the accumulator's previous contents are
+     * neither read nor needed (rows whose draws are all skipped become 0). Saves the caller a
+     * zero fill when moe_accum is a per-rank partial sum (expert or tensor parallel). */
+    AEON_B200_DECODE_OVERWRITE = 4
 };
 int aeon_b200_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t* slot_of_expert,
                          const void* x, int64_t x_stride, const int32_t* topk_ids,

@@ -58,6 +58,18 @@ int ao_threads() {
 #endif
 }
 
+// Sets the thread count of the parallel loops (a launcher may have exported
+// OMP_NUM_THREADS=1 before this library was loaded). Returns the count now in force.
+int ao_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 // out[0]=payload_bytes; then per matrix (W1, W2, W3): packed_offset, scale_offset,
 // rows, columns, rpw, lpr, iterations  (7 values each) -> 22 values.
 int ao_layout(const LayoutArgs* a, uint64_t* out) {

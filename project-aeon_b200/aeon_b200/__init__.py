@@ -19,6 +19,7 @@ F16, BF16 = 0, 1
 SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID = 0, 1
 DECODE_SKIP_ABSENT = 1
 DECODE_DEFER_ACCUMULATE = 2
+DECODE_OVERWRITE = 4
 
 STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "LOGIC", 3: "CUDA", 4: "OUT_OF_RANGE",
                 5: "TIMEOUT", 6: "UNSUPPORTED"}
@@ -239,6 +240,22 @@ def _ptr(t):
     return None if t is None else c_void_p(t.data_ptr())
 
 
+def _dense(t, name: str):
+    """Pointer of a tensor the library reads or writes as one dense block."""
+    if t is None:
+        return None
+    if not t.is_contiguous():
+        raise AeonError(1, f"{name} must be contiguous (the library is given a bare pointer)")
+    return c_void_p(t.data_ptr())
+
+
+def _rows(t, name: str):
+    """Pointer of a 2-D tensor passed with its row stride: the columns must be adjacent."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise AeonError(1, f"{name} must be 2-D with unit column stride (rows may be strided)")
+    return c_void_p(t.data_ptr())
+
+
 def _stream():
     import torch
     return c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -338,9 +355,10 @@ class Context:
         k = self.cfg.top_k
         weights = torch.empty(tokens, k, dtype=torch.float32, device=x.device)
         ids = torch.empty(tokens, k, dtype=torch.int32, device=x.device)
-        check(lib().aeon_b200_router_topk(self._h, _ptr(x), x.stride(0), _ptr(gate), _ptr(bias),
-                                          _ptr(hash_table), _ptr(token_ids), tokens, _ptr(weights),
-                                          _ptr(ids), _ptr(logits_out), _stream()))
+        check(lib().aeon_b200_router_topk(self._h, _rows(x, "x"), x.stride(0), _dense(gate, "gate"),
+                                          _dense(bias, "bias"), _dense(hash_table, "hash_table"),
+                                          _dense(token_ids, "token_ids"), tokens, _ptr(weights),
+                                          _ptr(ids), _dense(logits_out, "logits_out"), _stream()))
         return weights, ids
 
     def expert_permutation(self, ids, experts=None, weights=None):
@@ -352,27 +370,32 @@ class Context:
         token_idx = torch.full((tokens * slots,), -1, dtype=torch.int32, device=dev)
         draw_idx = torch.full((tokens * slots,), -1, dtype=torch.int32, device=dev)
         wpos = torch.zeros(tokens * slots, dtype=torch.float32, device=dev) if weights is not None else None
-        check(lib().aeon_b200_expert_permutation(self._h, _ptr(ids), tokens, slots, experts,
+        check(lib().aeon_b200_expert_permutation(self._h, _dense(ids, "ids"), tokens, slots, experts,
                                                  _ptr(offsets), _ptr(token_idx), _ptr(draw_idx),
-                                                 _ptr(weights), _ptr(wpos), _stream()))
+                                                 _dense(weights, "weights"), _ptr(wpos), _stream()))
         return offsets, token_idx, draw_idx, wpos
 
     def shared_expert(self, w1, w3, w2, x, moe_accum):
-        check(lib().aeon_b200_shared_expert(self._h, _ptr(w1), _ptr(w3), _ptr(w2), _ptr(x),
-                                            x.stride(0), x.shape[0], _ptr(moe_accum),
-                                            moe_accum.stride(0), _stream()))
+        check(lib().aeon_b200_shared_expert(self._h, _dense(w1, "w1"), _dense(w3, "w3"), _dense(w2, "w2"),
+                                            _rows(x, "x"), x.stride(0), x.shape[0],
+                                            _rows(moe_accum, "moe_accum"), moe_accum.stride(0), _stream()))
 
     def moe_decode(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum,
-                   skip_absent: bool = False, defer_accumulate: bool = False):
-        flags = (DECODE_SKIP_ABSENT if skip_absent else 0) | (DECODE_DEFER_ACCUMULATE if defer_accumulate else 0)
-        check(lib().aeon_b200_moe_decode(self._h, c_void_p(pool_base), _ptr(slot_of_expert), _ptr(x),
-                                         x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
-                                         _ptr(moe_accum), moe_accum.stride(0), flags, _stream()))
+                   skip_absent: bool = False, defer_accumulate: bool = False, overwrite: bool = False):
+        flags = ((DECODE_SKIP_ABSENT if skip_absent else 0) | (DECODE_DEFER_ACCUMULATE if defer_accumulate else 0) |
+                 (DECODE_OVERWRITE if overwrite else 0))
+        check(lib().aeon_b200_moe_decode(self._h, c_void_p(pool_base), _dense(slot_of_expert, "slot_of_expert"),
+                                         _rows(x, "x"), x.stride(0), _dense(ids, "ids"),
+                                         _dense(weights, "weights"), x.shape[0],
+                                         _rows(moe_accum, "moe_accum"), moe_accum.stride(0), flags, _stream()))
 
-    def moe_accumulate(self, slot_of_expert, ids, moe_accum, skip_absent: bool = False):
-        check(lib().aeon_b200_moe_accumulate(self._h, _ptr(slot_of_expert), _ptr(ids), ids.shape[0],
-                                             _ptr(moe_accum), moe_accum.stride(0),
-                                             DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
+    def moe_accumulate(self, slot_of_expert, ids, moe_accum, skip_absent: bool = False,
+                       overwrite: bool = False):
+        check(lib().aeon_b200_moe_accumulate(self._h, _dense(slot_of_expert, "slot_of_expert"),
+                                             _dense(ids, "ids"), ids.shape[0],
+                                             _rows(moe_accum, "moe_accum"), moe_accum.stride(0),
+                                             (DECODE_SKIP_ABSENT if skip_absent else 0) |
+                                             (DECODE_OVERWRITE if overwrite else 0), _stream()))
 
 
 def hc_params_default() -> HcParams:
@@ -406,11 +429,13 @@ def _hc_post(self, moe_out, res_mid, post, comb):
 
 
 def _moe_prefill(self, pool_base: int, slot_of_expert, x, ids, weights, moe_accum,
-                 skip_absent: bool = False):
-    check(lib().aeon_b200_moe_prefill(self._h, c_void_p(pool_base), _ptr(slot_of_expert), _ptr(x),
-                                      x.stride(0), _ptr(ids), _ptr(weights), x.shape[0],
-                                      _ptr(moe_accum), moe_accum.stride(0),
-                                      DECODE_SKIP_ABSENT if skip_absent else 0, _stream()))
+                 skip_absent: bool = False, overwrite: bool = False):
+    check(lib().aeon_b200_moe_prefill(self._h, c_void_p(pool_base), _dense(slot_of_expert, "slot_of_expert"),
+                                      _rows(x, "x"), x.stride(0), _dense(ids, "ids"),
+                                      _dense(weights, "weights"), x.shape[0],
+                                      _rows(moe_accum, "moe_accum"), moe_accum.stride(0),
+                                      (DECODE_SKIP_ABSENT if skip_absent else 0) |
+                                      (DECODE_OVERWRITE if overwrite else 0), _stream()))
 
 
 Context.moe_prefill = _moe_prefill
@@ -422,13 +447,13 @@ def router_topk_noalloc(cfg: MoeConfig, x, gate, weights_out, ids_out, bias=None
     """Router without a context and without any allocation: every buffer, outputs included,
     is the caller's; the logits scratch is built into the library (<= 64 tokens, <= 1024
     experts). For callers that cannot call cudaMalloc at the point of use."""
-    check(lib().aeon_b200_router_topk_noalloc(ctypes.byref(cfg), _ptr(x), x.stride(0), _ptr(gate),
-                                              _ptr(bias), x.shape[0], _ptr(weights_out),
-                                              _ptr(ids_out), _stream()))
+    check(lib().aeon_b200_router_topk_noalloc(ctypes.byref(cfg), _rows(x, "x"), x.stride(0), _dense(gate, "gate"),
+                                              _dense(bias, "bias"), x.shape[0], _dense(weights_out, "weights_out"),
+                                              _dense(ids_out, "ids_out"), _stream()))
 
 
 def ep_combine(out, partials) -> None:
     """out[t, :] += sum_r partials[r, t, :] in rank order (fp32)."""
     ranks, tokens, hidden = partials.shape
-    check(lib().aeon_b200_ep_combine(_ptr(out), out.stride(0), _ptr(partials), ranks, tokens, hidden,
-                                     _stream()))
+    check(lib().aeon_b200_ep_combine(_rows(out, "out"), out.stride(0), _dense(partials, "partials"), ranks,
+                                     tokens, hidden, _stream()))

@@ -345,6 +345,17 @@ class MoeStack:
         self._graph_launches = self.launches - before
         self._graph, self._graph_x, self._graph_out = graph, x.data_ptr(), out.data_ptr()
 
+    def release_graph(self):
+        """Drops the captured step. A graph that holds NCCL nodes keeps references into the
+        communicator (NCCL frees a captured plan only when its graph is destroyed), so the
+        process group must not be torn down while the graph is alive."""
+        if self._graph is not None:
+            import torch
+            torch.cuda.synchronize()
+            self._graph.reset()
+            self._graph = None
+            torch.cuda.synchronize()
+
     def forward_layer(self, l: int, x, out, collect_stats: bool = False, return_routing: bool = False):
         w = self.weights[l]
         ctx = self.ctx
@@ -376,7 +387,8 @@ class MoeStack:
             tokens_seen = tl * self.world
             weights, ids = ep_layer_forward(ops, self.dist, self.world, x, out,
                                             self.x_all[:tokens_seen], self.partial[:tokens_seen],
-                                            self.recv[:, :tl])
+                                            self.recv.view(-1)[:tokens_seen * x.shape[1]]
+                                            .view(self.world, tl, x.shape[1]))
             self._extra_launches += 2
         if collect_stats:
             distinct, _ = ctx.last_stats()

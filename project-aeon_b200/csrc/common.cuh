@@ -39,6 +39,8 @@ inline void require(bool ok, const char* message) {
     if (!ok) throw StatusError(AEON_B200_ERR_INVALID_ARGUMENT, message);
 }
 
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 template <class F>
 int guarded(F&& f) noexcept {
     try {

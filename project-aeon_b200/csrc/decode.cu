@@ -42,6 +42,7 @@
 #include "ptx.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace aeon_b200 {
 
@@ -66,6 +67,7 @@ struct DecodeParams {
     const int32_t* topk_ids;
     const int32_t* slot_of;
     int skip_absent;
+    int overwrite;
     int experts;
     __half* hid_hi;
     __half* hid_lo;
@@ -708,6 +710,439 @@ moe_w2_contrib_kernel(const DecodeParams p) {
     }
 }
 
+// =========================================================================================
+// Row-streaming forms of kernels A and B (group 128).
+//
+// Each warp owns whole weight rows: one 16-row tile of W1 and W3 (kernel A) or MT 16-row tiles
+// of W2 (kernel B) over the full K, with the accumulators in its registers from the first
+// column to the last. No K-split, so no cross-warp reduction, no per-tile barrier and no
+// scale staging: the warps of a CTA run independently and only meet when the CTA moves to
+// another work entry, whose activation rows they share in shared memory. A warp keeps D
+// "steps" of its rows' packed words and scales in flight in a register ring (a step is the
+// 512-byte line of each of its row-blocks: 256 columns for W1/W3, 128 for W2) and refills a
+// ring slot as soon as it has consumed it, across tile boundaries, so the loads never drain.
+//
+// Scheduling unit: W consecutive tiles of one entry, one per warp. A CTA owns a contiguous,
+// balanced range of units; all its warps walk the same units, so an entry change is uniform
+// across the CTA and is the only place with a CTA-wide barrier.
+// =========================================================================================
+
+__device__ __forceinline__ WorkEntry ldg_entry(const WorkEntry* p) {
+    const int4 v = __ldg(reinterpret_cast<const int4*>(p));
+    WorkEntry e;
+    e.expert = v.x; e.pos0 = v.y; e.ntok = v.z; e.slot = v.w;
+    return e;
+}
+
+__device__ __forceinline__ uint32_t ldg_stream16(const uint8_t* p) {
+    uint16_t v;
+    asm("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
+}
+
+template <int W, int D, int NSTEP>
+struct GeomRowsA {
+    static constexpr int kThreads = W * 32;
+    static constexpr int kHidden = NSTEP * 256;
+    static constexpr int kActRow = kHidden * 2 + kPad;
+    static constexpr int kActBytes = kTokTile * kActRow;
+    static constexpr int kGroups = kHidden / 128;
+    static constexpr int kBlockScaleBytes = NSTEP * 16;          // per 4-row block
+    static constexpr int kXsBytes = kGroups * kTokTile * 4;
+    static constexpr int kBarBytes = 64;
+    static constexpr int kSmem = kBarBytes + kActBytes + kXsBytes;
+    static_assert(NSTEP % D == 0, "the ring depth must divide the steps of a tile");
+};
+
+// One ring slot of kernel A: a step (256 columns) of rows g and g+8 of W1 and W3.
+struct RingA {
+    uint4 w[2][2][2];        // [matrix][row half][chunk of the step]
+    uint32_t sc[2][2];       // [matrix][row half]: the two chunks' fp16 scales
+};
+
+template <int W, int D, int NSTEP>
+__global__ void __launch_bounds__(W * 32, 1)
+moe_w13_rows_kernel(const DecodeParams p) {
+    using S = GeomRowsA<W, D, NSTEP>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t smem_base = ptx::smem_u32(smem);
+    const uint32_t act_bar = smem_base;
+    const uint32_t act_smem = smem_base + S::kBarBytes;
+    const uint32_t xs_smem = act_smem + S::kActBytes;
+    float* xs = reinterpret_cast<float*>(smem + S::kBarBytes + S::kActBytes);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+
+    const int entries = p.counts[0];
+    const int tiles = p.I / 16;                       // 16-row tiles per entry
+    const int upe = (tiles + W - 1) / W;              // units per entry
+    const int total_units = entries * upe;
+    const int lo = static_cast<int>(static_cast<int64_t>(total_units) * blockIdx.x / gridDim.x);
+    const int hi = static_cast<int>(static_cast<int64_t>(total_units) * (blockIdx.x + 1) / gridDim.x);
+    if (lo >= hi) return;
+
+    if (tid == 0) {
+        ptx::mbar_init(act_bar, 1);
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+
+    // Lane-constant offsets of its two rows inside a 16-row tile (4 row-blocks of 4 rows).
+    uint32_t lane_off[2], lane_sc[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + 8 * h;
+        const int blk = r >> 2, rib = r & 3;
+        lane_off[h] = blk * p.w1.block_bytes + (rib * 8 + t) * 16;
+        lane_sc[h] = blk * S::kBlockScaleBytes + rib * 4;
+    }
+    const uint64_t keep_policy = ptx::policy_evict_last();
+
+    // A unit -> this warp's tile: the entry, the row tile, and the four stream bases.
+    struct Tile {
+        const uint8_t* wp[2];     // packed W1 / W3 of the tile
+        const uint8_t* sp[2];     // scales  W1 / W3 of the tile
+        WorkEntry e;
+        int m, rt;
+        bool active;
+    };
+    auto locate = [&](int u, Tile& x) {
+        x.m = u / upe;
+        x.rt = (u - x.m * upe) * W + warp;
+        x.active = x.rt < tiles;
+        x.e = ldg_entry(p.entries + x.m);
+        const uint8_t* payload = p.pool + static_cast<uint64_t>(x.e.slot < 0 ? 0 : x.e.slot) * p.payload_bytes;
+        const size_t rt = static_cast<size_t>(x.active ? x.rt : 0);
+        x.wp[0] = payload + p.w1.packed_offset + rt * 4 * p.w1.block_bytes;
+        x.wp[1] = payload + p.w3.packed_offset + rt * 4 * p.w3.block_bytes;
+        x.sp[0] = payload + p.w1.scale_offset + rt * 4 * S::kBlockScaleBytes;
+        x.sp[1] = payload + p.w3.scale_offset + rt * 4 * S::kBlockScaleBytes;
+    };
+    auto load_step = [&](RingA& r, const Tile& x, int step) {
+#pragma unroll
+        for (int mat = 0; mat < 2; ++mat)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint8_t* src = x.wp[mat] + lane_off[h] + step * 512;
+                r.w[mat][h][0] = ldg_stream128(src);
+                r.w[mat][h][1] = ldg_stream128(src + 64);
+                r.sc[mat][h] = ldg_stream32(x.sp[mat] + lane_sc[h] + step * 16);
+            }
+    };
+
+    Tile cur, nxt;
+    locate(lo, cur);
+    if (cur.e.slot < 0 && tid == 0) flag_error(p.error, kErrExpertAbsent);
+    RingA ring[D];
+    if (cur.active) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) load_step(ring[d], cur, d);
+    }
+
+    int cur_entry = -1;
+    uint32_t act_phase = 0;
+    const uint32_t a_row = act_smem + g * S::kActRow;
+    for (int u = lo; u < hi; ++u) {
+        const bool has_next = u + 1 < hi;
+        nxt = cur;
+        if (has_next) {
+            locate(u + 1, nxt);
+            if (nxt.e.slot < 0 && tid == 0) flag_error(p.error, kErrExpertAbsent);
+        }
+        // ---- the entry's activation rows, when the CTA moves to another entry ----
+        if (cur.m != cur_entry) {
+            __syncthreads();                 // every warp is done with the previous rows
+            if (warp == 0) {
+                if (lane == 0) ptx::mbar_arrive_expect_tx(act_bar, cur.e.ntok * S::kHidden * 2);
+                __syncwarp();
+                if (lane < cur.e.ntok) {
+                    const int token = __ldg(p.token_idx + cur.e.pos0 + lane);
+                    ptx::bulk_g2s(act_smem + lane * S::kActRow,
+                                  p.xperm + static_cast<size_t>(token) * S::kHidden, S::kHidden * 2,
+                                  act_bar, keep_policy);
+                }
+            }
+            if (!ptx::mbar_wait(act_bar, act_phase & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
+            ++act_phase;
+            cur_entry = cur.m;
+            __syncwarp();
+            group_sums<128>(act_smem, S::kActRow, 0, 1, cur.e.ntok, S::kGroups, xs, warp, W, lane);
+            __syncthreads();
+        }
+
+        float acc[2][4];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
+
+        if (cur.active) {
+#pragma unroll 1
+            for (int s0 = 0; s0 < NSTEP; s0 += D) {
+                const bool last = s0 + D >= NSTEP;
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const int s = s0 + d;
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int c = 2 * s + cc;
+                        // Rows of tokens past the entry's count hold stale bytes: an MMA column
+                        // only feeds its own output column, and those columns are never stored.
+                        uint4 bf[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) bf[i] = ptx::lds128(a_row + (c * 128 + i * 32 + t * 8) * 2);
+                        const float2 xsum = ptx::lds_f2(xs_smem + (c * kTokTile + 2 * t) * 4);
+#pragma unroll
+                        for (int mat = 0; mat < 2; ++mat) {
+                            const uint32_t s0bits = ring[d].sc[mat][0], s1bits = ring[d].sc[mat][1];
+                            const float sca = half_bits_to_float(cc ? (s0bits >> 16) : (s0bits & 0xFFFFu));
+                            const float scb = half_bits_to_float(cc ? (s1bits >> 16) : (s1bits & 0xFFFFu));
+                            const uint4 wa = ring[d].w[mat][0][cc], wb = ring[d].w[mat][1][cc];
+                            float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                            float thi[4] = {0.f, 0.f, 0.f, 0.f};
+                            ptx::mma_word(tlo, thi, wa.x, wb.x, bf[0]);
+                            ptx::mma_word(tlo, thi, wa.y, wb.y, bf[1]);
+                            ptx::mma_word(tlo, thi, wa.z, wb.z, bf[2]);
+                            ptx::mma_word(tlo, thi, wa.w, wb.w, bf[3]);
+                            ptx::fold_group(acc[mat], tlo, thi, sca, scb, xsum);
+                        }
+                    }
+                    // the slot is free: this tile's step s + D, or the next tile's step d
+                    if (!last) load_step(ring[d], cur, s + D);
+                    else if (has_next && nxt.active) load_step(ring[d], nxt, d);
+                }
+            }
+            // clamped SwiGLU and the (hi, lo) store: gate and up of an element sit in one lane
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int token = 2 * t + (j & 1);
+                const int row = g + 8 * (j >> 1);
+                if (token < cur.e.ntok) {
+                    const float gate = fminf(acc[0][j], p.limit);
+                    const float up = fminf(fmaxf(acc[1][j], -p.limit), p.limit);
+                    const float hval = (gate / (1.0f + expf(-gate))) * up;
+                    const __half hi16 = __float2half_rn(hval);
+                    const __half lo16 = __float2half_rn(hval - __half2float(hi16));
+                    const size_t at = static_cast<size_t>(cur.e.pos0 + token) * p.I + perm_col<128>(cur.rt * 16 + row);
+                    p.hid_hi[at] = hi16;
+                    p.hid_lo[at] = lo16;
+                }
+            }
+        } else if (has_next && nxt.active) {
+            // an idle warp of a partly filled unit still starts its next tile's stream
+#pragma unroll
+            for (int d = 0; d < D; ++d) load_step(ring[d], nxt, d);
+        }
+        cur = nxt;
+    }
+}
+
+template <int W, int MT, int D, int NCHUNK>
+struct GeomRowsB {
+    static constexpr int kThreads = W * 32;
+    static constexpr int kInter = NCHUNK * 128;
+    static constexpr int kActRow = 2 * kInter * 2 + kPad;           // hi then lo
+    static constexpr int kActBytes = kTokTile * kActRow;
+    static constexpr int kGroups = NCHUNK;
+    static constexpr int kBlockScaleBytes = NCHUNK * 16;           // per 8-row block
+    static constexpr int kXsBytes = kGroups * 2 * kTokTile * 4;    // [group][hi|lo][token]
+    static constexpr int kBarBytes = 64;
+    static constexpr int kSmem = kBarBytes + kActBytes + kXsBytes;
+    static constexpr int kItemRows = MT * 16;
+    static_assert(NCHUNK % D == 0, "the ring depth must divide the chunks of a tile");
+};
+
+// One ring slot of kernel B: a chunk (128 columns) of rows g and g+8 of MT tiles of W2.
+template <int MT>
+struct RingB {
+    uint4 w[MT][2];
+    uint32_t sc[MT][2];
+};
+
+template <int W, int MT, int D, int NCHUNK>
+__global__ void __launch_bounds__(W * 32, 1)
+moe_w2_rows_kernel(const DecodeParams p) {
+    using S = GeomRowsB<W, MT, D, NCHUNK>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t smem_base = ptx::smem_u32(smem);
+    const uint32_t act_bar = smem_base;
+    const uint32_t act_smem = smem_base + S::kBarBytes;
+    const uint32_t xs_smem = act_smem + S::kActBytes;
+    float* xs = reinterpret_cast<float*>(smem + S::kBarBytes + S::kActBytes);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+
+    const int entries = p.counts[0];
+    const int items = p.H / S::kItemRows;             // MT-tile items per entry
+    const int upe = (items + W - 1) / W;
+    const int total_units = entries * upe;
+    const int lo = static_cast<int>(static_cast<int64_t>(total_units) * blockIdx.x / gridDim.x);
+    const int hi = static_cast<int>(static_cast<int64_t>(total_units) * (blockIdx.x + 1) / gridDim.x);
+    if (lo >= hi) return;
+
+    if (tid == 0) {
+        ptx::mbar_init(act_bar, 1);
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+
+    // W2 row-blocks hold 8 rows: rows g of a tile are its first block, rows g+8 the second; a
+    // warp's 32 lanes read one contiguous 512-byte line per block and chunk.
+    const uint32_t lane_off = (g * 4 + t) * 16;
+    const uint32_t lane_sc = g * 2;
+    const uint64_t keep_policy = ptx::policy_evict_last();
+
+    struct Tile {
+        const uint8_t* wp;        // packed rows of the item (2 * MT row-blocks)
+        const uint8_t* sp;        // their scales
+        WorkEntry e;
+        int m, it;
+        bool active;
+    };
+    auto locate = [&](int u, Tile& x) {
+        x.m = u / upe;
+        x.it = (u - x.m * upe) * W + warp;
+        x.active = x.it < items;
+        x.e = ldg_entry(p.entries + x.m);
+        const uint8_t* payload = p.pool + static_cast<uint64_t>(x.e.slot < 0 ? 0 : x.e.slot) * p.payload_bytes;
+        const size_t block0 = static_cast<size_t>(x.active ? x.it : 0) * 2 * MT;
+        x.wp = payload + p.w2.packed_offset + block0 * p.w2.block_bytes;
+        x.sp = payload + p.w2.scale_offset + block0 * S::kBlockScaleBytes;
+    };
+    auto load_chunk_b = [&](RingB<MT>& r, const Tile& x, int c) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int blk = mt * 2 + h;
+                r.w[mt][h] = ldg_stream128(x.wp + static_cast<size_t>(blk) * p.w2.block_bytes + lane_off + c * 512);
+                r.sc[mt][h] = ldg_stream16(x.sp + blk * S::kBlockScaleBytes + lane_sc + c * 16);
+            }
+    };
+
+    Tile cur, nxt;
+    locate(lo, cur);
+    if (cur.e.slot < 0 && tid == 0) flag_error(p.error, kErrExpertAbsent);
+    RingB<MT> ring[D];
+    if (cur.active) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) load_chunk_b(ring[d], cur, d);
+    }
+
+    int cur_entry = -1;
+    uint32_t act_phase = 0;
+    for (int u = lo; u < hi; ++u) {
+        const bool has_next = u + 1 < hi;
+        nxt = cur;
+        if (has_next) {
+            locate(u + 1, nxt);
+            if (nxt.e.slot < 0 && tid == 0) flag_error(p.error, kErrExpertAbsent);
+        }
+        if (cur.m != cur_entry) {
+            __syncthreads();
+            if (warp == 0) {
+                if (lane == 0) ptx::mbar_arrive_expect_tx(act_bar, cur.e.ntok * S::kInter * 4);
+                __syncwarp();
+                if (lane < 2 * cur.e.ntok) {
+                    const int tok = lane >> 1, part = lane & 1;
+                    const __half* src = (part == 0 ? p.hid_hi : p.hid_lo) +
+                                        static_cast<size_t>(cur.e.pos0 + tok) * S::kInter;
+                    ptx::bulk_g2s(act_smem + tok * S::kActRow + part * S::kInter * 2, src, S::kInter * 2,
+                                  act_bar, keep_policy);
+                }
+            }
+            if (!ptx::mbar_wait(act_bar, act_phase & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
+            ++act_phase;
+            cur_entry = cur.m;
+            __syncwarp();
+            group_sums<128>(act_smem, S::kActRow, S::kInter * 2, 2, cur.e.ntok, S::kGroups, xs, warp, W, lane);
+            __syncthreads();
+        }
+
+        // Up to four tokens: hi and lo ride in one MMA as eight token columns (0-3 hi of tokens
+        // 0-3, 4-7 lo) and the two halves are added in the epilogue. More tokens: one pass per part.
+        const bool packed = cur.e.ntok <= 4;
+        float acc[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[mt][c] = 0.f;
+
+        if (cur.active) {
+            const int tok = packed ? (g & 3) : g;
+            const uint32_t b_tok = act_smem + tok * S::kActRow;
+#pragma unroll 1
+            for (int c0 = 0; c0 < NCHUNK; c0 += D) {
+                const bool last = c0 + D >= NCHUNK;
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const int c = c0 + d;
+                    const int passes = packed ? 1 : 2;
+                    float sca[MT], scb[MT];
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        sca[mt] = half_bits_to_float(ring[d].sc[mt][0]);
+                        scb[mt] = half_bits_to_float(ring[d].sc[mt][1]);
+                    }
+                    for (int part = 0; part < passes; ++part) {
+                        const int my_part = packed ? (g >> 2) : part;
+                        const uint32_t b_row = b_tok + my_part * (S::kInter * 2);
+                        const uint32_t xs_col = packed ? ((t >> 1) * kTokTile + 2 * (t & 1))
+                                                       : (part * kTokTile + 2 * t);
+                        uint4 bf[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) bf[i] = ptx::lds128(b_row + (c * 128 + i * 32 + t * 8) * 2);
+                        const float2 xsum = ptx::lds_f2(xs_smem + (c * 2 * kTokTile + xs_col) * 4);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const uint4 wa = ring[d].w[mt][0], wb = ring[d].w[mt][1];
+                            float tlo[4] = {0.f, 0.f, 0.f, 0.f};
+                            float thi[4] = {0.f, 0.f, 0.f, 0.f};
+                            ptx::mma_word(tlo, thi, wa.x, wb.x, bf[0]);
+                            ptx::mma_word(tlo, thi, wa.y, wb.y, bf[1]);
+                            ptx::mma_word(tlo, thi, wa.z, wb.z, bf[2]);
+                            ptx::mma_word(tlo, thi, wa.w, wb.w, bf[3]);
+                            ptx::fold_group(acc[mt], tlo, thi, sca[mt], scb[mt], xsum);
+                        }
+                    }
+                    if (!last) load_chunk_b(ring[d], cur, c + D);
+                    else if (has_next && nxt.active) load_chunk_b(ring[d], nxt, d);
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float v = acc[mt][j];
+                    if (packed) v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);   // lo half sits two lanes on
+                    const int token = 2 * t + (j & 1);
+                    const bool mine = packed ? (t < 2) : true;
+                    const int row = (cur.it * MT + mt) * 16 + g + 8 * (j >> 1);
+                    if (mine && token < cur.e.ntok) {
+                        const int pos = cur.e.pos0 + token;
+                        p.contrib[static_cast<size_t>(__ldg(p.draw_idx + pos)) * p.H + row] = __ldg(p.wpos + pos) * v;
+                    }
+                }
+        } else if (has_next && nxt.active) {
+#pragma unroll
+            for (int d = 0; d < D; ++d) load_chunk_b(ring[d], nxt, d);
+        }
+        cur = nxt;
+    }
+}
+
 // ----- kernel C: slot-order accumulate -------------------------------------------------------
 // accum[t, :] += sum over slot 0..k-1, in that order, of contrib[t*k + slot, :] (fp32). The
 // fixed order and the single writer per element of kernel B make the whole routed path
@@ -717,7 +1152,7 @@ __global__ void moe_accumulate_kernel(float* __restrict__ accum, int64_t accum_s
                                       const float* __restrict__ contrib,
                                       const int32_t* __restrict__ ids,
                                       const int32_t* __restrict__ slot_of, int skip_absent,
-                                      int experts, int tokens, int top_k, int H) {
+                                      int overwrite, int experts, int tokens, int top_k, int H) {
     const int vec_per_row = H / 4;
     const int64_t total = static_cast<int64_t>(tokens) * vec_per_row;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -725,7 +1160,7 @@ __global__ void moe_accumulate_kernel(float* __restrict__ accum, int64_t accum_s
         const int token = static_cast<int>(i / vec_per_row);
         const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
         float4* dst = reinterpret_cast<float4*>(accum + token * accum_stride) + v;
-        float4 a = *dst;
+        float4 a = overwrite ? make_float4(0.f, 0.f, 0.f, 0.f) : *dst;
         for (int slot = 0; slot < top_k; ++slot) {
             const int draw = token * top_k + slot;
             const int id = ids[draw];
@@ -785,26 +1220,26 @@ void launch_pair(aeon_b200_ctx* ctx, const DecodeParams& p, KernelA ka, int thre
         const int64_t vecs = static_cast<int64_t>(p.tokens) * p.H / 4;
         const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 4 * ctx->sm_count));
         moe_accumulate_kernel<<<blocks, 256, 0, stream>>>(p.accum, p.accum_stride, p.contrib, p.topk_ids,
-                                                          p.slot_of, p.skip_absent, p.experts, p.tokens,
-                                                          p.top_k, p.H);
+                                                          p.slot_of, p.skip_absent, p.overwrite, p.experts,
+                                                          p.tokens, p.top_k, p.H);
         AEON_CUDA_CHECK(cudaGetLastError());
         ctx->launches += 1;
     }
 }
 
-template <int G, int KWA, int NCHA>
+template <int G, int KWA, int NCHA, int MWB = 2, int MTB = 2, int KWB = 8, int NCHB = 2, int PB = 1>
 void launch_decode_kernels(aeon_b200_ctx* ctx, const DecodeParams& p, cudaStream_t stream) {
     using SA = GeomA<G, KWA, NCHA>;
     // intermediate = 2048: two workers of eight warps, two 16-row tiles per worker, two chunks
     // per warp (64-row items). Measured alternatives, all slower on B200: four K-warps x four
     // chunks with two CTAs per SM (spills under the 128-register cap, 2.0 TB/s), one worker of
     // four tiles (2.8 TB/s), one worker with two items in flight (2.8 TB/s); this one 3.1 TB/s.
-    using SB = GeomB<G, 2, 2, 8, 2, 1>;
+    using SB = GeomB<G, MWB, MTB, KWB, NCHB, PB>;
     if (p.I != SB::kInter || p.H != SA::kHidden)
         throw StatusError(AEON_B200_ERR_UNSUPPORTED,
                           "aeon_b200_moe_decode: no kernel instance for this hidden/intermediate size");
     launch_pair(ctx, p, moe_w13_swiglu_kernel<G, KWA, NCHA>, SA::kThreads, SA::kSmem,
-                moe_w2_contrib_kernel<G, 2, 2, 8, 2, 1>, SB::kThreads, SB::kSmem, 1, stream);
+                moe_w2_contrib_kernel<G, MWB, MTB, KWB, NCHB, PB>, SB::kThreads, SB::kSmem, 1, stream);
 }
 
 __global__ void ep_combine_kernel(float* __restrict__ out, int64_t out_stride,
@@ -831,8 +1266,9 @@ __global__ void ep_combine_kernel(float* __restrict__ out, int64_t out_stride,
 void launch_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks,
                        int tokens, int hidden, cudaStream_t stream) {
     require(out && partials, "aeon_b200_ep_combine: null pointer argument");
-    require(ranks > 0 && tokens > 0 && hidden > 0 && hidden % 4 == 0 && out_stride % 4 == 0,
-            "aeon_b200_ep_combine: hidden and out_stride must be multiples of 4");
+    require(ranks > 0 && tokens > 0 && hidden > 0 && hidden % 4 == 0 && out_stride % 4 == 0 &&
+                aligned16(out) && aligned16(partials),
+            "aeon_b200_ep_combine: hidden and out_stride must be multiples of 4, pointers 16-byte aligned");
     const int64_t total = static_cast<int64_t>(tokens) * hidden / 4;
     const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 2048));
     ep_combine_kernel<<<blocks, 256, 0, stream>>>(out, out_stride, partials, ranks, tokens, hidden);
@@ -846,12 +1282,15 @@ void launch_moe_accumulate(aeon_b200_ctx* ctx, const int32_t* slot_of_expert, co
     require(slot_of_expert && topk_ids && moe_accum, "aeon_b200_moe_accumulate: null pointer argument");
     require(tokens > 0 && tokens <= ctx->max_tokens,
             "aeon_b200_moe_accumulate: tokens must be in [1, max_tokens of the context]");
-    require(accum_stride >= cfg.hidden && accum_stride % 4 == 0, "aeon_b200_moe_accumulate: bad row stride");
+    require(accum_stride >= cfg.hidden && accum_stride % 4 == 0 && aligned16(moe_accum),
+            "aeon_b200_moe_accumulate: moe_accum must be 16-byte aligned, accum_stride >= hidden and a "
+            "multiple of 4");
     const int64_t vecs = static_cast<int64_t>(tokens) * cfg.hidden / 4;
     const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 4 * ctx->sm_count));
     moe_accumulate_kernel<<<blocks, 256, 0, stream>>>(
         moe_accum, accum_stride, ctx->d_contrib, topk_ids, slot_of_expert,
-        (flags & AEON_B200_DECODE_SKIP_ABSENT) ? 1 : 0, cfg.experts, tokens, cfg.top_k, cfg.hidden);
+        (flags & AEON_B200_DECODE_SKIP_ABSENT) ? 1 : 0, (flags & AEON_B200_DECODE_OVERWRITE) ? 1 : 0,
+        cfg.experts, tokens, cfg.top_k, cfg.hidden);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 1;
 }
@@ -867,6 +1306,9 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
             "aeon_b200_moe_decode: tokens must be in [1, max_tokens of the context]");
     require(x_stride >= cfg.hidden && accum_stride >= cfg.hidden,
             "aeon_b200_moe_decode: row strides must be at least the hidden width");
+    require(accum_stride % 4 == 0 && aligned16(moe_accum),
+            "aeon_b200_moe_decode: moe_accum must be 16-byte aligned and accum_stride a multiple of 4 "
+            "(the accumulate uses 128-bit accesses)");
 
     // 1. activations -> fp16 in kernel column order
     const int64_t total = static_cast<int64_t>(tokens) * cfg.hidden;
@@ -907,6 +1349,7 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     p.topk_ids = topk_ids;
     p.slot_of = slot_of_expert;
     p.skip_absent = (flags & AEON_B200_DECODE_SKIP_ABSENT) ? 1 : 0;
+    p.overwrite = (flags & AEON_B200_DECODE_OVERWRITE) ? 1 : 0;
     p.experts = cfg.experts;
     p.hid_hi = ctx->d_hidden_hi;
     p.hid_lo = ctx->d_hidden_lo;
@@ -917,6 +1360,48 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     p.error = ctx->d_error;
 
     // Kernel instances: K-warps x chunks-per-warp x 128 columns = hidden.
+#ifdef AEON_B200_TUNING
+    // Development builds only: kernel geometries selectable at run time for A/B timing sweeps.
+    static const int tune_a = getenv("AEON_B200_TUNE_A") ? atoi(getenv("AEON_B200_TUNE_A")) : 0;
+    static const int tune_b = getenv("AEON_B200_TUNE_B") ? atoi(getenv("AEON_B200_TUNE_B")) : 0;
+    if (cfg.group_size == 128 && cfg.hidden == 7168 && cfg.intermediate == 2048 && (tune_a || tune_b)) {
+        auto ka = moe_w13_swiglu_kernel<128, 14, 4>;
+        int ta = GeomA<128, 14, 4>::kThreads, sa = GeomA<128, 14, 4>::kSmem;
+        auto kb = moe_w2_contrib_kernel<128, 2, 2, 8, 2, 1>;
+        int tb = GeomB<128, 2, 2, 8, 2, 1>::kThreads, sb = GeomB<128, 2, 2, 8, 2, 1>::kSmem;
+#define PICK_A(K, ...) { ka = K; using GG = __VA_ARGS__; ta = GG::kThreads; sa = GG::kSmem; }
+#define PICK_B(K, ...) { kb = K; using GG = __VA_ARGS__; tb = GG::kThreads; sb = GG::kSmem; }
+        switch (tune_a) {
+            case 0: break;
+            case 1: PICK_A((moe_w13_swiglu_kernel<128, 8, 7>), GeomA<128, 8, 7>); break;
+            case 2: PICK_A((moe_w13_swiglu_kernel<128, 7, 8>), GeomA<128, 7, 8>); break;
+            case 3: PICK_A((moe_w13_swiglu_kernel<128, 28, 2>), GeomA<128, 28, 2>); break;
+            case 5: PICK_A((moe_w13_rows_kernel<16, 2, 28>), GeomRowsA<16, 2, 28>); break;
+            case 6: PICK_A((moe_w13_rows_kernel<12, 2, 28>), GeomRowsA<12, 2, 28>); break;
+            case 7: PICK_A((moe_w13_rows_kernel<8, 4, 28>), GeomRowsA<8, 4, 28>); break;
+            case 8: PICK_A((moe_w13_rows_kernel<8, 2, 28>), GeomRowsA<8, 2, 28>); break;
+            case 9: PICK_A((moe_w13_rows_kernel<16, 1, 28>), GeomRowsA<16, 1, 28>); break;
+            default: throw StatusError(AEON_B200_ERR_UNSUPPORTED, "unknown tuning selection A");
+        }
+        switch (tune_b) {
+            case 0: break;
+            case 1: PICK_B((moe_w2_contrib_kernel<128, 2, 2, 4, 4, 2>), GeomB<128, 2, 2, 4, 4, 2>); break;
+            case 2: PICK_B((moe_w2_contrib_kernel<128, 2, 2, 4, 4, 1>), GeomB<128, 2, 2, 4, 4, 1>); break;
+            case 3: PICK_B((moe_w2_contrib_kernel<128, 2, 1, 8, 2, 2>), GeomB<128, 2, 1, 8, 2, 2>); break;
+            case 4: PICK_B((moe_w2_contrib_kernel<128, 4, 1, 4, 4, 1>), GeomB<128, 4, 1, 4, 4, 1>); break;
+            case 5: PICK_B((moe_w2_rows_kernel<16, 2, 2, 16>), GeomRowsB<16, 2, 2, 16>); break;
+            case 6: PICK_B((moe_w2_rows_kernel<12, 2, 4, 16>), GeomRowsB<12, 2, 4, 16>); break;
+            case 7: PICK_B((moe_w2_rows_kernel<12, 2, 2, 16>), GeomRowsB<12, 2, 2, 16>); break;
+            case 8: PICK_B((moe_w2_rows_kernel<16, 1, 4, 16>), GeomRowsB<16, 1, 4, 16>); break;
+            case 9: PICK_B((moe_w2_rows_kernel<8, 2, 4, 16>), GeomRowsB<8, 2, 4, 16>); break;
+            default: throw StatusError(AEON_B200_ERR_UNSUPPORTED, "unknown tuning selection B");
+        }
+#undef PICK_A
+#undef PICK_B
+        launch_pair(ctx, p, ka, ta, sa, kb, tb, sb, 1, stream);
+        return;
+    }
+#endif
     if (cfg.group_size == 128 && cfg.hidden == 7168) {
         launch_decode_kernels<128, 14, 4>(ctx, p, stream);
     } else if (cfg.group_size == 128 && cfg.hidden == 4096) {

@@ -412,7 +412,7 @@ __global__ void moe_accumulate_prefill_kernel(float* __restrict__ accum, int64_t
                                               const float* __restrict__ contrib,
                                               const int32_t* __restrict__ ids,
                                               const int32_t* __restrict__ slot_of, int skip_absent,
-                                              int experts, int tokens, int top_k, int H) {
+                                              int overwrite, int experts, int tokens, int top_k, int H) {
     const int vec_per_row = H / 4;
     const int64_t total = static_cast<int64_t>(tokens) * vec_per_row;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -420,7 +420,7 @@ __global__ void moe_accumulate_prefill_kernel(float* __restrict__ accum, int64_t
         const int token = static_cast<int>(i / vec_per_row);
         const int v = static_cast<int>(i - static_cast<int64_t>(token) * vec_per_row);
         float4* dst = reinterpret_cast<float4*>(accum + token * accum_stride) + v;
-        float4 a = *dst;
+        float4 a = overwrite ? make_float4(0.f, 0.f, 0.f, 0.f) : *dst;
         for (int slot = 0; slot < top_k; ++slot) {
             const int draw = token * top_k + slot;
             const int id = ids[draw];
@@ -501,6 +501,8 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
     require(tokens > 0 && tokens <= 65536, "aeon_b200_moe_prefill: tokens must be in [1, 65536]");
     require(x_stride >= cfg.hidden && x_stride % 8 == 0 && accum_stride >= cfg.hidden && accum_stride % 4 == 0,
             "aeon_b200_moe_prefill: bad row stride");
+    require(aligned16(x) && aligned16(moe_accum),
+            "aeon_b200_moe_prefill: x and moe_accum must be 16-byte aligned (128-bit accesses)");
     require(cfg.hidden % (kTileK * kPrefetch) == 0 && cfg.intermediate % (kTileK * kPrefetch) == 0,
             "aeon_b200_moe_prefill: hidden and intermediate must be multiples of 256");
     PrefillScratch* s = ensure_scratch(ctx, tokens);
@@ -560,8 +562,9 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
     const int64_t vecs = static_cast<int64_t>(tokens) * cfg.hidden / 4;
     const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 8 * ctx->sm_count));
     moe_accumulate_prefill_kernel<<<blocks, 256, 0, stream>>>(moe_accum, accum_stride, s->contrib, topk_ids,
-                                                              slot_of_expert, skip ? 1 : 0, cfg.experts, tokens,
-                                                              cfg.top_k, cfg.hidden);
+                                                              slot_of_expert, skip ? 1 : 0,
+                                                              (flags & AEON_B200_DECODE_OVERWRITE) ? 1 : 0,
+                                                              cfg.experts, tokens, cfg.top_k, cfg.hidden);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 6;
 }

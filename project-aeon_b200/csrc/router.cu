@@ -117,7 +117,8 @@ __global__ void __launch_bounds__(kSelectWarps * 32)
 router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                      const int64_t* __restrict__ hash_table, const int32_t* __restrict__ token_ids,
                      int tokens, int experts, int top_k, int score_fn, int renormalize,
-                     float scaling, float* __restrict__ out_weights, int32_t* __restrict__ out_ids) {
+                     float scaling, float* __restrict__ out_weights, int32_t* __restrict__ out_ids,
+                     int32_t* __restrict__ error) {
     extern __shared__ float keys[];   // [kSelectWarps][experts]
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -134,7 +135,13 @@ router_select_kernel(const float* __restrict__ logits, const float* __restrict__
     if (hash_table != nullptr && token_ids != nullptr) {
         if (lane < top_k) {
             my_id = static_cast<int32_t>(hash_table[static_cast<size_t>(token_ids[token]) * top_k + lane]);
-            my_weight = score_of(row[my_id], score_fn);
+            // a table entry outside [0, experts) is reported and never used as an index
+            if (my_id < 0 || my_id >= experts) {
+                if (error != nullptr) atomicCAS(error, kErrNone, kErrIdOutOfRange);
+                my_weight = 0.f;
+            } else {
+                my_weight = score_of(row[my_id], score_fn);
+            }
         }
     } else {
         for (int e = lane; e < experts; e += 32)
@@ -169,7 +176,9 @@ router_select_kernel(const float* __restrict__ logits, const float* __restrict__
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
     if (lane < top_k) {
         float w = my_weight;
-        if (renormalize) w = w / sum;
+        // moe_router.hpp:176-186 divides by (sum + 1e-20f): scores that all underflow give
+        // weights of 0, not NaN
+        if (renormalize) w = w / (sum + 1e-20f);
         w *= scaling;
         w_out[lane] = w;
         id_out[lane] = my_id;
@@ -213,6 +222,8 @@ void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const vo
             "aeon_b200_router_topk: tokens exceed the context's max_tokens and no logits buffer was given");
     require(x_stride >= cfg.hidden && x_stride % 8 == 0,
             "aeon_b200_router_topk: x_stride must be >= hidden and a multiple of 8");
+    require(aligned16(x) && aligned16(gate),
+            "aeon_b200_router_topk: x and gate must be 16-byte aligned (128-bit loads)");
     require(cfg.top_k <= 32, "aeon_b200_router_topk: top_k above 32 is not supported");
     float* logits = logits_out != nullptr ? logits_out : ctx->d_logits;
 
@@ -220,7 +231,7 @@ void launch_router(aeon_b200_ctx* ctx, const void* x, int64_t x_stride, const vo
     const size_t smem = static_cast<size_t>(kSelectWarps) * cfg.experts * sizeof(float);
     router_select_kernel<<<(tokens + kSelectWarps - 1) / kSelectWarps, kSelectWarps * 32, smem, stream>>>(
         logits, bias, hash_table, token_ids, tokens, cfg.experts, cfg.top_k, cfg.score_fn,
-        cfg.renormalize, cfg.routed_scaling, topk_weights, topk_ids);
+        cfg.renormalize, cfg.routed_scaling, topk_weights, topk_ids, ctx->d_error);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 2;
 }
@@ -274,13 +285,15 @@ void launch_router_noalloc(const aeon_b200_moe_config& cfg, const void* x, int64
                           "built-in scratch; use aeon_b200_router_topk with a context beyond that");
     require(x_stride >= cfg.hidden && x_stride % 8 == 0,
             "aeon_b200_router_topk_noalloc: x_stride must be >= hidden and a multiple of 8");
+    require(aligned16(x) && aligned16(gate),
+            "aeon_b200_router_topk_noalloc: x and gate must be 16-byte aligned (128-bit loads)");
     float* logits = noalloc_scratch_for_current_device();
 
     launch_logits(cfg, x, x_stride, gate, tokens, logits, stream);
     const size_t smem = static_cast<size_t>(kSelectWarps) * cfg.experts * sizeof(float);
     router_select_kernel<<<(tokens + kSelectWarps - 1) / kSelectWarps, kSelectWarps * 32, smem, stream>>>(
         logits, bias, nullptr, nullptr, tokens, cfg.experts, cfg.top_k, cfg.score_fn, cfg.renormalize,
-        cfg.routed_scaling, topk_weights, topk_ids);
+        cfg.routed_scaling, topk_weights, topk_ids, nullptr);
     AEON_CUDA_CHECK(cudaGetLastError());
 }
 

@@ -94,6 +94,35 @@ def oracle_routed(oracle, layer: SyntheticLayer, x_bits, ids, weights, token_sub
     return result
 
 
+def mirrored_oracle(oracle, layer, x_bits, ids, weights, tokens):
+    """The oracle for the grouped (prefill) path: fp64 accumulation over the operands that path feeds
+    its tensor-core MMAs -- weights fp16(q * scale), activations fp16, hidden vector rounded to fp16
+    between the two GEMMs -- combined in slot order, for the chosen tokens: {token: vector[H]}.
+    The reference gates its own grouped kernels the same way
+    (tests/test_v4_grouped_wmma_oracle.cpp:63-73,219-228)."""
+    cfg = layer.cfg
+    la = oracle.layout_args(cfg)
+    x16 = synth.from_bits16(x_bits, cfg.act_dtype).astype(np.float16).astype(np.float64)
+    L = cfg.swiglu_limit
+    cache = {}
+    out = {}
+    for t in tokens:
+        acc = np.zeros(cfg.hidden)
+        for s in range(ids.shape[1]):
+            e = int(ids[t, s])
+            if e not in cache:
+                payload = oracle.synth_expert_payload(la, layer.seed, layer.layer, e, layer.scale_table)
+                cache[e] = [oracle.decode_matrix(la, k, payload).astype(np.float16).astype(np.float64)
+                            for k in (0, 2, 1)]
+            w1, w3, w2 = cache[e]
+            gate = np.minimum(w1 @ x16[t], L)
+            up = np.clip(w3 @ x16[t], -L, L)
+            h = (gate / (1.0 + np.exp(-gate)) * up).astype(np.float16).astype(np.float64)
+            acc += float(weights[t, s]) * (w2 @ h)
+        out[t] = acc
+    return out
+
+
 def assert_close(oracle, want, got, label="", tol_abs=TOL_MAX_ABS, tol_l2=TOL_REL_L2):
     s = oracle.compare(want, got)
     assert s["max_abs"] <= tol_abs and s["rel_l2"] <= tol_l2, (label, s)

@@ -50,6 +50,11 @@ def threads() -> int:
     return _L.ao_threads()
 
 
+def set_threads(n: int) -> int:
+    """Thread count of the oracle's parallel loops from now on; returns the count in force."""
+    return _L.ao_set_threads(int(n))
+
+
 def layout(la: LayoutArgs) -> dict:
     out = (c_uint64 * 22)()
     _chk(_L.ao_layout(ctypes.byref(la), out))

@@ -15,31 +15,6 @@ import gpu_support as gs
 pytestmark = pytest.mark.gpu
 
 
-def mirrored_oracle(oracle, layer, x_bits, ids, weights, tokens):
-    """fp64 accumulation over fp16-rounded operands, slot-order combine, for chosen tokens."""
-    cfg = layer.cfg
-    la = oracle.layout_args(cfg)
-    x16 = synth.from_bits16(x_bits, cfg.act_dtype).astype(np.float16).astype(np.float64)
-    L = cfg.swiglu_limit
-    cache = {}
-    out = {}
-    for t in tokens:
-        acc = np.zeros(cfg.hidden)
-        for s in range(ids.shape[1]):
-            e = int(ids[t, s])
-            if e not in cache:
-                payload = oracle.synth_expert_payload(la, layer.seed, layer.layer, e, layer.scale_table)
-                cache[e] = [oracle.decode_matrix(la, k, payload).astype(np.float16).astype(np.float64)
-                            for k in (0, 2, 1)]
-            w1, w3, w2 = cache[e]
-            gate = np.minimum(w1 @ x16[t], L)
-            up = np.clip(w3 @ x16[t], -L, L)
-            h = (gate / (1.0 + np.exp(-gate)) * up).astype(np.float16).astype(np.float64)
-            acc += float(weights[t, s]) * (w2 @ h)
-        out[t] = acc
-    return out
-
-
 @pytest.mark.parametrize("tokens,resident", [(40, list(range(16, 32))), (330, [1, 2, 3, 5, 8, 13, 21, 34, 55])])
 def test_prefill_matches_mirrored_oracle_and_decode(oracle, tokens, resident):
     import torch
@@ -62,7 +37,7 @@ def test_prefill_matches_mirrored_oracle_and_decode(oracle, tokens, resident):
     got = out.cpu().numpy().astype(np.float64) - init
 
     check = sorted({0, tokens // 3, tokens - 1})
-    want = mirrored_oracle(oracle, layer, x_bits, ids, w.astype(np.float64), check)
+    want = gs.mirrored_oracle(oracle, layer, x_bits, ids, w.astype(np.float64), check)
     for t in check:
         s = gs.assert_close(oracle, want[t], got[t], f"prefill token {t}")
         print(f"\nT={tokens} token {t}: vs mirrored oracle max_abs={s['max_abs']:.3e} rel_l2={s['rel_l2']:.3e}")
@@ -101,7 +76,7 @@ def test_prefill_reference_preset(oracle):
     ctx.moe_prefill(layer.pool.base, layer.slot_of, x, torch.from_numpy(ids).cuda(),
                     torch.from_numpy(w).cuda(), out)
     ctx.check()
-    want = mirrored_oracle(oracle, layer, x_bits, ids, w.astype(np.float64), [0, tokens - 1])
+    want = gs.mirrored_oracle(oracle, layer, x_bits, ids, w.astype(np.float64), [0, tokens - 1])
     got = out.cpu().numpy().astype(np.float64)
     for t in (0, tokens - 1):
         gs.assert_close(oracle, want[t], got[t], f"ref preset prefill token {t}")
