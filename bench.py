@@ -42,7 +42,11 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 1/8/32/128 sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default="full", choices=["full", "small", "small128", "b1", "prefill_small", "tp"],
+    ap.add_argument("--eager", action="store_true", help="launch the step kernel by kernel instead of replaying a CUDA graph")
+    ap.add_argument("--nccl-combine", action="store_true",
+                    help="N > 1: combine through the all-to-all collective instead of the peer-memory stores fused "
+                         "with the accumulate")
+    ap.add_argument("--case", default="full", choices=["full", "small", "small128", "b1", "prefill_small", "prefill", "tp"],
                     help="small: one layer of 64 experts at batch 32 (1.45 GB of weights, larger "
                          "than L2), the case the ncu captures under profiles/ run; not a bench value")
     args = ap.parse_args()
@@ -50,8 +54,10 @@ def parse_args():
         args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 32, True, True
     if args.case == "small128":   # the same layer at batch 128: the shared expert takes its tensor-core form
         args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 128, True, True
-    if args.case == "prefill_small":   # 64 experts, 512 tokens through the grouped GEMMs (ncu captures)
+    if args.case == "prefill_small":   # 64 experts, 2048 tokens (256 per expert) through the grouped GEMMs (ncu captures)
         args.layers, args.batch, args.no_sweep, args.no_cpu_baseline = 1, 8, True, True
+    if args.case == "prefill":         # configuration 2 alone: one layer of 256 experts, 4096 tokens
+        args.layers, args.no_sweep, args.no_cpu_baseline = 1, True, True
     if args.case == "b1":      # configuration 1 at batch 1 over 8 layers (launch lists)
         args.batch, args.no_sweep, args.no_cpu_baseline = 1, True, True
     return args
@@ -240,6 +246,20 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def ncu_traffic(kernel: str, distinct_experts: float):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of `kernel`, per expert
+    streamed, times the experts of this launch; the capture's figures are kept in
+    profiles/ncu_dram_traffic.json beside the summary they come from."""
+    path = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
+    try:
+        with open(path) as f:
+            record = json.load(f)[kernel]
+        per_expert = (record["dram_bytes_read"] + record["dram_bytes_write"]) / record["distinct_experts"]
+        return distinct_experts * per_expert
+    except (OSError, KeyError, ValueError, ZeroDivisionError):
+        return None
+
+
 def workload_config(args, n_gpus):
     return {
         "workload": (f"cfg3 stack: {args.layers} MoE layers x decode batch {args.batch}, hidden 7168, "
@@ -247,6 +267,8 @@ def workload_config(args, n_gpus):
                      "bf16 activations, sigmoid router (cfg1 layer at batch 128 per layer)"),
         "layers": args.layers, "batch": args.batch,
         "parallelism": "single GPU, all experts resident" if n_gpus == 1 else f"expert-parallel ep{n_gpus}",
+        "combine": "none" if n_gpus == 1 else ("nccl all-to-all" if getattr(args, "nccl_combine", False)
+                                               else "peer stores fused with the accumulate"),
         "l2_policy": "inputs larger than L2: every layer streams >= 5.7 GB of distinct expert weights",
     }
 
@@ -316,7 +338,7 @@ def prefill_bench(model, cfg, peaks, tokens=4096, iters=5):
 # generator, rank-specific seed); the numerical equivalence of real shards is the job of
 # tests/test_gpu_tp_shards.py.
 # ----------------------------------------------------------------------------------------
-def tp_bench(args, cfg, dist, rank, world, local_rank, peaks):
+def tp_bench(args, cfg, dist, rank, world, local_rank, peaks, group=None):
     import numpy as np
     import torch
     import aeon_b200
@@ -340,10 +362,9 @@ def tp_bench(args, cfg, dist, rank, world, local_rank, peaks):
     out_local = torch.empty(tokens // world, H, dtype=torch.float32, device=dev)
 
     def step():
-        partial.zero_()
-        ctx.moe_prefill(pool.base, slot_of, x, ids, weights, partial)
+        ctx.moe_prefill(pool.base, slot_of, x, ids, weights, partial, overwrite=True)
         if world > 1:
-            dist.reduce_scatter_tensor(out_local, partial)
+            group.reduce_scatter_tensor(out_local, partial)
         else:
             out_local.copy_(partial)
 
@@ -417,15 +438,19 @@ def main():
         if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
                 peaks = json.load(f)
-        line = tp_bench(args, cfg, dist, rank, world, local_rank, peaks)
+        group = aeon_b200.Group.from_process_group(dist, local_rank) if world > 1 else None
+        line = tp_bench(args, cfg, dist, rank, world, local_rank, peaks, group)
         if rank == 0:
             print(json.dumps(line), flush=True)
+        if group is not None:
+            group.close()
         shutdown(dist)
         return
     if args.case in ("small", "small128", "prefill_small"):
         cfg = cfg.copy(experts=64)
     model = stack.MoeStack(cfg, layers=args.layers, max_tokens=args.batch, seed=SEED,
-                           device=local_rank, rank=rank, world=world, dist=dist)
+                           device=local_rank, rank=rank, world=world, dist=dist,
+                           peer_combine=(world > 1 and not args.nccl_combine))
     T, H = args.batch, cfg.hidden
     if T % world:
         raise SystemExit("--batch must divide by the number of GPUs")
@@ -501,14 +526,16 @@ def main():
         model.overlap_shared = True
     # the timed step replays a CUDA graph of the whole stack (one launch per step)
     graph_note = "cuda graph replay"
-    if args.case == "full" and world == 1:
+    if args.case == "full" and not args.eager:
+        # Multi-rank steps are captured too (the collectives are NCCL calls on the capturing
+        # stream). NCCL frees a captured plan only when its graph is destroyed, so the graph is
+        # released before the group is (MoeStack.close); a communicator torn down under a live
+        # graph blocks.
         try:
             model.capture(x_dev, out_dev)
         except Exception as exc:          # keep the eager path if capture is refused
-            graph_note = f"eager launches (graph capture failed: {type(exc).__name__})"
+            graph_note = f"eager launches (graph capture failed: {type(exc).__name__}: {exc})"[:200]
     else:
-        # Multi-rank steps stay eager: a graph holding NCCL collectives made
-        # destroy_process_group() block at exit on this software stack.
         graph_note = "eager launches"
     launches_before = model.launches
     ms, clocks = timed(step_resident, args.steps, warmup, sample_clocks=True)
@@ -562,15 +589,15 @@ def main():
         "gpu_launches": int(round(launches_per_step * args.steps)),
         "gpu_launches_per_step": launches_per_step,
         "roofline": {
-            "bound": "hbm", "kernel": "moe_w13_swiglu_kernel", "achieved": achieved_a, "peak": peak_gbs,
+            "bound": "hbm", "kernel": "moe_w13_rows_kernel", "achieved": achieved_a, "peak": peak_gbs,
             "unit": "GB/s", "frac": (achieved_a / peak_gbs) if achieved_a else None,
             "peak_source": peak_kind,
-            # ncu DRAM traffic of this kernel on the small case (63 experts: 954.3 MB read +
-            # 5.7 MB written, profiles/moe_w13_swiglu_small_decode.md), scaled by the distinct
-            # experts of a launch; every weight byte is read once, so traffic is proportional
-            "traffic": mean_distinct * (959_984_128 / 63.0),
+            # measured DRAM bytes of one ncu capture of this kernel (a small case), scaled to this
+            # launch by the distinct experts streamed: every weight byte is read once, so the traffic
+            # is proportional (null when no capture record is present)
+            "traffic": ncu_traffic("moe_w13_rows_kernel", mean_distinct),
             "algorithmic_bytes_per_launch": bytes_a, "avg_launch_ms": avg_a_ms, "launches_timed": n_a,
-            "second_kernel": {"kernel": "moe_w2_contrib_kernel", "achieved": achieved_b,
+            "second_kernel": {"kernel": "moe_w2_rows_kernel", "traffic": ncu_traffic("moe_w2_rows_kernel", mean_distinct), "achieved": achieved_b,
                               "frac": (achieved_b / peak_gbs) if achieved_b else None,
                               "algorithmic_bytes_per_launch": bytes_b, "avg_launch_ms": avg_b_ms},
             "whole_step": {"algorithmic_bytes": step_bytes,
@@ -599,7 +626,9 @@ def main():
                                                           iters=max(10, args.steps)))
         section("prefill", lambda: prefill_bench(model, cfg, peaks, iters=max(3, min(args.steps, 10))))
     if args.case == "prefill_small":
-        section("prefill", lambda: prefill_bench(model, cfg, peaks, tokens=512, iters=2))
+        section("prefill", lambda: prefill_bench(model, cfg, peaks, tokens=2048, iters=2))
+    if args.case == "prefill":
+        section("prefill", lambda: prefill_bench(model, cfg, peaks, iters=max(3, min(args.steps, 10))))
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
         def cpu_section():
             tps, sec, cores = cpu_oracle_tokens_per_s(args.layers, args.batch, 1)
@@ -612,10 +641,10 @@ def main():
     if world > 1 and args.case == "full":
         model.release_graph()
         peaks_tp = dict(peaks)
-        section("tp", lambda: tp_bench(args, cfg, dist, rank, world, local_rank, peaks_tp))
+        section("tp", lambda: tp_bench(args, cfg, dist, rank, world, local_rank, peaks_tp, model.group))
     if rank == 0:
         print(json.dumps(line), flush=True)
-    model.release_graph()
+    model.close()
     shutdown(dist)
     if not parity["ok"]:
         raise SystemExit(f"parity check failed: {parity}")

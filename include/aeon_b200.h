@@ -150,6 +150,19 @@ uint64_t aeon_b200_ctx_scratch_bytes(const aeon_b200_ctx* ctx);
 int aeon_b200_ctx_check(aeon_b200_ctx* ctx, void* stream);
 /* Kernel launches issued by this context since creation (the benchmark's count). */
 uint64_t aeon_b200_ctx_launches(const aeon_b200_ctx* ctx);
+/* Declares how many slots the expert pool given to this context's calls has. From then on a
+ * slot_of_expert entry at or above it is reported (aeon_b200_ctx_check: OUT_OF_RANGE) and its
+ * expert treated as absent, instead of being used as an address. 0 withdraws the declaration.
+ * The reference bounds its slot by construction (ExpertPayloadPool::get_slot_base throws,
+ * src/infrastructure/expert/storage/expert_payload_pool.hpp:70-78); here the table lives on the
+ * device, so the check does too. */
+int aeon_b200_ctx_set_pool_slots(aeon_b200_ctx* ctx, int slots);
+/* 1 when the library was built with -DAEON_B200_BOUNDS=1: every run-time-derived index in the
+ * kernels is checked against its buffer and skipped when outside (the error flag is set), and
+ * aeon_b200_ctx_check also verifies guard regions behind the context's scratch buffers. The
+ * stand-in for a memory checker; the reference relies on its own host-side checks
+ * (src/infrastructure/hip_check.hpp:20-27). */
+int aeon_b200_bounds_checked(void);
 
 /* Expert payload pool: one device slab of slots x payload_bytes, a slot being a
  * byte-identical expert payload. Replaces ExpertPayloadPool
@@ -309,6 +322,102 @@ int aeon_b200_hc_post(aeon_b200_ctx* ctx, const float* moe_out, int64_t moe_stri
  * (src/platform/ops/moe_accumulate.hpp:73-92). */
 int aeon_b200_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks,
                          int tokens, int hidden, void* stream);
+
+/* ---- devices, streams, events, pinned memory --------------------------------------------------
+ * What a C++ host needs around the kernels without including the CUDA runtime. Replaces the
+ * reference's direct runtime calls in select_device / DeviceScope (src/platform/device.hpp:29-90),
+ * DeviceStreams (src/infrastructure/device_streams.hpp:32-74), enable_peer_access
+ * (src/infrastructure/parallel/peer_access.hpp:29-50) and the pinned staging and event ordering of
+ * its tiered expert supply (src/infrastructure/expert/transport/tiered_expert_supply.hpp).
+ * aeon_b200_device_select validates the index against the visible devices and makes it current
+ * (OUT_OF_RANGE for a bad index: a caller that asked for a device that is not there wants to
+ * know). Streams are non-blocking and belong to the device current at creation. Peer access is
+ * best effort and never an error: enabled_host tells whether the pair is enabled afterwards. */
+int aeon_b200_device_count(int* count_host);
+int aeon_b200_device_current(int* device_host);
+int aeon_b200_device_select(int index);
+int aeon_b200_device_describe(int index, char* name_host, int name_bytes, int* pci_bus_host,
+                              int* sm_count_host, uint64_t* memory_bytes_host);
+int aeon_b200_device_enable_peer_access(int accessor, int peer, int* enabled_host);
+int aeon_b200_device_alloc(uint64_t bytes, int device, void** out_host);
+int aeon_b200_device_free(void* device_ptr);
+int aeon_b200_stream_create(void** stream_host);
+int aeon_b200_stream_destroy(void* stream);
+int aeon_b200_stream_synchronize(void* stream);
+int aeon_b200_stream_wait_event(void* stream, void* event);
+int aeon_b200_event_create(void** event_host);
+int aeon_b200_event_destroy(void* event);
+int aeon_b200_event_record(void* event, void* stream);
+int aeon_b200_event_synchronize(void* event);
+int aeon_b200_host_alloc_pinned(uint64_t bytes, void** out_host);
+int aeon_b200_host_free_pinned(void* pinned);
+int aeon_b200_copy_to_device_async(void* dst_device, const void* src_host, uint64_t bytes, void* stream);
+int aeon_b200_copy_to_host_async(void* dst_host, const void* src_device, uint64_t bytes, void* stream);
+
+/* ---- multi-GPU groups (one process per GPU, NCCL over NVLink / NVSwitch) -------------------
+ * The reference engine refuses tensor-parallel topologies today
+ * (src/architecture/deepseek_v4/runtime/v4_model_host.hpp:94-100) and plans a C++
+ * TensorParallelGroup with an NCCL-style communicator
+ * (plans-and-docs/execution/active/MULTI_GPU_EXECUTION_PLAN.md:189-235); these entry points are
+ * that layer for the routed-expert path. One rank creates an id, hands the 128 bytes to the
+ * others by any host channel, and every rank creates its group with it (a collective call).
+ * NCCL is loaded on first use; a library build without NCCL present still serves one GPU. */
+#define AEON_B200_GROUP_ID_BYTES 128
+typedef struct aeon_b200_group aeon_b200_group;
+int aeon_b200_group_unique_id(void* id_host);
+int aeon_b200_group_create(const void* id_host, int rank, int world, int device,
+                           aeon_b200_group** out_host);
+int aeon_b200_group_destroy(aeon_b200_group* group);
+int aeon_b200_group_rank(const aeon_b200_group* group);
+int aeon_b200_group_world(const aeon_b200_group* group);
+
+/* Expert-parallel dispatch: every rank contributes its tokens_local activation rows of
+ * row_bytes bytes each and receives all ranks' rows in rank order, x_all[world * tokens_local]
+ * (an all-gather; at decode sizes a padded all-to-all would move the same bytes). */
+int aeon_b200_ep_dispatch(aeon_b200_group* group, const void* x_local, int tokens_local,
+                          int64_t row_bytes, void* x_all, void* stream);
+/* Expert-parallel exchange: partial[world * tokens_local, hidden] holds this rank's partial
+ * output rows for every token of the batch; rows [r * tokens_local, (r+1) * tokens_local) go to
+ * rank r, whose recv[s, :, :] receives the slice computed by rank s (an equal-split all-to-all).
+ * aeon_b200_ep_combine then adds the `world` slices in rank order. */
+int aeon_b200_ep_exchange(aeon_b200_group* group, const float* partial, int tokens_local, int hidden,
+                          float* recv, void* stream);
+/* Tensor-parallel reduce: partial[world * tokens_local, hidden] fp32 partial outputs (each rank
+ * holds a slice of every expert's intermediate dimension) are summed over the ranks and rank r
+ * keeps rows [r * tokens_local, (r+1) * tokens_local) in out_local (a reduce-scatter). The W2
+ * split this finishes is the one tests/test_w2_shard_equivalence.cpp:138-296 shows exact. */
+int aeon_b200_tp_reduce(aeon_b200_group* group, const float* partial, int tokens_local, int hidden,
+                        float* out_local, void* stream);
+/* Pipeline-stage hand-off of `bytes` bytes to / from rank `peer`: a byte copy, like
+ * handoff_residual (src/architecture/deepseek_v4/runtime/v4_graph.hpp:454-513). */
+int aeon_b200_pp_send(aeon_b200_group* group, const void* rows, uint64_t bytes, int peer, void* stream);
+int aeon_b200_pp_recv(aeon_b200_group* group, void* rows, uint64_t bytes, int peer, void* stream);
+
+/* ---- expert-parallel combine fused with the accumulate, over peer memory ---------------------
+ * The one-kernel form of "accumulate, exchange, combine": every rank owns a receive buffer
+ * [world, tokens_local_max, hidden] fp32 that its peers map through CUDA IPC (created
+ * collectively over a group; at most 8 ranks of one box). aeon_b200_moe_accumulate_push is the
+ * second half of a deferred decode call (like aeon_b200_moe_accumulate) for an expert-parallel
+ * rank: it sums, per token of the whole batch and in slot order, the per-draw slices of the
+ * experts resident here and stores each row straight into the receive buffer of the rank that
+ * owns the token (plain peer stores over NVLink), then raises that owner's flag for this rank.
+ * aeon_b200_ep_peer_combine waits, with a bound, for the `world` flags of the call and adds the
+ * slices to out[tokens_local, :] in rank order. A flag that does not arrive within the budget
+ * (default 2 s) is reported by aeon_b200_ctx_check as TIMEOUT; the peer object is then out of
+ * step and must be destroyed. Calls must alternate push / combine, once each per layer on every
+ * rank, with the layer's dispatch (aeon_b200_ep_dispatch) between one layer's combine and the
+ * next layer's push: that collective is what keeps a fast rank from overwriting rows a slow
+ * owner still reads. No counterpart in the reference (no expert parallelism there); the
+ * summation order follows src/platform/ops/moe_accumulate.hpp:73-92. */
+typedef struct aeon_b200_ep_peer aeon_b200_ep_peer;
+int aeon_b200_ep_peer_create(aeon_b200_group* group, int device, int tokens_local_max, int hidden,
+                             aeon_b200_ep_peer** out_host);
+int aeon_b200_ep_peer_destroy(aeon_b200_ep_peer* peer);
+int aeon_b200_ep_peer_set_wait_budget(aeon_b200_ep_peer* peer, double milliseconds);
+int aeon_b200_moe_accumulate_push(aeon_b200_ctx* ctx, aeon_b200_ep_peer* peer, const int32_t* slot_of_expert,
+                                  const int32_t* topk_ids, int tokens_local, void* stream);
+int aeon_b200_ep_peer_combine(aeon_b200_ctx* ctx, aeon_b200_ep_peer* peer, float* out, int64_t out_stride,
+                              int tokens_local, void* stream);
 
 /* Statistics of the last decode/prefill call of this context (host values read
  * back after a synchronise): distinct experts touched and work-list entries. */

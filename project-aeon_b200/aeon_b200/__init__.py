@@ -13,7 +13,8 @@ from ctypes import (POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint1
                     c_uint64, c_void_p)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libaeon_b200.so")
+# AEON_B200_LIBRARY selects another build of the same library (the bounds-checked one, say)
+LIB_PATH = os.environ.get("AEON_B200_LIBRARY") or os.path.join(os.path.dirname(_HERE), "lib", "libaeon_b200.so")
 
 F16, BF16 = 0, 1
 SCORE_SQRT_SOFTPLUS, SCORE_SIGMOID = 0, 1
@@ -38,6 +39,18 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_expert_shard_bytes", "aeon_b200_pack_expert_shards", "aeon_b200_unpack_expert_shards",
     "aeon_b200_expert_rank_slice", "aeon_b200_merge_expert_shards",
     "aeon_b200_hc_params_default", "aeon_b200_hc_ffn_front", "aeon_b200_hc_post",
+    "aeon_b200_group_unique_id", "aeon_b200_group_create", "aeon_b200_group_destroy",
+    "aeon_b200_group_rank", "aeon_b200_group_world", "aeon_b200_ep_dispatch", "aeon_b200_ep_exchange",
+    "aeon_b200_tp_reduce", "aeon_b200_pp_send", "aeon_b200_pp_recv",
+    "aeon_b200_device_count", "aeon_b200_device_current", "aeon_b200_device_select",
+    "aeon_b200_device_describe", "aeon_b200_device_enable_peer_access", "aeon_b200_device_alloc",
+    "aeon_b200_device_free", "aeon_b200_stream_create", "aeon_b200_stream_destroy",
+    "aeon_b200_stream_synchronize", "aeon_b200_stream_wait_event", "aeon_b200_event_create",
+    "aeon_b200_event_destroy", "aeon_b200_event_record", "aeon_b200_event_synchronize",
+    "aeon_b200_host_alloc_pinned", "aeon_b200_host_free_pinned", "aeon_b200_copy_to_device_async",
+    "aeon_b200_copy_to_host_async", "aeon_b200_ctx_set_pool_slots", "aeon_b200_bounds_checked",
+    "aeon_b200_ep_peer_create", "aeon_b200_ep_peer_destroy", "aeon_b200_ep_peer_set_wait_budget",
+    "aeon_b200_moe_accumulate_push", "aeon_b200_ep_peer_combine",
 ]
 
 
@@ -141,6 +154,22 @@ def lib() -> ctypes.CDLL:
                                                c_void_p]
     L.aeon_b200_synth_fill_dense16.argtypes = [c_void_p, c_uint64, c_uint64, c_uint32, c_uint32,
                                                c_void_p, c_uint32, c_void_p]
+    L.aeon_b200_ctx_set_pool_slots.argtypes = [c_void_p, c_int]
+    L.aeon_b200_ep_peer_create.argtypes = [c_void_p, c_int, c_int, c_int, POINTER(c_void_p)]
+    L.aeon_b200_ep_peer_destroy.argtypes = [c_void_p]
+    L.aeon_b200_ep_peer_set_wait_budget.argtypes = [c_void_p, ctypes.c_double]
+    L.aeon_b200_moe_accumulate_push.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+    L.aeon_b200_ep_peer_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]
+    L.aeon_b200_group_unique_id.argtypes = [c_void_p]
+    L.aeon_b200_group_create.argtypes = [c_void_p, c_int, c_int, c_int, POINTER(c_void_p)]
+    L.aeon_b200_group_destroy.argtypes = [c_void_p]
+    L.aeon_b200_group_rank.argtypes = [c_void_p]
+    L.aeon_b200_group_world.argtypes = [c_void_p]
+    L.aeon_b200_ep_dispatch.argtypes = [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]
+    L.aeon_b200_ep_exchange.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    L.aeon_b200_tp_reduce.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    L.aeon_b200_pp_send.argtypes = [c_void_p, c_void_p, c_uint64, c_int, c_void_p]
+    L.aeon_b200_pp_recv.argtypes = [c_void_p, c_void_p, c_uint64, c_int, c_void_p]
     _lib = L
     return L
 
@@ -148,6 +177,11 @@ def lib() -> ctypes.CDLL:
 def check(status: int) -> None:
     if status != 0:
         raise AeonError(status, lib().aeon_b200_last_error().decode())
+
+
+def bounds_checked() -> bool:
+    """True when the library is the bounds-checked build (-DAEON_B200_BOUNDS=1)."""
+    return bool(lib().aeon_b200_bounds_checked())
 
 
 def preset(name: str) -> MoeConfig:
@@ -333,6 +367,11 @@ class Context:
     def check(self) -> None:
         check(lib().aeon_b200_ctx_check(self._h, _stream()))
 
+    def set_pool_slots(self, slots: int) -> None:
+        """Declares the slot count of the pools this context is used with: a slot table entry at or
+        above it is reported by check() instead of being used as an address."""
+        check(lib().aeon_b200_ctx_set_pool_slots(self._h, slots))
+
     def last_stats(self):
         distinct, entries = c_int32(), c_int32()
         check(lib().aeon_b200_ctx_last_stats(self._h, _stream(), ctypes.byref(distinct),
@@ -457,3 +496,122 @@ def ep_combine(out, partials) -> None:
     ranks, tokens, hidden = partials.shape
     check(lib().aeon_b200_ep_combine(_rows(out, "out"), out.stride(0), _dense(partials, "partials"), ranks,
                                      tokens, hidden, _stream()))
+
+
+GROUP_ID_BYTES = 128
+
+
+def group_unique_id() -> bytes:
+    """The 128-byte id one rank creates and hands to the others (any host channel)."""
+    buf = ctypes.create_string_buffer(GROUP_ID_BYTES)
+    check(lib().aeon_b200_group_unique_id(buf))
+    return buf.raw
+
+
+class Group:
+    """This rank's membership of a multi-GPU group (the library's own NCCL communicator).
+
+    The data-path collectives of expert / tensor / pipeline parallelism go through the C ABI,
+    so a C++ host and this binding share one path. The methods named like torch.distributed's
+    (all_gather_into_tensor, all_to_all_single, reduce_scatter_tensor, send, recv) let the
+    protocol functions of aeon_b200.stack run over a Group or over a torch process group."""
+
+    def __init__(self, unique_id: bytes, rank: int, world: int, device: int):
+        if len(unique_id) != GROUP_ID_BYTES:
+            raise AeonError(1, "a group id is 128 bytes")
+        handle = c_void_p()
+        check(lib().aeon_b200_group_create(unique_id, rank, world, device, ctypes.byref(handle)))
+        self._h, self.rank, self.world, self.device = handle, rank, world, device
+
+    @classmethod
+    def from_process_group(cls, dist, device: int, group=None):
+        """Bootstraps over an initialised torch.distributed group: rank 0's id is broadcast."""
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [group_unique_id() if rank == 0 else None]
+        src = 0 if group is None else dist.get_global_rank(group, 0)
+        dist.broadcast_object_list(box, src=src, group=group)
+        return cls(box[0], rank, world, device)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            check(lib().aeon_b200_group_destroy(self._h))
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def get_rank(self) -> int:
+        return self.rank
+
+    def get_world_size(self) -> int:
+        return self.world
+
+    # -- the C ABI calls ----------------------------------------------------------------------
+    def ep_dispatch(self, x_local, x_all) -> None:
+        row_bytes = x_local.shape[1] * x_local.element_size()
+        check(lib().aeon_b200_ep_dispatch(self._h, _dense(x_local, "x_local"), x_local.shape[0], row_bytes,
+                                          _dense(x_all, "x_all"), _stream()))
+
+    def ep_exchange(self, partial, recv) -> None:
+        tl = partial.shape[0] // self.world
+        check(lib().aeon_b200_ep_exchange(self._h, _dense(partial, "partial"), tl, partial.shape[1],
+                                          _dense(recv, "recv"), _stream()))
+
+    def tp_reduce(self, partial, out_local) -> None:
+        check(lib().aeon_b200_tp_reduce(self._h, _dense(partial, "partial"), out_local.shape[0],
+                                        out_local.shape[1], _dense(out_local, "out_local"), _stream()))
+
+    # -- torch.distributed-shaped names, for the protocol functions ------------------------------
+    def all_gather_into_tensor(self, out, inp, group=None) -> None:
+        self.ep_dispatch(inp, out)
+
+    def all_to_all_single(self, out, inp, group=None) -> None:
+        self.ep_exchange(inp, out)
+
+    def reduce_scatter_tensor(self, out, inp, group=None) -> None:
+        self.tp_reduce(inp, out)
+
+    def send(self, tensor, dst: int) -> None:
+        check(lib().aeon_b200_pp_send(self._h, _dense(tensor, "tensor"), tensor.numel() * tensor.element_size(),
+                                      dst, _stream()))
+
+    def recv(self, tensor, src: int) -> None:
+        check(lib().aeon_b200_pp_recv(self._h, _dense(tensor, "tensor"), tensor.numel() * tensor.element_size(),
+                                      src, _stream()))
+
+
+class PeerCombine:
+    """Receive buffers of an expert-parallel group mapped between the ranks of one box (CUDA IPC),
+    for the combine that is fused with the slot-order accumulate: push() is the second half of a
+    deferred decode call and stores every finished row straight into its owner's buffer, combine()
+    waits (bounded) for all ranks' rows and adds them in rank order. Creation is collective."""
+
+    def __init__(self, group: Group, device: int, tokens_local_max: int, hidden: int):
+        handle = c_void_p()
+        check(lib().aeon_b200_ep_peer_create(group._h, device, tokens_local_max, hidden, ctypes.byref(handle)))
+        self._h, self.group = handle, group
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            check(lib().aeon_b200_ep_peer_destroy(self._h))
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_wait_budget(self, milliseconds: float) -> None:
+        check(lib().aeon_b200_ep_peer_set_wait_budget(self._h, float(milliseconds)))
+
+    def push(self, ctx: Context, slot_of_expert, ids, tokens_local: int) -> None:
+        check(lib().aeon_b200_moe_accumulate_push(ctx._h, self._h, _dense(slot_of_expert, "slot_of_expert"),
+                                                  _dense(ids, "ids"), tokens_local, _stream()))
+
+    def combine(self, ctx: Context, out) -> None:
+        check(lib().aeon_b200_ep_peer_combine(ctx._h, self._h, _rows(out, "out"), out.stride(0), out.shape[0],
+                                              _stream()))

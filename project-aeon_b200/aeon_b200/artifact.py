@@ -111,29 +111,51 @@ def write_expert_artifact(model_dir: str, cfg, layers: int, source_of, max_tenso
         for off, length in entries:
             idx.write(struct.pack("<QQ", off, length))
     if write_manifest:
-        manifest = {
-            "manifest_version": 2 if D > 1 else 1,
-            "weight_backend": "swizzled_w4a16",
-            "num_layers": layers,
-            "experts_per_layer": cfg.experts,
-            "max_tensor_parallel": D,
-            "artifact": {
-                "experts_filename": EXPERTS_FILENAME,
-                "index_filename": INDEX_FILENAME,
-                "dense_filename": DENSE_FILENAME,
-                "dense_format_version": DENSE_FORMAT_VERSION,
-                "expert_format": "swizzled_w4a16",
-                "expert_format_version": fmt.version,
-                "expert_sector_size": SECTOR_SIZE,
-                "expert_payload_bytes": fmt.payload_bytes,
-                "expert_shard_count": D,
-                "expert_shard_bytes": shard_bytes,
-            },
-        }
-        with open(os.path.join(model_dir, MANIFEST_FILENAME), "w", encoding="utf-8") as f:
-            json.dump(manifest, f, indent=2)
-            f.write("\n")
+        write_model_manifest(model_dir, fmt)
     return fmt
+
+
+def write_model_manifest(model_dir: str, fmt: ExpertFormat, model_family: str = "deepseek",
+                         architecture: str = "deepseek_v4") -> dict:
+    """model_manifest.json as the reference's loader reads it
+    (src/infrastructure/artifact/model_manifest.hpp:102-209: identity, weight backend, file names,
+    versions, sizes) plus the shard fields of the shard-aware container. dense_file_bytes is taken
+    from the dense file if it is already there; write_dense_container fills it in otherwise."""
+    dense_path = os.path.join(model_dir, DENSE_FILENAME)
+    manifest = {
+        "manifest_version": 2 if fmt.shard_count > 1 else 1,
+        "model_family": model_family,
+        "architecture": architecture,
+        "weight_backend": "swizzled_w4a16",
+        "dense_file_bytes": os.path.getsize(dense_path) if os.path.exists(dense_path) else 0,
+        "num_layers": fmt.num_layers,
+        "experts_per_layer": fmt.experts_per_layer,
+        "max_tensor_parallel": fmt.shard_count,
+        "artifact": {
+            "experts_filename": EXPERTS_FILENAME,
+            "index_filename": INDEX_FILENAME,
+            "dense_filename": DENSE_FILENAME,
+            "dense_format_version": DENSE_FORMAT_VERSION,
+            "expert_format": "swizzled_w4a16",
+            "expert_format_version": fmt.version,
+            "expert_sector_size": fmt.sector_size,
+            "expert_payload_bytes": fmt.payload_bytes,
+            "expert_shard_count": fmt.shard_count,
+            "expert_shard_bytes": fmt.shard_bytes or fmt.payload_bytes,
+        },
+    }
+    with open(os.path.join(model_dir, MANIFEST_FILENAME), "w", encoding="utf-8") as f:
+        json.dump(manifest, f, indent=2)
+        f.write("\n")
+    return manifest
+
+
+def read_model_manifest(model_dir: str) -> dict | None:
+    path = os.path.join(model_dir, MANIFEST_FILENAME)
+    if not os.path.exists(path):
+        return None
+    with open(path, encoding="utf-8") as f:
+        return json.load(f)
 
 
 class ExpertArtifact:
@@ -262,6 +284,18 @@ def write_dense_container(path: str, tensors) -> None:
         f.write(b"\x00" * pad)
         for a in blobs:
             f.write(a.tobytes())
+    _record_dense_size(path)
+
+
+def _record_dense_size(dense_path: str) -> None:
+    """A manifest beside a freshly written dense file learns the file's size."""
+    model_dir = os.path.dirname(os.path.abspath(dense_path))
+    manifest = read_model_manifest(model_dir)
+    if manifest is not None and os.path.basename(dense_path) == manifest["artifact"]["dense_filename"]:
+        manifest["dense_file_bytes"] = os.path.getsize(dense_path)
+        with open(os.path.join(model_dir, MANIFEST_FILENAME), "w", encoding="utf-8") as f:
+            json.dump(manifest, f, indent=2)
+            f.write("\n")
 
 
 class DenseContainer:
@@ -482,6 +516,7 @@ def _write_dense_raw(path: str, tensors) -> None:
         f.write(b"\x00" * pad)
         for _, _, _, raw in tensors:
             f.write(np.asarray(raw).tobytes())
+    _record_dense_size(path)
 
 
 def _main(argv=None) -> int:

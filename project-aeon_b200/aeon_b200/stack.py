@@ -35,20 +35,34 @@ def _torch_bits(bits: np.ndarray, dtype: int, device):
     return t.view(torch.bfloat16 if dtype == aeon_b200.BF16 else torch.float16)
 
 
+def ep_layer_forward_peer(ops, dist, world, x_local, out_local, x_all, group=None):
+    """The same layer with the combine fused into the accumulate over peer memory: after the
+    dispatch gather and the replicated router, `ops.routed_push` runs the resident experts and
+    stores each finished partial row straight into the receive buffer of the rank that owns the
+    token; `ops.combine_peer` waits for every rank's rows and adds them in rank order. One
+    collective per layer instead of two, no local partial, no exchange kernel."""
+    scope = {} if group is None else {"group": group}
+    dist.all_gather_into_tensor(x_all, x_local, **scope)
+    weights, ids = ops.router(x_all)
+    ops.shared(x_local, out_local)
+    ops.routed_push(x_all, ids, weights, out_local, x_local.shape[0])
+    ops.combine_peer(out_local)
+    return weights, ids
+
+
 def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv, group=None):
     """One expert-parallel MoE layer on this rank (the protocol of the module docstring).
 
     `ops` supplies the compute: router(x) -> (weights, ids); shared(x, out) writes the shared
-    expert into out; routed(x, ids, weights, out, skip_absent) adds the resident experts'
-    contributions; combine(out, recv) adds recv[r] for r = 0..world-1 in that order. The
+    expert into out; routed(x, ids, weights, out, skip_absent, overwrite) adds the resident
+    experts' contributions to out, or writes them over it when overwrite is set; combine(out, recv) adds recv[r] for r = 0..world-1 in that order. The
     collectives are `dist`'s (NCCL on GPUs; gloo in the CPU tests of the protocol).
     Returns the (replicated) routing of the whole batch."""
     scope = {} if group is None else {"group": group}          # the ranks of one pipeline stage
     dist.all_gather_into_tensor(x_all, x_local, **scope)        # dispatch
     weights, ids = ops.router(x_all)                            # replicated, identical inputs
     ops.shared(x_local, out_local)
-    partial.zero_()
-    ops.routed(x_all, ids, weights, partial, skip_absent=True)
+    ops.routed(x_all, ids, weights, partial, skip_absent=True, overwrite=True)   # writes, needs no zero fill
     if not recv.is_contiguous():
         raise ValueError("the receive buffer must be a dense [world, tokens_local, hidden] block")
     dist.all_to_all_single(recv.view(-1, recv.shape[-1]), partial, **scope)   # combine: rows to owners
@@ -134,8 +148,7 @@ def tp_layer_forward(ops, dist, world, x, out_local, partial):
     tl = tokens // world
     rank = dist.get_rank()
     weights, ids = ops.router(x)
-    partial.zero_()
-    ops.routed(x, ids, weights, partial, skip_absent=False)
+    ops.routed(x, ids, weights, partial, skip_absent=False, overwrite=True)
     routed_local = out_local.new_empty(out_local.shape)
     dist.reduce_scatter_tensor(routed_local, partial)
     ops.shared(x[rank * tl:(rank + 1) * tl], out_local)
@@ -180,12 +193,23 @@ class _DeviceOps:
     def shared(self, x, out):
         self.ctx.shared_expert(self.w.shared[0], self.w.shared[1], self.w.shared[2], x, out)
 
-    def routed(self, x, ids, weights, out, skip_absent):
+    def routed(self, x, ids, weights, out, skip_absent, overwrite=False):
         self.ctx.moe_decode(self.w.pool.base, self.w.slot_of, x, ids, weights, out,
-                            skip_absent=skip_absent)
+                            skip_absent=skip_absent, overwrite=overwrite)
 
     def combine(self, out, recv):
         aeon_b200.ep_combine(out, recv)
+
+    # -- the peer-memory form of the combine -------------------------------------------------------
+    peer = None
+
+    def routed_push(self, x, ids, weights, scratch_out, tokens_local):
+        self.ctx.moe_decode(self.w.pool.base, self.w.slot_of, x, ids, weights, scratch_out,
+                            skip_absent=True, defer_accumulate=True)
+        self.peer.push(self.ctx, self.w.slot_of, ids, tokens_local)
+
+    def combine_peer(self, out):
+        self.peer.combine(self.ctx, out)
 
 
 class MoeLayerWeights:
@@ -271,7 +295,7 @@ class LoadedLayer:
 
 class MoeStack:
     def __init__(self, cfg, layers: int, max_tokens: int, seed: int = 0, device: int = 0,
-                 rank: int = 0, world: int = 1, dist=None):
+                 rank: int = 0, world: int = 1, dist=None, peer_combine: bool = False):
         import torch
         if world > 1 and (cfg.experts % world or max_tokens % world):
             raise aeon_b200.AeonError(1, "experts and tokens must divide by the number of ranks")
@@ -290,11 +314,18 @@ class MoeStack:
                         for l in range(layers)]
         self.ctx = aeon_b200.Context(cfg, device, max_tokens)
         self._stats = [dict(distinct=0, draws=0, tokens=0) for _ in range(layers)]
+        self.group = None
+        self.peer = None
         if world > 1:
             H = cfg.hidden
+            # the data-path collectives run on the library's own communicator (C ABI); `dist` only
+            # carries the 128-byte id to the other ranks
+            self.group = aeon_b200.Group.from_process_group(dist, device)
             self.x_all = torch.empty(max_tokens, H, dtype=self.weights[0].gate.dtype, device=dev)
             self.partial = torch.empty(max_tokens, H, dtype=torch.float32, device=dev)
             self.recv = torch.empty(world, max_tokens // world, H, dtype=torch.float32, device=dev)
+            # peer_combine: the combine fused with the accumulate over CUDA-IPC mapped buffers
+            self.peer = aeon_b200.PeerCombine(self.group, device, max_tokens // world, H) if peer_combine else None
         self._extra_launches = 0
         # False: the shared expert runs on the caller's stream ahead of the router, so that no
         # other kernel is resident while the routed kernels run (used to time them alone)
@@ -345,6 +376,16 @@ class MoeStack:
         self._graph_launches = self.launches - before
         self._graph, self._graph_x, self._graph_out = graph, x.data_ptr(), out.data_ptr()
 
+    def close(self):
+        """Releases the captured step and leaves the multi-GPU group (a collective call)."""
+        self.release_graph()
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
+        if self.group is not None:
+            self.group.close()
+            self.group = None
+
     def release_graph(self):
         """Drops the captured step. A graph that holds NCCL nodes keeps references into the
         communicator (NCCL frees a captured plan only when its graph is destroyed), so the
@@ -385,7 +426,18 @@ class MoeStack:
         else:
             tl = x.shape[0]
             tokens_seen = tl * self.world
-            weights, ids = ep_layer_forward(ops, self.dist, self.world, x, out,
+            if self.peer is not None:
+                ops.peer = self.peer
+                weights, ids = ep_layer_forward_peer(ops, self.group, self.world, x, out, self.x_all[:tokens_seen])
+                self._extra_launches += 1
+                if collect_stats:
+                    distinct, _ = ctx.last_stats()
+                    flat = ids.flatten()
+                    local = ((flat >= self.first_expert) &
+                             (flat < self.first_expert + self.cfg.experts // self.world)).sum().item()
+                    self._stats[l] = dict(distinct=distinct, draws=int(local), tokens=tokens_seen)
+                return (weights, ids) if return_routing else None
+            weights, ids = ep_layer_forward(ops, self.group, self.world, x, out,
                                             self.x_all[:tokens_seen], self.partial[:tokens_seen],
                                             self.recv.view(-1)[:tokens_seen * x.shape[1]]
                                             .view(self.world, tl, x.shape[1]))
@@ -417,17 +469,30 @@ class MoeStack:
                 distinct.append(self._stats[l]["distinct"])
             torch.cuda.synchronize()
             total_iters = max(iters, self.layers)
+            # per-kernel device times: eager launches with the library's events around the kernels
             self.ctx.set_timing(True)
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
             for i in range(total_iters):
                 l = i % self.layers
                 self.forward_layer(l, x[l, :b], out[l, :b])
-            end.record()
-            torch.cuda.synchronize()
             (ms_a, n_a), (ms_b, n_b) = self.ctx.kernel_times()
             self.ctx.set_timing(False)
-            us_layer = start.elapsed_time(end) * 1e3 / total_iters
+            # the layer time: one pass over the layers replayed as a CUDA graph, so the figure is the
+            # device's and not the host's launch rate (at batch 1 a layer is ten launches of 3-40 us)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for l in range(self.layers):
+                    self.forward_layer(l, x[l, :b], out[l, :b])
+            replays = max(1, total_iters // self.layers)
+            graph.replay()
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(replays):
+                graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            us_layer = start.elapsed_time(end) * 1e3 / (replays * self.layers)
+            graph.reset()
             mean_d = float(np.mean(distinct))
             routed_bytes = mean_d * expert_bytes
             kernel_us = (ms_a + ms_b) * 1e3 / max(n_a, 1)

@@ -131,11 +131,9 @@ void relayout_w4a16(const uint32_t* src_packed, const uint16_t* src_scale, uint3
 namespace {
 
 template <class T>
-T* device_alloc(size_t count, uint64_t& total) {
-    T* p = nullptr;
-    AEON_CUDA_CHECK(cudaMalloc(&p, count * sizeof(T)));
+T* device_alloc(aeon_b200_ctx* ctx, size_t count, uint64_t& total, const char* name) {
     total += count * sizeof(T);
-    return p;
+    return static_cast<T*>(ctx_device_alloc(ctx, count * sizeof(T), name));
 }
 
 cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
@@ -152,12 +150,42 @@ struct DeviceGuard {
     }
 };
 
+}  // namespace
+
+void* ctx_device_alloc(aeon_b200_ctx* ctx, size_t bytes, const char* name) {
+    void* p = nullptr;
+    AEON_CUDA_CHECK(cudaMalloc(&p, bytes + (kBoundsChecked ? kGuardBytes : 0)));
+    if (kBoundsChecked) {
+        uint8_t* guard = static_cast<uint8_t*>(p) + bytes;
+        const cudaError_t e = cudaMemset(guard, kGuardPattern, kGuardBytes);
+        if (e != cudaSuccess) {
+            (void)cudaFree(p);
+            AEON_CUDA_CHECK(e);
+        }
+        if (ctx->guards == nullptr) ctx->guards = new std::vector<ScratchGuard>();
+        ctx->guards->push_back(ScratchGuard{p, guard, name});
+    }
+    return p;
+}
+
+void ctx_device_free(aeon_b200_ctx* ctx, void* base) noexcept {
+    if (base == nullptr) return;
+    if (ctx->guards != nullptr)
+        for (size_t i = 0; i < ctx->guards->size(); ++i)
+            if ((*ctx->guards)[i].base == base) {
+                ctx->guards->erase(ctx->guards->begin() + static_cast<std::ptrdiff_t>(i));
+                break;
+            }
+    (void)cudaFree(base);
+}
+
+namespace {
+
 void free_ctx_buffers(aeon_b200_ctx* c) {
     void* bufs[] = {c->d_xperm, c->d_logits, c->d_offsets, c->d_token_idx, c->d_draw_idx, c->d_wpos,
                     c->d_entries, c->d_counts, c->d_hidden_hi, c->d_hidden_lo, c->d_contrib,
                     c->d_error, c->d_sh_hi, c->d_sh_mid, c->d_sh_lo};
-    for (void* b : bufs)
-        if (b) (void)cudaFree(b);
+    for (void* b : bufs) ctx_device_free(c, b);
     free_prefill_scratch(c);
     free_shared_tc_scratch(c);
     if (c->timing_events) {
@@ -165,6 +193,8 @@ void free_ctx_buffers(aeon_b200_ctx* c) {
         delete c->timing_events;
         c->timing_events = nullptr;
     }
+    delete c->guards;
+    c->guards = nullptr;
 }
 
 }  // namespace
@@ -273,21 +303,21 @@ int aeon_b200_ctx_create(const aeon_b200_moe_config* cfg, int device, int max_to
             const size_t T = static_cast<size_t>(max_tokens);
             const size_t draws = T * cfg->top_k;
             uint64_t total = 0;
-            c->d_xperm = device_alloc<__half>(T * cfg->hidden, total);
-            c->d_logits = device_alloc<float>(T * cfg->experts, total);
-            c->d_offsets = device_alloc<int32_t>(cfg->experts + 1, total);
-            c->d_token_idx = device_alloc<int32_t>(draws, total);
-            c->d_draw_idx = device_alloc<int32_t>(draws, total);
-            c->d_wpos = device_alloc<float>(draws, total);
-            c->d_entries = device_alloc<WorkEntry>(cfg->experts + draws / 8 + 1, total);
-            c->d_counts = device_alloc<int32_t>(4, total);
-            c->d_hidden_hi = device_alloc<__half>(draws * cfg->intermediate, total);
-            c->d_hidden_lo = device_alloc<__half>(draws * cfg->intermediate, total);
-            c->d_contrib = device_alloc<float>(draws * cfg->hidden, total);
-            c->d_error = device_alloc<int32_t>(1, total);
-            c->d_sh_hi = device_alloc<__half>(T * cfg->intermediate, total);
-            c->d_sh_mid = device_alloc<__half>(T * cfg->intermediate, total);
-            c->d_sh_lo = device_alloc<__half>(T * cfg->intermediate, total);
+            c->d_xperm = device_alloc<__half>(c, T * cfg->hidden, total, "xperm");
+            c->d_logits = device_alloc<float>(c, T * cfg->experts, total, "logits");
+            c->d_offsets = device_alloc<int32_t>(c, cfg->experts + 1, total, "offsets");
+            c->d_token_idx = device_alloc<int32_t>(c, draws, total, "token_idx");
+            c->d_draw_idx = device_alloc<int32_t>(c, draws, total, "draw_idx");
+            c->d_wpos = device_alloc<float>(c, draws, total, "wpos");
+            c->d_entries = device_alloc<WorkEntry>(c, cfg->experts + draws / 8 + 1, total, "entries");
+            c->d_counts = device_alloc<int32_t>(c, 4, total, "counts");
+            c->d_hidden_hi = device_alloc<__half>(c, draws * cfg->intermediate, total, "hidden_hi");
+            c->d_hidden_lo = device_alloc<__half>(c, draws * cfg->intermediate, total, "hidden_lo");
+            c->d_contrib = device_alloc<float>(c, draws * cfg->hidden, total, "contrib");
+            c->d_error = device_alloc<int32_t>(c, 1, total, "error");
+            c->d_sh_hi = device_alloc<__half>(c, T * cfg->intermediate, total, "sh_hi");
+            c->d_sh_mid = device_alloc<__half>(c, T * cfg->intermediate, total, "sh_mid");
+            c->d_sh_lo = device_alloc<__half>(c, T * cfg->intermediate, total, "sh_lo");
             AEON_CUDA_CHECK(cudaMemset(c->d_error, 0, sizeof(int32_t)));
             AEON_CUDA_CHECK(cudaMemset(c->d_counts, 0, 4 * sizeof(int32_t)));
             c->scratch_bytes = total;
@@ -327,12 +357,36 @@ int aeon_b200_ctx_check(aeon_b200_ctx* ctx, void* stream) {
                 case kErrExpertAbsent:
                     throw StatusError(AEON_B200_ERR_LOGIC,
                                       "device: a routed expert has no pool slot (slot_of_expert < 0)");
+                case kErrBounds:
+                    throw StatusError(AEON_B200_ERR_OUT_OF_RANGE,
+                                      "device: an index left its buffer (bounds-checked build; the access was skipped)");
                 default:
-                    throw StatusError(AEON_B200_ERR_OUT_OF_RANGE, "device: expert id out of range");
+                    throw StatusError(AEON_B200_ERR_OUT_OF_RANGE,
+                                      "device: an expert id, a hash-table entry or a pool slot is out of range");
+            }
+        }
+        if (kBoundsChecked && ctx->guards != nullptr) {
+            uint8_t host[kGuardBytes];
+            for (const ScratchGuard& guard : *ctx->guards) {
+                AEON_CUDA_CHECK(cudaMemcpy(host, guard.guard, kGuardBytes, cudaMemcpyDeviceToHost));
+                for (size_t i = 0; i < kGuardBytes; ++i)
+                    if (host[i] != kGuardPattern)
+                        throw StatusError(AEON_B200_ERR_OUT_OF_RANGE,
+                                          std::string("device: the guard region behind scratch buffer '") + guard.name +
+                                              "' was overwritten at byte " + std::to_string(i));
             }
         }
     });
 }
+
+int aeon_b200_ctx_set_pool_slots(aeon_b200_ctx* ctx, int slots) {
+    return guarded([&] {
+        require(ctx != nullptr && slots >= 0, "aeon_b200_ctx_set_pool_slots: null context or negative slot count");
+        ctx->pool_slots = slots;
+    });
+}
+
+int aeon_b200_bounds_checked(void) { return kBoundsChecked ? 1 : 0; }
 
 int aeon_b200_ctx_set_timing(aeon_b200_ctx* ctx, int enabled) {
     return guarded([&] {

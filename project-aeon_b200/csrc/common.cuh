@@ -84,13 +84,44 @@ enum : int {
     kErrNone = 0,
     kErrWaitTimeout = 1,      // an mbarrier wait ran out of iterations
     kErrExpertAbsent = 2,     // slot_of_expert[e] < 0 for a routed expert
-    kErrIdOutOfRange = 3
+    kErrIdOutOfRange = 3,     // an expert id, a table entry or a pool slot outside its range
+    kErrBounds = 4            // bounds-checked build: an index left its buffer (the access was skipped)
 };
+
+// ---------------------------------------------------------------------------
+// Bounds-checked build: make EXTRA_NVCCFLAGS=-DAEON_B200_BOUNDS=1. Every index the kernels
+// derive from run-time data (gathers through token / draw / slot lists, stores into scratch and
+// output buffers) is checked against the extent of its buffer; a violation sets the context's
+// error flag and the access is skipped -- nothing traps, so the context stays usable and
+// aeon_b200_ctx_check reports AEON_B200_ERR_OUT_OF_RANGE. The context's scratch buffers also get
+// a guard region behind them whose pattern aeon_b200_ctx_check verifies. In the normal build
+// index_ok is the constant true and the guards are not allocated. This is the substitute for a
+// memory checker where none can be run.
+// ---------------------------------------------------------------------------
+#ifdef AEON_B200_BOUNDS
+constexpr bool kBoundsChecked = true;
+__device__ __forceinline__ bool index_ok(long long index, long long extent, int32_t* error) {
+    if (index >= 0 && index < extent) return true;
+    if (error != nullptr) atomicCAS(error, kErrNone, kErrBounds);
+    return false;
+}
+#else
+constexpr bool kBoundsChecked = false;
+__device__ __forceinline__ constexpr bool index_ok(long long, long long, int32_t*) { return true; }
+#endif
+constexpr size_t kGuardBytes = 256;
+constexpr uint8_t kGuardPattern = 0xC5;
 
 // One entry of the decode work list: the tokens [pos0, pos0+ntok) of the
 // expert-sorted draw order all belong to `expert`, whose payload is pool slot `slot`.
 struct WorkEntry {
     int expert, pos0, ntok, slot;
+};
+
+struct ScratchGuard {
+    const void* base;         // the buffer
+    const uint8_t* guard;     // kGuardBytes of kGuardPattern right behind it
+    const char* name;
 };
 
 }  // namespace aeon_b200
@@ -118,6 +149,9 @@ struct aeon_b200_ctx {
     float* d_contrib;       // [max_tokens * k, H]
     int32_t* d_error;       // device error flag
     // optional per-kernel timing (events recorded on the caller's stream)
+    int pool_slots;         // slots of the expert pool the calls will be given (0: not declared)
+    // bounds-checked build: guard regions behind the scratch buffers
+    std::vector<aeon_b200::ScratchGuard>* guards;
     int timing_enabled;
     std::vector<cudaEvent_t>* timing_events;   // triples: before A, between A and B, after B
     size_t timing_used;
@@ -161,6 +195,10 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
                         const float* topk_weights, int tokens, float* moe_accum, int64_t accum_stride,
                         uint32_t flags, cudaStream_t stream);
 void free_prefill_scratch(aeon_b200_ctx* ctx);
+// cudaMalloc of `bytes` for a context; the bounds-checked build appends a guard region, fills it
+// with the guard pattern and registers it under `name` for aeon_b200_ctx_check.
+void* ctx_device_alloc(aeon_b200_ctx* ctx, size_t bytes, const char* name);
+void ctx_device_free(aeon_b200_ctx* ctx, void* base) noexcept;
 void launch_ep_combine(float* out, int64_t out_stride, const float* partials, int ranks,
                        int tokens, int hidden, cudaStream_t stream);
 void launch_shared_expert(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,

@@ -76,6 +76,11 @@ struct DecodeParams {
     int64_t accum_stride;
     float limit;
     int32_t* error;
+    // extents of the buffers above, for the bounds-checked build
+    long long hidden_elems;    // hid_hi / hid_lo
+    long long contrib_elems;   // contrib
+    int draws_cap;             // rows of hid_* / contrib, entries of token_idx / draw_idx / wpos
+    int entries_cap;           // entries
 };
 
 template <int G>
@@ -138,8 +143,10 @@ __device__ __forceinline__ void load_chunk(ChunkRegs<G, kMats>& r, const uint8_t
 // in shared memory `row_stride` bytes apart (a second plane, the lo part of the hidden vector,
 // `plane_stride` bytes after the first when planes == 2). Output xs[(grp * planes + plane) * 8
 // + row] as fp32; rows >= valid_rows get 0. Warps take (plane, row, group) triples round
-// robin; every sum is a fixed lane pattern plus a butterfly, so it is reproducible.
-template <int G>
+// robin; every sum is a fixed lane pattern plus a butterfly, so it is reproducible. kHiScaled:
+// the columns that meet the high-nibble plane (bit 1 of the column index) are stored divided by
+// 16 (row-streaming kernels) and enter the sum multiplied back.
+template <int G, bool kHiScaled = false>
 __device__ __forceinline__ void group_sums(uint32_t act_smem, int row_stride, int plane_stride,
                                            int planes, int valid_rows, int groups, float* xs,
                                            int warp, int warps, int lane) {
@@ -155,7 +162,10 @@ __device__ __forceinline__ void group_sums(uint32_t act_smem, int row_stride, in
                 const uint2 q = ptx::lds64(at + lane * 8);
                 const __half2 a = *reinterpret_cast<const __half2*>(&q.x);
                 const __half2 b = *reinterpret_cast<const __half2*>(&q.y);
-                v = (__low2float(a) + __high2float(a)) + (__low2float(b) + __high2float(b));
+                // a lane's four positions are columns 0,1,2,3 or 4,5,6,7 modulo 8: the second pair is
+                // the scaled one either way
+                v = (__low2float(a) + __high2float(a)) +
+                    (kHiScaled ? 16.0f : 1.0f) * (__low2float(b) + __high2float(b));
             } else {
                 v = __half2float(__ushort_as_half(static_cast<unsigned short>(ptx::lds16(at + lane * 2))));
             }
@@ -207,7 +217,7 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
     const int g = lane >> 2;
     const int t = lane & 3;
 
-    const int entries = p.counts[0];
+    const int entries = index_ok(p.counts[0], p.entries_cap + 1, p.error) ? p.counts[0] : 0;
     const int placed = p.counts[2];
     const int tiles = p.I / 16;
     const int total_items = entries * tiles;
@@ -297,7 +307,9 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
                 if (lane == 0) ptx::mbar_arrive_expect_tx(act_bar, e.ntok * S::kHidden * 2);
                 __syncwarp();
                 if (lane < e.ntok) {
-                    const int token = token_idx[e.pos0 + lane];
+                    // a token index outside the batch is reported and row 0 copied in its place
+                    const int raw = index_ok(e.pos0 + lane, p.draws_cap, p.error) ? token_idx[e.pos0 + lane] : 0;
+                    const int token = index_ok(raw, p.tokens, p.error) ? raw : 0;
                     ptx::bulk_g2s(act_smem + lane * S::kActRow,
                                   p.xperm + static_cast<size_t>(token) * S::kHidden, S::kHidden * 2,
                                   act_bar, keep_policy);
@@ -413,8 +425,10 @@ moe_w13_swiglu_kernel(const DecodeParams p) {
                 const __half hi16 = __float2half_rn(hval);
                 const __half lo16 = __float2half_rn(hval - __half2float(hi16));
                 const size_t at = static_cast<size_t>(cur.pos0 + token) * p.I + perm_col<G>(cur_rt * 16 + row);
-                p.hid_hi[at] = hi16;
-                p.hid_lo[at] = lo16;
+                if (index_ok(static_cast<long long>(at), p.hidden_elems, p.error)) {
+                    p.hid_hi[at] = hi16;
+                    p.hid_lo[at] = lo16;
+                }
             }
         }
     }
@@ -469,7 +483,7 @@ moe_w2_contrib_kernel(const DecodeParams p) {
     const int g = lane >> 2;
     const int t = lane & 3;
 
-    const int entries = p.counts[0];
+    const int entries = index_ok(p.counts[0], p.entries_cap + 1, p.error) ? p.counts[0] : 0;
     const int placed = p.counts[2];
     const int tiles = p.H / S::kItemRows;
     const int total_items = entries * tiles;
@@ -581,8 +595,8 @@ moe_w2_contrib_kernel(const DecodeParams p) {
                     __syncwarp();
                     if (lane < 2 * e.ntok) {
                         const int tok = lane >> 1, part = lane & 1;
-                        const __half* src = (part == 0 ? p.hid_hi : p.hid_lo) +
-                                            static_cast<size_t>(e.pos0 + tok) * S::kInter;
+                        const int pos = index_ok(e.pos0 + tok, p.draws_cap, p.error) ? e.pos0 + tok : 0;
+                        const __half* src = (part == 0 ? p.hid_hi : p.hid_lo) + static_cast<size_t>(pos) * S::kInter;
                         ptx::bulk_g2s(act_smem + tok * S::kActRow + part * S::kInter * 2, src,
                                       S::kInter * 2, act_bar, keep_policy);
                     }
@@ -703,7 +717,11 @@ moe_w2_contrib_kernel(const DecodeParams p) {
                 const int row = ((rt * MW + wk) * MT + mt) * 16 + go + 8 * (c >> 1);
                 if (token < e.ntok) {
                     const int pos = e.pos0 + token;
-                    p.contrib[static_cast<size_t>(draw_idx[pos]) * p.H + row] = wpos[pos] * sum;
+                    if (index_ok(pos, p.draws_cap, p.error)) {
+                        const int draw = draw_idx[pos];
+                        if (index_ok(draw, p.draws_cap, p.error))
+                            p.contrib[static_cast<size_t>(draw) * p.H + row] = wpos[pos] * sum;
+                    }
                 }
             }
         }
@@ -781,7 +799,7 @@ moe_w13_rows_kernel(const DecodeParams p) {
     const int g = lane >> 2;
     const int t = lane & 3;
 
-    const int entries = p.counts[0];
+    const int entries = index_ok(p.counts[0], p.entries_cap + 1, p.error) ? p.counts[0] : 0;
     const int tiles = p.I / 16;                       // 16-row tiles per entry
     const int upe = (tiles + W - 1) / W;              // units per entry
     const int total_units = entries * upe;
@@ -864,7 +882,9 @@ moe_w13_rows_kernel(const DecodeParams p) {
                 if (lane == 0) ptx::mbar_arrive_expect_tx(act_bar, cur.e.ntok * S::kHidden * 2);
                 __syncwarp();
                 if (lane < cur.e.ntok) {
-                    const int token = __ldg(p.token_idx + cur.e.pos0 + lane);
+                    // a token index outside the batch is reported and row 0 copied in its place
+                    const int raw = index_ok(cur.e.pos0 + lane, p.draws_cap, p.error) ? __ldg(p.token_idx + cur.e.pos0 + lane) : 0;
+                    const int token = index_ok(raw, p.tokens, p.error) ? raw : 0;
                     ptx::bulk_g2s(act_smem + lane * S::kActRow,
                                   p.xperm + static_cast<size_t>(token) * S::kHidden, S::kHidden * 2,
                                   act_bar, keep_policy);
@@ -874,7 +894,7 @@ moe_w13_rows_kernel(const DecodeParams p) {
             ++act_phase;
             cur_entry = cur.m;
             __syncwarp();
-            group_sums<128>(act_smem, S::kActRow, 0, 1, cur.e.ntok, S::kGroups, xs, warp, W, lane);
+            group_sums<128, true>(act_smem, S::kActRow, 0, 1, cur.e.ntok, S::kGroups, xs, warp, W, lane);
             __syncthreads();
         }
 
@@ -899,20 +919,21 @@ moe_w13_rows_kernel(const DecodeParams p) {
                         uint4 bf[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) bf[i] = ptx::lds128(a_row + (c * 128 + i * 32 + t * 8) * 2);
-                        const float2 xsum = ptx::lds_f2(xs_smem + (c * kTokTile + 2 * t) * 4);
+                        float2 xs8 = ptx::lds_f2(xs_smem + (c * kTokTile + 2 * t) * 4);
+                        xs8.x *= -8.0f;
+                        xs8.y *= -8.0f;
 #pragma unroll
                         for (int mat = 0; mat < 2; ++mat) {
                             const uint32_t s0bits = ring[d].sc[mat][0], s1bits = ring[d].sc[mat][1];
-                            const float sca = half_bits_to_float(cc ? (s0bits >> 16) : (s0bits & 0xFFFFu));
-                            const float scb = half_bits_to_float(cc ? (s1bits >> 16) : (s1bits & 0xFFFFu));
+                            const float sca = cc ? ptx::half_hi_as_float(s0bits) : ptx::half_lo_as_float(s0bits);
+                            const float scb = cc ? ptx::half_hi_as_float(s1bits) : ptx::half_lo_as_float(s1bits);
                             const uint4 wa = ring[d].w[mat][0][cc], wb = ring[d].w[mat][1][cc];
-                            float tlo[4] = {0.f, 0.f, 0.f, 0.f};
-                            float thi[4] = {0.f, 0.f, 0.f, 0.f};
-                            ptx::mma_word(tlo, thi, wa.x, wb.x, bf[0]);
-                            ptx::mma_word(tlo, thi, wa.y, wb.y, bf[1]);
-                            ptx::mma_word(tlo, thi, wa.z, wb.z, bf[2]);
-                            ptx::mma_word(tlo, thi, wa.w, wb.w, bf[3]);
-                            ptx::fold_group(acc[mat], tlo, thi, sca, scb, xsum);
+                            float T[4];
+                            ptx::mma_planes<true>(T, ptx::word_planes(wa.x, wb.x), bf[0]);
+                            ptx::mma_planes<false>(T, ptx::word_planes(wa.y, wb.y), bf[1]);
+                            ptx::mma_planes<false>(T, ptx::word_planes(wa.z, wb.z), bf[2]);
+                            ptx::mma_planes<false>(T, ptx::word_planes(wa.w, wb.w), bf[3]);
+                            ptx::fold_single(acc[mat], T, sca, scb, xs8);
                         }
                     }
                     // the slot is free: this tile's step s + D, or the next tile's step d
@@ -929,11 +950,17 @@ moe_w13_rows_kernel(const DecodeParams p) {
                     const float gate = fminf(acc[0][j], p.limit);
                     const float up = fminf(fmaxf(acc[1][j], -p.limit), p.limit);
                     const float hval = (gate / (1.0f + expf(-gate))) * up;
-                    const __half hi16 = __float2half_rn(hval);
-                    const __half lo16 = __float2half_rn(hval - __half2float(hi16));
+                    __half hi16 = __float2half_rn(hval);
+                    __half lo16 = __float2half_rn(hval - __half2float(hi16));
+                    if (g & 2) {   // hidden columns that meet kernel B's high-nibble plane: stored / 16
+                        hi16 = __hmul(hi16, __float2half_rn(0.0625f));
+                        lo16 = __hmul(lo16, __float2half_rn(0.0625f));
+                    }
                     const size_t at = static_cast<size_t>(cur.e.pos0 + token) * p.I + perm_col<128>(cur.rt * 16 + row);
-                    p.hid_hi[at] = hi16;
-                    p.hid_lo[at] = lo16;
+                    if (index_ok(static_cast<long long>(at), p.hidden_elems, p.error)) {
+                        p.hid_hi[at] = hi16;
+                        p.hid_lo[at] = lo16;
+                    }
                 }
             }
         } else if (has_next && nxt.active) {
@@ -984,7 +1011,7 @@ moe_w2_rows_kernel(const DecodeParams p) {
     const int g = lane >> 2;
     const int t = lane & 3;
 
-    const int entries = p.counts[0];
+    const int entries = index_ok(p.counts[0], p.entries_cap + 1, p.error) ? p.counts[0] : 0;
     const int items = p.H / S::kItemRows;             // MT-tile items per entry
     const int upe = (items + W - 1) / W;
     const int total_units = entries * upe;
@@ -1043,6 +1070,8 @@ moe_w2_rows_kernel(const DecodeParams p) {
 
     int cur_entry = -1;
     uint32_t act_phase = 0;
+    int my_draw[2] = {0, 0};
+    float my_weight[2] = {0.f, 0.f};
     for (int u = lo; u < hi; ++u) {
         const bool has_next = u + 1 < hi;
         nxt = cur;
@@ -1057,8 +1086,8 @@ moe_w2_rows_kernel(const DecodeParams p) {
                 __syncwarp();
                 if (lane < 2 * cur.e.ntok) {
                     const int tok = lane >> 1, part = lane & 1;
-                    const __half* src = (part == 0 ? p.hid_hi : p.hid_lo) +
-                                        static_cast<size_t>(cur.e.pos0 + tok) * S::kInter;
+                    const int pos = index_ok(cur.e.pos0 + tok, p.draws_cap, p.error) ? cur.e.pos0 + tok : 0;
+                    const __half* src = (part == 0 ? p.hid_hi : p.hid_lo) + static_cast<size_t>(pos) * S::kInter;
                     ptx::bulk_g2s(act_smem + tok * S::kActRow + part * S::kInter * 2, src, S::kInter * 2,
                                   act_bar, keep_policy);
                 }
@@ -1067,8 +1096,18 @@ moe_w2_rows_kernel(const DecodeParams p) {
             ++act_phase;
             cur_entry = cur.m;
             __syncwarp();
-            group_sums<128>(act_smem, S::kActRow, S::kInter * 2, 2, cur.e.ntok, S::kGroups, xs, warp, W, lane);
+            group_sums<128, true>(act_smem, S::kActRow, S::kInter * 2, 2, cur.e.ntok, S::kGroups, xs, warp, W, lane);
             __syncthreads();
+            // the two tokens this lane stores for: draw rows and routing weights, once per entry
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int token = 2 * t + j;
+                const bool live = token < cur.e.ntok && index_ok(cur.e.pos0 + token, p.draws_cap, p.error);
+                my_draw[j] = live ? __ldg(p.draw_idx + cur.e.pos0 + token) : -1;
+                my_weight[j] = live ? __ldg(p.wpos + cur.e.pos0 + token) : 0.f;
+                // a draw index outside the scratch is reported; the lane then stores nothing for it
+                if (live && !index_ok(my_draw[j], p.draws_cap, p.error)) my_draw[j] = -1;
+            }
         }
 
         // Up to four tokens: hi and lo ride in one MMA as eight token columns (0-3 hi of tokens
@@ -1089,33 +1128,47 @@ moe_w2_rows_kernel(const DecodeParams p) {
 #pragma unroll
                 for (int d = 0; d < D; ++d) {
                     const int c = c0 + d;
-                    const int passes = packed ? 1 : 2;
-                    float sca[MT], scb[MT];
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        sca[mt] = half_bits_to_float(ring[d].sc[mt][0]);
-                        scb[mt] = half_bits_to_float(ring[d].sc[mt][1]);
+                    // Packed: one pass over eight columns (hi of tokens 0-3, lo of tokens 0-3). Otherwise
+                    // the hi and the lo part of the eight tokens are two passes that share the masked
+                    // weight planes and add into the same accumulator (same token columns).
+                    const uint32_t b_first = b_tok + (packed ? (g >> 2) : 0) * (S::kInter * 2) + (c * 128 + t * 8) * 2;
+                    const uint32_t xs_at = xs_smem + (c * 2 * kTokTile + (packed ? ((t >> 1) * kTokTile + 2 * (t & 1)) : 2 * t)) * 4;
+                    float2 xs8 = ptx::lds_f2(xs_at);
+                    if (!packed) {
+                        const float2 lo_sum = ptx::lds_f2(xs_at + kTokTile * 4);
+                        xs8.x += lo_sum.x;
+                        xs8.y += lo_sum.y;
                     }
-                    for (int part = 0; part < passes; ++part) {
-                        const int my_part = packed ? (g >> 2) : part;
-                        const uint32_t b_row = b_tok + my_part * (S::kInter * 2);
-                        const uint32_t xs_col = packed ? ((t >> 1) * kTokTile + 2 * (t & 1))
-                                                       : (part * kTokTile + 2 * t);
-                        uint4 bf[4];
+                    xs8.x *= -8.0f;
+                    xs8.y *= -8.0f;
+                    float T[MT][4], Tb[MT][4];     // the lo pass keeps its own chain: twice the MMAs in flight
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) bf[i] = ptx::lds128(b_row + (c * 128 + i * 32 + t * 8) * 2);
-                        const float2 xsum = ptx::lds_f2(xs_smem + (c * 2 * kTokTile + xs_col) * 4);
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 bf_a = ptx::lds128(b_first + i * 64);
+                        uint4 bf_b = make_uint4(0, 0, 0, 0);
+                        if (!packed) bf_b = ptx::lds128(b_first + S::kInter * 2 + i * 64);
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
                             const uint4 wa = ring[d].w[mt][0], wb = ring[d].w[mt][1];
-                            float tlo[4] = {0.f, 0.f, 0.f, 0.f};
-                            float thi[4] = {0.f, 0.f, 0.f, 0.f};
-                            ptx::mma_word(tlo, thi, wa.x, wb.x, bf[0]);
-                            ptx::mma_word(tlo, thi, wa.y, wb.y, bf[1]);
-                            ptx::mma_word(tlo, thi, wa.z, wb.z, bf[2]);
-                            ptx::mma_word(tlo, thi, wa.w, wb.w, bf[3]);
-                            ptx::fold_group(acc[mt], tlo, thi, sca[mt], scb[mt], xsum);
+                            const uint32_t wai = i == 0 ? wa.x : i == 1 ? wa.y : i == 2 ? wa.z : wa.w;
+                            const uint32_t wbi = i == 0 ? wb.x : i == 1 ? wb.y : i == 2 ? wb.z : wb.w;
+                            const ptx::WordPlanes planes = ptx::word_planes(wai, wbi);
+                            if (i == 0) ptx::mma_planes<true>(T[mt], planes, bf_a);
+                            else ptx::mma_planes<false>(T[mt], planes, bf_a);
+                            if (!packed) {
+                                if (i == 0) ptx::mma_planes<true>(Tb[mt], planes, bf_b);
+                                else ptx::mma_planes<false>(Tb[mt], planes, bf_b);
+                            }
                         }
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        if (!packed) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) T[mt][q] += Tb[mt][q];
+                        }
+                        ptx::fold_single(acc[mt], T[mt], half_bits_to_float(ring[d].sc[mt][0]),
+                                         half_bits_to_float(ring[d].sc[mt][1]), xs8);
                     }
                     if (!last) load_chunk_b(ring[d], cur, c + D);
                     else if (has_next && nxt.active) load_chunk_b(ring[d], nxt, d);
@@ -1130,10 +1183,8 @@ moe_w2_rows_kernel(const DecodeParams p) {
                     const int token = 2 * t + (j & 1);
                     const bool mine = packed ? (t < 2) : true;
                     const int row = (cur.it * MT + mt) * 16 + g + 8 * (j >> 1);
-                    if (mine && token < cur.e.ntok) {
-                        const int pos = cur.e.pos0 + token;
-                        p.contrib[static_cast<size_t>(__ldg(p.draw_idx + pos)) * p.H + row] = __ldg(p.wpos + pos) * v;
-                    }
+                    if (mine && token < cur.e.ntok && my_draw[j & 1] >= 0)
+                        p.contrib[static_cast<size_t>(my_draw[j & 1]) * p.H + row] = my_weight[j & 1] * v;
                 }
         } else if (has_next && nxt.active) {
 #pragma unroll
@@ -1152,7 +1203,7 @@ __global__ void moe_accumulate_kernel(float* __restrict__ accum, int64_t accum_s
                                       const float* __restrict__ contrib,
                                       const int32_t* __restrict__ ids,
                                       const int32_t* __restrict__ slot_of, int skip_absent,
-                                      int overwrite, int experts, int tokens, int top_k, int H) {
+                                      int overwrite, int experts, int tokens, int top_k, int H, int pool_slots) {
     const int vec_per_row = H / 4;
     const int64_t total = static_cast<int64_t>(tokens) * vec_per_row;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -1164,7 +1215,9 @@ __global__ void moe_accumulate_kernel(float* __restrict__ accum, int64_t accum_s
         for (int slot = 0; slot < top_k; ++slot) {
             const int draw = token * top_k + slot;
             const int id = ids[draw];
-            if (id >= 0 && id < experts && !(skip_absent && slot_of[id] < 0)) {
+            // absent: no slot, or a slot beyond the declared pool (reported by the work-list kernel)
+            if (id >= 0 && id < experts &&
+                !(skip_absent && (slot_of[id] < 0 || (pool_slots > 0 && slot_of[id] >= pool_slots)))) {
                 const float4 c = reinterpret_cast<const float4*>(contrib + static_cast<size_t>(draw) * H)[v];
                 a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
             }
@@ -1176,7 +1229,8 @@ __global__ void moe_accumulate_kernel(float* __restrict__ accum, int64_t accum_s
 // ----- activation staging: 16-bit -> fp16 in the kernels' column order -------------------
 template <int G>
 __global__ void stage_activations_kernel(const void* __restrict__ x, int64_t x_stride, int dtype,
-                                         int tokens, int H, __half* __restrict__ out) {
+                                         int tokens, int H, __half* __restrict__ out, long long out_elems,
+                                         int32_t* __restrict__ error) {
     const int64_t total = static_cast<int64_t>(tokens) * H;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -1188,7 +1242,11 @@ __global__ void stage_activations_kernel(const void* __restrict__ x, int64_t x_s
         } else {
             v = __half2float(reinterpret_cast<const __half*>(x)[token * x_stride + k]);
         }
-        out[static_cast<size_t>(token) * H + perm_col<G>(k)] = __float2half_rn(v);
+        __half h = __float2half_rn(v);
+        // group 128 (row-streaming kernels): columns that meet the high-nibble plane are stored / 16
+        if (G == 128 && (k & 2)) h = __hmul(h, __float2half_rn(0.0625f));
+        const size_t at = static_cast<size_t>(token) * H + perm_col<G>(k);
+        if (index_ok(static_cast<long long>(at), out_elems, error)) out[at] = h;
     }
 }
 
@@ -1221,7 +1279,7 @@ void launch_pair(aeon_b200_ctx* ctx, const DecodeParams& p, KernelA ka, int thre
         const int blocks = static_cast<int>(std::min<int64_t>((vecs + 255) / 256, 4 * ctx->sm_count));
         moe_accumulate_kernel<<<blocks, 256, 0, stream>>>(p.accum, p.accum_stride, p.contrib, p.topk_ids,
                                                           p.slot_of, p.skip_absent, p.overwrite, p.experts,
-                                                          p.tokens, p.top_k, p.H);
+                                                          p.tokens, p.top_k, p.H, ctx->pool_slots);
         AEON_CUDA_CHECK(cudaGetLastError());
         ctx->launches += 1;
     }
@@ -1290,7 +1348,7 @@ void launch_moe_accumulate(aeon_b200_ctx* ctx, const int32_t* slot_of_expert, co
     moe_accumulate_kernel<<<blocks, 256, 0, stream>>>(
         moe_accum, accum_stride, ctx->d_contrib, topk_ids, slot_of_expert,
         (flags & AEON_B200_DECODE_SKIP_ABSENT) ? 1 : 0, (flags & AEON_B200_DECODE_OVERWRITE) ? 1 : 0,
-        cfg.experts, tokens, cfg.top_k, cfg.hidden);
+        cfg.experts, tokens, cfg.top_k, cfg.hidden, ctx->pool_slots);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 1;
 }
@@ -1314,11 +1372,13 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     const int64_t total = static_cast<int64_t>(tokens) * cfg.hidden;
     const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 4 * ctx->sm_count));
     if (cfg.group_size == 128) {
-        stage_activations_kernel<128><<<blocks, 256, 0, stream>>>(x, x_stride, cfg.act_dtype, tokens,
-                                                                  cfg.hidden, ctx->d_xperm);
+        stage_activations_kernel<128><<<blocks, 256, 0, stream>>>(
+            x, x_stride, cfg.act_dtype, tokens, cfg.hidden, ctx->d_xperm,
+            static_cast<long long>(ctx->max_tokens) * cfg.hidden, ctx->d_error);
     } else {
-        stage_activations_kernel<32><<<blocks, 256, 0, stream>>>(x, x_stride, cfg.act_dtype, tokens,
-                                                                 cfg.hidden, ctx->d_xperm);
+        stage_activations_kernel<32><<<blocks, 256, 0, stream>>>(
+            x, x_stride, cfg.act_dtype, tokens, cfg.hidden, ctx->d_xperm,
+            static_cast<long long>(ctx->max_tokens) * cfg.hidden, ctx->d_error);
     }
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 1;
@@ -1358,6 +1418,10 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     p.accum_stride = accum_stride;
     p.limit = cfg.swiglu_limit;
     p.error = ctx->d_error;
+    p.draws_cap = ctx->max_tokens * cfg.top_k;
+    p.hidden_elems = static_cast<long long>(p.draws_cap) * cfg.intermediate;
+    p.contrib_elems = static_cast<long long>(p.draws_cap) * cfg.hidden;
+    p.entries_cap = cfg.experts + p.draws_cap / 8 + 1;
 
     // Kernel instances: K-warps x chunks-per-warp x 128 columns = hidden.
 #ifdef AEON_B200_TUNING
@@ -1365,17 +1429,14 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     static const int tune_a = getenv("AEON_B200_TUNE_A") ? atoi(getenv("AEON_B200_TUNE_A")) : 0;
     static const int tune_b = getenv("AEON_B200_TUNE_B") ? atoi(getenv("AEON_B200_TUNE_B")) : 0;
     if (cfg.group_size == 128 && cfg.hidden == 7168 && cfg.intermediate == 2048 && (tune_a || tune_b)) {
-        auto ka = moe_w13_swiglu_kernel<128, 14, 4>;
-        int ta = GeomA<128, 14, 4>::kThreads, sa = GeomA<128, 14, 4>::kSmem;
-        auto kb = moe_w2_contrib_kernel<128, 2, 2, 8, 2, 1>;
-        int tb = GeomB<128, 2, 2, 8, 2, 1>::kThreads, sb = GeomB<128, 2, 2, 8, 2, 1>::kSmem;
+        auto ka = moe_w13_rows_kernel<8, 4, 28>;
+        int ta = GeomRowsA<8, 4, 28>::kThreads, sa = GeomRowsA<8, 4, 28>::kSmem;
+        auto kb = moe_w2_rows_kernel<16, 2, 2, 16>;
+        int tb = GeomRowsB<16, 2, 2, 16>::kThreads, sb = GeomRowsB<16, 2, 2, 16>::kSmem;
 #define PICK_A(K, ...) { ka = K; using GG = __VA_ARGS__; ta = GG::kThreads; sa = GG::kSmem; }
 #define PICK_B(K, ...) { kb = K; using GG = __VA_ARGS__; tb = GG::kThreads; sb = GG::kSmem; }
         switch (tune_a) {
             case 0: break;
-            case 1: PICK_A((moe_w13_swiglu_kernel<128, 8, 7>), GeomA<128, 8, 7>); break;
-            case 2: PICK_A((moe_w13_swiglu_kernel<128, 7, 8>), GeomA<128, 7, 8>); break;
-            case 3: PICK_A((moe_w13_swiglu_kernel<128, 28, 2>), GeomA<128, 28, 2>); break;
             case 5: PICK_A((moe_w13_rows_kernel<16, 2, 28>), GeomRowsA<16, 2, 28>); break;
             case 6: PICK_A((moe_w13_rows_kernel<12, 2, 28>), GeomRowsA<12, 2, 28>); break;
             case 7: PICK_A((moe_w13_rows_kernel<8, 4, 28>), GeomRowsA<8, 4, 28>); break;
@@ -1385,15 +1446,13 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
         }
         switch (tune_b) {
             case 0: break;
-            case 1: PICK_B((moe_w2_contrib_kernel<128, 2, 2, 4, 4, 2>), GeomB<128, 2, 2, 4, 4, 2>); break;
-            case 2: PICK_B((moe_w2_contrib_kernel<128, 2, 2, 4, 4, 1>), GeomB<128, 2, 2, 4, 4, 1>); break;
-            case 3: PICK_B((moe_w2_contrib_kernel<128, 2, 1, 8, 2, 2>), GeomB<128, 2, 1, 8, 2, 2>); break;
-            case 4: PICK_B((moe_w2_contrib_kernel<128, 4, 1, 4, 4, 1>), GeomB<128, 4, 1, 4, 4, 1>); break;
-            case 5: PICK_B((moe_w2_rows_kernel<16, 2, 2, 16>), GeomRowsB<16, 2, 2, 16>); break;
-            case 6: PICK_B((moe_w2_rows_kernel<12, 2, 4, 16>), GeomRowsB<12, 2, 4, 16>); break;
-            case 7: PICK_B((moe_w2_rows_kernel<12, 2, 2, 16>), GeomRowsB<12, 2, 2, 16>); break;
-            case 8: PICK_B((moe_w2_rows_kernel<16, 1, 4, 16>), GeomRowsB<16, 1, 4, 16>); break;
-            case 9: PICK_B((moe_w2_rows_kernel<8, 2, 4, 16>), GeomRowsB<8, 2, 4, 16>); break;
+            case 1: PICK_B((moe_w2_rows_kernel<16, 1, 4, 16>), GeomRowsB<16, 1, 4, 16>); break;
+            case 2: PICK_B((moe_w2_rows_kernel<12, 2, 2, 16>), GeomRowsB<12, 2, 2, 16>); break;
+            case 3: PICK_B((moe_w2_rows_kernel<12, 2, 4, 16>), GeomRowsB<12, 2, 4, 16>); break;
+            case 4: PICK_B((moe_w2_rows_kernel<12, 1, 4, 16>), GeomRowsB<12, 1, 4, 16>); break;
+            case 5: PICK_B((moe_w2_rows_kernel<16, 1, 2, 16>), GeomRowsB<16, 1, 2, 16>); break;
+            case 6: PICK_B((moe_w2_rows_kernel<8, 2, 4, 16>), GeomRowsB<8, 2, 4, 16>); break;
+            case 7: PICK_B((moe_w2_rows_kernel<8, 2, 8, 16>), GeomRowsB<8, 2, 8, 16>); break;
             default: throw StatusError(AEON_B200_ERR_UNSUPPORTED, "unknown tuning selection B");
         }
 #undef PICK_A
@@ -1402,10 +1461,22 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
         return;
     }
 #endif
-    if (cfg.group_size == 128 && cfg.hidden == 7168) {
-        launch_decode_kernels<128, 14, 4>(ctx, p, stream);
-    } else if (cfg.group_size == 128 && cfg.hidden == 4096) {
-        launch_decode_kernels<128, 16, 2>(ctx, p, stream);
+    // Group 128: the row-streaming kernels. Kernel A: eight warps (two per scheduler, no register
+    // cap in the way) with a four-step ring, 128 KB of weights in flight per SM; kernel B: sixteen
+    // warps of two tiles each with a two-chunk ring. Both chosen by timing the alternatives on
+    // B200 (8/12/16 warps x ring depths 1..8), alone and beside the shared expert's kernels. Group
+    // 32 (the reference model's own shape) keeps the K-split kernels.
+    if (cfg.group_size == 128 && cfg.intermediate == 2048 && (cfg.hidden == 7168 || cfg.hidden == 4096)) {
+        using SB = GeomRowsB<16, 2, 2, 16>;
+        if (cfg.hidden == 7168) {
+            using SA = GeomRowsA<8, 4, 28>;
+            launch_pair(ctx, p, moe_w13_rows_kernel<8, 4, 28>, SA::kThreads, SA::kSmem,
+                        moe_w2_rows_kernel<16, 2, 2, 16>, SB::kThreads, SB::kSmem, 1, stream);
+        } else {
+            using SA = GeomRowsA<8, 4, 16>;
+            launch_pair(ctx, p, moe_w13_rows_kernel<8, 4, 16>, SA::kThreads, SA::kSmem,
+                        moe_w2_rows_kernel<16, 2, 2, 16>, SB::kThreads, SB::kSmem, 1, stream);
+        }
     } else if (cfg.group_size == 32 && cfg.hidden == 4096) {
         launch_decode_kernels<32, 16, 2>(ctx, p, stream);
     } else if (cfg.group_size == 32 && cfg.hidden == 7168) {

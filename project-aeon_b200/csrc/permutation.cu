@@ -51,7 +51,8 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
                           int32_t* __restrict__ token_idx, int32_t* __restrict__ draw_idx,
                           const float* __restrict__ weights, float* __restrict__ wpos,
                           const int32_t* __restrict__ slot_of, WorkEntry* __restrict__ entries,
-                          int32_t* __restrict__ counts, int skip_absent) {
+                          int32_t* __restrict__ counts, int skip_absent, int pool_slots, int entries_cap,
+                          int32_t* __restrict__ error) {
     extern __shared__ int hist[];   // [walk_warps][experts]
     __shared__ int warp_sums[32];
     __shared__ int scan_total;
@@ -109,9 +110,11 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
             const unsigned peers = __match_any_sync(0xFFFFFFFFu, key);
             if (valid) {
                 const int pos = hist[warp * experts + e] + __popc(peers & lt_mask);
-                token_idx[pos] = d / slots;
-                draw_idx[pos] = d;
-                if (weights != nullptr) wpos[pos] = weights[d];
+                if (index_ok(pos, draws, error)) {
+                    token_idx[pos] = d / slots;
+                    draw_idx[pos] = d;
+                    if (weights != nullptr) wpos[pos] = weights[d];
+                }
             }
             __syncwarp();
             if (valid && (peers & lt_mask) == 0) hist[warp * experts + e] += __popc(peers);
@@ -121,7 +124,13 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
 
     // Decode work list: one entry per (expert, group of up to 8 of its positions).
     if (entries != nullptr) {
-        const int my_slot = (tid < experts) ? (slot_of != nullptr ? slot_of[tid] : tid) : -1;
+        int my_slot = (tid < experts) ? (slot_of != nullptr ? slot_of[tid] : tid) : -1;
+        // a slot at or above the declared pool size is reported and its expert treated as absent:
+        // it must never become an address
+        if (pool_slots > 0 && my_slot >= pool_slots) {
+            if (error != nullptr) atomicCAS(error, kErrNone, kErrIdOutOfRange);
+            my_slot = -1;
+        }
         // An expert without a pool slot gets no entry when absent experts are skipped
         // (expert-parallel slice); otherwise it keeps its entries and the kernels flag it.
         const bool listed = tid < experts && !(skip_absent && my_slot < 0);
@@ -139,7 +148,7 @@ expert_permutation_kernel(const int32_t* __restrict__ ids, int draws, int slots,
                 w.pos0 = offset + 8 * c;
                 w.ntok = min(8, total - 8 * c);
                 w.slot = slot;
-                entries[ebase + c] = w;
+                if (index_ok(ebase + c, entries_cap, error)) entries[ebase + c] = w;
             }
         }
         if (tid == 0) {
@@ -157,6 +166,8 @@ void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens,
                         int32_t* draw_indices, const float* weights, float* weights_by_position,
                         const int32_t* slot_of_expert, WorkEntry* entries, int32_t* counts,
                         bool skip_absent, cudaStream_t stream) {
+    // the work list holds at most one entry per expert plus one per eight draws (rounded up per expert)
+    const int entries_cap = experts + tokens * slots / 8 + 1;
     require(tokens >= 0 && slots > 0, "aeon_b200_expert_permutation: bad token or slot count");
     // An empty chunk is legal (the reference's permutation gate runs T = 0): only the
     // offsets are written then, so the per-draw arrays may be absent.
@@ -173,7 +184,8 @@ void launch_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, int tokens,
     const size_t smem = static_cast<size_t>(walk_warps) * experts * sizeof(int);
     expert_permutation_kernel<<<1, kPermThreads, smem, stream>>>(
         topk_ids, draws, slots, experts, walk_warps, expert_offsets, token_indices, draw_indices,
-        weights, weights_by_position, slot_of_expert, entries, counts, skip_absent ? 1 : 0);
+        weights, weights_by_position, slot_of_expert, entries, counts, skip_absent ? 1 : 0, ctx->pool_slots,
+        entries_cap, ctx->d_error);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 1;
 }

@@ -9,22 +9,32 @@
 // the offsets; here the tile list is built on the device and one persistent launch per GEMM
 // walks it, so there is no host round trip and no per-launch expert limit.
 //
-// Shape of one tile. The weight rows are the MMA M dimension (128 per tile, always full),
-// the expert's tokens the N dimension (16..256, so ragged token counts cost little), K runs in
-// blocks of 64:
-//     D[128 weight rows, N tokens] += Wq[128, 64] * X[N, 64]^T        (tcgen05.mma kind::f16)
-// with the fp32 accumulator in tensor memory (two buffers of 256 columns, so the epilogue of
-// one tile overlaps the main loop of the next).
+// Shape of one tile. The weight rows are the MMA M dimension, the expert's tokens the N
+// dimension (16..128, so ragged token counts cost little), K runs in blocks of 64. A CTA tile is
+// 256 weight rows: two 128-row MMAs per k-step that share one activation tile in shared memory,
+//     D_h[128 weight rows, N tokens] += Wq_h[128, 64] * X[N, 64]^T   h = 0, 1   (tcgen05.mma kind::f16)
+// so every activation byte that comes up from L2 feeds 256 weight rows. (With 128-row CTA tiles
+// each k-block pulled 16 KB of activations for 1 M MACs and the kernel sat at the L2-to-SM
+// bandwidth and TMA latency of that stream, not at the tensor pipe: doubling the dequantising
+// warps changed nothing.) The fp32 accumulators live in tensor memory: two buffers of two
+// 128-column halves, so the epilogue of one tile overlaps the main loop of the next.
 //
 // Warp roles of a CTA (448 threads):
-//   warps 0-3  epilogue: tcgen05.ld their TMEM lane quadrant, finish (SwiGLU / routing weight),
-//              store;
-//   warps 4-11 dequantise: two threads per weight row of the tile; a thread loads its packed
-//              int4 atom with a 128-bit load (four k-blocks ahead), converts it to
-//              fp16(q * scale) in registers and writes its half of the row into the
-//              128-byte-swizzled K-major operand tile in shared memory;
-//   warp 12    one thread issues the tiled TMA loads of the activation operand (no multicast);
-//   warp 13    one thread issues the MMAs and the commits; the warp owns the TMEM allocation.
+//   warps 0-3   epilogue: tcgen05.ld their TMEM lane quadrant of both halves, finish (SwiGLU /
+//               routing weight), store;
+//   warps 4-11  dequantise: one thread per weight row of the 256-row tile. Per k-block a thread
+//               loads its row's two packed atoms (32 bytes, four k-blocks ahead) and the scale,
+//               converts the 64 int4 values to fp16(q * scale) in registers and writes the row's
+//               128 bytes into the 128-byte-swizzled K-major operand tile in shared memory. The
+//               loop is unrolled over the ring so stage indices, parities' positions and every
+//               address offset are compile-time constants: profiling the first form (two
+//               threads per row, run-time stage arithmetic) showed the kernel bound by issued
+//               instructions -- 3,000 warp instructions per k-block, of which the conversion
+//               itself needs about 900 -- not by the tensor pipe, HBM, L2 or shared memory
+//               (leaving out the stores, the conversion arithmetic, the activation loads or
+//               even the MMAs each changed the time by less than 15 %);
+//   warp 12     one thread issues the tiled TMA loads of the activation operand (no multicast);
+//   warp 13     one thread issues the MMAs and the commits; the warp owns the TMEM allocation.
 // A 4-stage ring of (weight tile, activation tile) pairs connects them through mbarriers.
 // Every wait is bounded; a wait that runs out sets the context's error flag, after which all
 // waits fall through and the kernel ends (TMEM is always freed).
@@ -35,29 +45,35 @@
 // same three roundings (the method of the reference's own grouped gate,
 // tests/test_v4_grouped_wmma_oracle.cpp:63-73,219-228).
 //
-// GEMM 1 tiles interleave W1 and W3: tile row r is row (rb*64 + (r/32)*16 + r%16) of W1 when
-// (r/16) is even and of W3 when odd, so a gate value and its up value sit 16 lanes apart in one
-// warp of the epilogue and meet through one shuffle.
+// GEMM 1 puts W1 in the first 128-row half of a CTA tile and the same rows of W3 in the second:
+// the gate and the up value of a hidden element sit in the same TMEM lane of the two accumulator
+// halves, so one epilogue thread reads both and no lane is idle or shuffling.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tc5.cuh"
 #include "tensor_map.cuh"
 
 #include <algorithm>
+#include <cstdlib>
+#include <type_traits>
 
 namespace aeon_b200 {
 
 namespace {
 
-constexpr int kTileM = 128;         // weight rows per tile
+constexpr int kHalfM = 128;         // weight rows per MMA (the TMEM lanes)
+constexpr int kHalves = 2;          // MMAs per k-step that share the activation tile
+constexpr int kTileM = kHalfM * kHalves;   // weight rows per CTA tile
 constexpr int kTileK = 64;          // K per pipeline stage (one 128-byte swizzled row)
-constexpr int kMaxN = 256;          // tokens per tile
+constexpr int kMaxN = 128;          // tokens per tile
 constexpr int kStages = 4;
-constexpr int kEpilogueWarps = 4, kDequantWarps = 8;
+constexpr int kEpilogueWarps = 4;
+constexpr int kDequantWarps = kTileM / 32;            // one thread per weight row of the tile
 constexpr int kPrefetch = 4;         // k-blocks of packed weights a dequantising thread keeps in flight
 constexpr int kThreads = (kEpilogueWarps + kDequantWarps + 2) * 32;
-constexpr int kStageA = kTileM * kTileK * 2;          // 16 KB
-constexpr int kStageB = kMaxN * kTileK * 2;           // 32 KB
+constexpr int kHalfA = kHalfM * kTileK * 2;           // 16 KB: one half's operand tile
+constexpr int kStageA = kHalves * kHalfA;             // 32 KB
+constexpr int kStageB = kMaxN * kTileK * 2;           // 16 KB
 constexpr int kSmemBytes = 1024 /*align*/ + kStages * (kStageA + kStageB) + 256 /*barriers*/;
 constexpr int kTmemCols = 512;
 
@@ -82,6 +98,10 @@ struct PrefillParams {
     float* contrib;       // [draws, H] fp32
     float limit;
     int32_t* error;
+    int tune;             // development builds: how the dequantising warps wait for a free stage
+    // extents for the bounds-checked build
+    int draws_cap;        // rows of hidden / contrib, entries of draw_idx / wpos
+    int tiles_cap;        // tiles
 };
 
 __device__ __forceinline__ void flag_error(int32_t* error, int code) { atomicCAS(error, kErrNone, code); }
@@ -151,9 +171,9 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     const uint32_t tmem_base = *tmem_slot_gen;
 
     const int K = kGateUp ? p.H : p.I;
-    const int row_blocks = kGateUp ? (2 * p.I) / kTileM : p.H / kTileM;
+    const int row_blocks = kGateUp ? p.I / kHalfM : p.H / kTileM;
     const int kblocks = K / kTileK;
-    const int n_tiles = *p.n_tiles;
+    const int n_tiles = index_ok(*p.n_tiles, p.tiles_cap + 1, p.error) ? *p.n_tiles : 0;
     const int total_items = n_tiles * row_blocks;
 
     if (warp == kEpilogueWarps + kDequantWarps) {
@@ -181,12 +201,12 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
                 const PrefillTile tile = p.tiles[item / row_blocks];
                 const uint32_t n_mma = static_cast<uint32_t>((tile.ntok + 15) & ~15);
-                const uint32_t idesc = tc5::idesc_f16(kTileM, n_mma);
+                const uint32_t idesc = tc5::idesc_f16(kHalfM, n_mma);
                 const uint32_t buf = it & 1;
                 if (!ptx::mbar_wait(acc_empty + 8 * buf, ((it >> 1) & 1) ^ 1, p.error))
                     flag_error(p.error, kErrWaitTimeout);
                 tc5::fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * kMaxN;
+                const uint32_t d_tmem = tmem_base + buf * (kHalves * kMaxN);
                 for (int kb = 0; kb < kblocks; ++kb, ++n) {
                     const int s = n % kStages;
                     const uint32_t parity = (n / kStages) & 1;
@@ -195,11 +215,13 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
                     const uint32_t a_addr = a_smem + s * kStageA;
                     const uint32_t b_addr = b_smem + s * kStageB;
 #pragma unroll
-                    for (int kk = 0; kk < kTileK / 16; ++kk) {
-                        tc5::mma_f16_ss(d_tmem, tc5::smem_desc_sw128(a_addr + kk * 32),
-                                        tc5::smem_desc_sw128(b_addr + kk * 32), idesc,
-                                        (kb > 0 || kk > 0) ? 1u : 0u);
-                    }
+                    for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+                        for (int kk = 0; kk < kTileK / 16; ++kk) {
+                            tc5::mma_f16_ss(d_tmem + h * kMaxN, tc5::smem_desc_sw128(a_addr + h * kHalfA + kk * 32),
+                                            tc5::smem_desc_sw128(b_addr + kk * 32), idesc,
+                                            (kb > 0 || kk > 0) ? 1u : 0u);
+                        }
                     tc5::commit(empty_bar + 8 * s);      // stage free when these MMAs are done
                 }
                 tc5::commit(acc_full + 8 * buf);         // accumulator complete
@@ -207,83 +229,109 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         }
     } else if (warp >= kEpilogueWarps) {
         // ------------------------------ dequantise the weight operand ------------------------
-        // Two threads per tile row: thread (r, half) converts atom `half` (32 columns) of the
-        // k-block. Packed words and scales are loaded kPrefetch k-blocks ahead, so the global
-        // latency is off the critical path of the ring.
+        // Thread (mh, r) owns row r of 128-row half mh for the whole item. Round j covers the four
+        // k-blocks 4j .. 4j+3, which are exactly the four ring stages in order (an item starts on a
+        // multiple of four k-blocks), so inside the unrolled round the stage, the shared-memory
+        // address and the load offsets are constants and only the phase bit changes per round.
         const int d = tid - kEpilogueWarps * 32;
-        const int r = d >> 1;                             // tile row, 0..127
-        const int half = d & 1;
-        const uint32_t row_smem = (r >> 3) * 1024 + (r & 7) * 128;
-        uint32_t n = 0;
+        const int mh = d / kHalfM;
+        const int r = d - mh * kHalfM;
+        // chunk c (16 bytes, 8 columns) of the row goes to position c ^ (r & 7) of its 128-byte line
+        uint8_t* const row_dst = smem_gen + mh * kHalfA + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint32_t swz = static_cast<uint32_t>(r & 7) << 4;
+        // The swizzle configuration is fixed per matrix kind (validated with the config):
+        // W1/W3 rows come 4 to a 512-byte line with 8 atoms each, W2 rows 8 with 4 atoms.
+        constexpr int RPW = kGateUp ? 4 : 8, LPR = kGateUp ? 8 : 4;
+        constexpr int apg = G / 32;                    // atoms per scale group
+        constexpr int kScaleLineBytes = 32 / apg * 2;  // scale bytes per 512-byte line
+        constexpr int kRoundBytes = (8 / LPR) * 512;   // packed bytes a row advances per round (8 atoms)
+        constexpr int kRoundScaleBytes = (8 / LPR) * kScaleLineBytes;
+        uint32_t phase = 0;                            // parity of the ring pass the next round fills
         for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
             const int ti = item / row_blocks;
             const int rb = item - ti * row_blocks;
             const PrefillTile tile = p.tiles[ti];
             const uint8_t* payload = p.pool + static_cast<uint64_t>(tile.slot < 0 ? 0 : tile.slot) * p.payload_bytes;
-            // which matrix and which row of it this thread feeds
             const MatrixGeom* gm;
             int row;
             if constexpr (kGateUp) {
-                gm = ((r >> 4) & 1) ? &p.w3 : &p.w1;
-                row = rb * 64 + (r >> 5) * 16 + (r & 15);
+                gm = mh ? &p.w3 : &p.w1;               // first half: gate rows, second half: up rows
+                row = rb * kHalfM + r;
             } else {
                 gm = &p.w2;
-                row = rb * kTileM + r;
+                row = rb * kTileM + mh * kHalfM + r;
             }
-            // The swizzle configuration is fixed per matrix kind (validated with the config):
-            // W1/W3 rows come 4 to a 512-byte line with 8 atoms each, W2 rows 8 with 4 atoms.
-            constexpr int RPW = kGateUp ? 4 : 8, LPR = kGateUp ? 8 : 4;
-            constexpr int apg = G / 32;                    // atoms per scale group
-            constexpr int kScaleIterBytes = 32 / apg * 2;  // scale bytes per 512-byte line
             const int blk = row / RPW, rib = row - blk * RPW;
-            // atom a of the row (32 columns each): line a / LPR, position rib * LPR + a % LPR
+            // atom a of the row (32 columns): line a / LPR, position rib * LPR + a % LPR; k-block kb is
+            // the atom pair (2 kb, 2 kb + 1), adjacent in its line
             const uint8_t* packed = payload + gm->packed_offset + static_cast<size_t>(blk) * gm->block_bytes +
-                                    (rib * LPR + half) * 16;
-            const uint16_t* scales = reinterpret_cast<const uint16_t*>(
-                payload + gm->scale_offset + static_cast<size_t>(blk) * gm->block_scale_bytes +
-                rib * (LPR / apg) * 2);
-            // k-block kb0 + i uses atom 2*(kb0+i) + half; with kb0 a multiple of 4 every offset
-            // below is a compile-time constant plus a base that moves 8 atoms per round
-            auto fetch = [&](int kb0, int i, uint4& q, uint32_t& s2) {
-                const int line0 = (kb0 * 2) / LPR;                 // first line of this round
-                constexpr int kLinesPerRound = 8 / LPR;            // 1 (W1/W3) or 2 (W2)
-                (void)kLinesPerRound;
-                const int a = i * 2;                               // atom within the round (even part)
-                const int line = line0 + a / LPR;
-                const int sl = a % LPR;                            // + half, folded into `packed`
-                q = ldg128(packed + static_cast<size_t>(line) * 512 + sl * 16);
-                // raw load only: any arithmetic on the value here would wait for it
-                s2 = __ldg(scales + line * (kScaleIterBytes / 2) + (sl + half) / apg);
+                                    (rib * LPR) * 16;
+            const uint8_t* scales = payload + gm->scale_offset + static_cast<size_t>(blk) * gm->block_scale_bytes +
+                                    rib * (LPR / apg) * 2;
+            // k-block i of a round: its 32 packed bytes and its scale(s), as offsets from the round's base
+            auto fetch = [&](const uint8_t* pk, const uint8_t* sc, int i, uint4& q0, uint4& q1, uint32_t& s2) {
+                const int a = 2 * i;                                   // first atom of the k-block within the round
+                const int off = (a / LPR) * 512 + (a % LPR) * 16;
+                q0 = ldg128(pk + off);
+                q1 = ldg128(pk + off + 16);
+                // raw loads only: any arithmetic on the values here would wait for them
+                const int soff = (a / LPR) * kScaleLineBytes + ((a % LPR) / apg) * 2;
+                if constexpr (apg == 1) s2 = __ldg(reinterpret_cast<const uint32_t*>(sc + soff));      // two atoms, two scales
+                else s2 = __ldg(reinterpret_cast<const uint16_t*>(sc + soff));                         // one scale for both
             };
-            uint4 qbuf[kPrefetch];
-            uint32_t sbuf[kPrefetch];
+            uint4 qa[kStages], qb[kStages];
+            uint32_t sbuf[kStages];
 #pragma unroll
-            for (int i = 0; i < kPrefetch; ++i) fetch(0, i, qbuf[i], sbuf[i]);
-            uint32_t dst_off[4];
+            for (int i = 0; i < kStages; ++i) fetch(packed, scales, i, qa[i], qb[i], sbuf[i]);
+            const int rounds = kblocks / kStages;
+            for (int j = 0; j < rounds; ++j) {
+                const bool more = j + 1 < rounds;
+                packed += kRoundBytes;
+                scales += kRoundScaleBytes;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) dst_off[c] = row_smem + (((half * 4 + c) ^ (r & 7)) << 4);
-            for (int kb0 = 0; kb0 < kblocks; kb0 += kPrefetch) {
-                const bool more = kb0 + kPrefetch < kblocks;
-#pragma unroll
-                for (int i = 0; i < kPrefetch; ++i) {
-                    const int s = n % kStages;
-                    const uint32_t parity = (n / kStages) & 1;
-                    ++n;
-                    const uint4 q = qbuf[i];
-                    const uint32_t s2 = sbuf[i] * 0x10001u;     // the scale in both halves
-                    if (more) fetch(kb0 + kPrefetch, i, qbuf[i], sbuf[i]);
-                    if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error))
-                        flag_error(p.error, kErrWaitTimeout);
-                    uint8_t* dst = smem_gen + s * kStageA;
-                    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<uint4*>(dst + dst_off[c]) = dequant_word(words[c], s2);
+                for (int i = 0; i < kStages; ++i) {
+                    const uint4 q0 = qa[i], q1 = qb[i];
+                    const uint32_t sraw = sbuf[i];
+                    if (more) fetch(packed, scales, i, qa[i], qb[i], sbuf[i]);
+                    uint32_t s2a, s2b;                              // the scale in both halves of a word
+                    if constexpr (apg == 1) {
+                        s2a = (sraw & 0xFFFFu) * 0x10001u;
+                        s2b = (sraw >> 16) * 0x10001u;
+                    } else {
+                        s2a = s2b = sraw * 0x10001u;
+                    }
+#ifdef AEON_B200_TUNING
+                    if (p.tune == 1 || p.tune == 3) {          // one lane waits, the warp follows
+                        if (lane == 0) {
+                            if (p.tune == 3) {
+                                uint32_t spins = 0;
+                                while (!ptx::mbar_test_wait(empty_bar + 8 * i, phase ^ 1) && ++spins < (1u << 24)) {}
+                            } else if (!ptx::mbar_wait(empty_bar + 8 * i, phase ^ 1, p.error)) {
+                                flag_error(p.error, kErrWaitTimeout);
+                            }
+                        }
+                        __syncwarp();
+                    } else if (p.tune == 2) {                  // every lane probes without suspending
+                        uint32_t spins = 0;
+                        while (!ptx::mbar_test_wait(empty_bar + 8 * i, phase ^ 1) && ++spins < (1u << 24)) {}
+                    } else
+#endif
+                    if (!ptx::mbar_wait(empty_bar + 8 * i, phase ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
+                    uint8_t* dst = row_dst + i * kStageA;
+                    *reinterpret_cast<uint4*>(dst + ((0u << 4) ^ swz)) = dequant_word(q0.x, s2a);
+                    *reinterpret_cast<uint4*>(dst + ((1u << 4) ^ swz)) = dequant_word(q0.y, s2a);
+                    *reinterpret_cast<uint4*>(dst + ((2u << 4) ^ swz)) = dequant_word(q0.z, s2a);
+                    *reinterpret_cast<uint4*>(dst + ((3u << 4) ^ swz)) = dequant_word(q0.w, s2a);
+                    *reinterpret_cast<uint4*>(dst + ((4u << 4) ^ swz)) = dequant_word(q1.x, s2b);
+                    *reinterpret_cast<uint4*>(dst + ((5u << 4) ^ swz)) = dequant_word(q1.y, s2b);
+                    *reinterpret_cast<uint4*>(dst + ((6u << 4) ^ swz)) = dequant_word(q1.z, s2b);
+                    *reinterpret_cast<uint4*>(dst + ((7u << 4) ^ swz)) = dequant_word(q1.w, s2b);
                     // generic-proxy writes must be visible to the tensor core (async proxy)
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(full_bar + 8 * s);
+                    if (lane == 0) ptx::mbar_arrive(full_bar + 8 * i);
                 }
+                phase ^= 1;
             }
         }
     } else {
@@ -297,32 +345,47 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             const uint32_t buf = it & 1;
             if (!ptx::mbar_wait(acc_full + 8 * buf, (it >> 1) & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
             tc5::fence_after_sync();
-            const uint32_t taddr = tmem_base + ((static_cast<uint32_t>(quad) * 32u) << 16) + buf * kMaxN;
-            for (int c0 = 0; c0 < tile.ntok; c0 += 32) {
-                uint32_t v[32];
-                tc5::ld_32x32(taddr + c0, v);
-                tc5::ld_wait();
-                if constexpr (kGateUp) {
-                    const int hcol = rb * 64 + quad * 16 + (lane & 15);
+            const uint32_t tlane = tmem_base + ((static_cast<uint32_t>(quad) * 32u) << 16) + buf * (kHalves * kMaxN);
+            if constexpr (kGateUp) {
+                // lane L of the first half holds the gate of hidden column rb*128 + L, the same lane of
+                // the second half its up value: one thread finishes the element. The hidden vector is
+                // rounded to fp16 right after, so the fast exponential and division cost nothing visible.
+                const int hcol = rb * kHalfM + quad * 32 + lane;
+                for (int c0 = 0; c0 < tile.ntok; c0 += 16) {
+                    uint32_t gv[16], uv[16];
+                    tc5::ld_32x16(tlane + c0, gv);
+                    tc5::ld_32x16(tlane + kMaxN + c0, uv);
+                    tc5::ld_wait();
+                    __half* out = p.hidden + static_cast<size_t>(tile.pos0 + c0) * p.I + hcol;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float mine = __uint_as_float(v[j]);
-                        const float other = __shfl_xor_sync(0xFFFFFFFFu, mine, 16);
-                        if (lane < 16 && c0 + j < tile.ntok) {
-                            float gate = fminf(mine, p.limit);
-                            float up = fminf(fmaxf(other, -p.limit), p.limit);
-                            const float h = (gate / (1.0f + expf(-gate))) * up;
-                            p.hidden[static_cast<size_t>(tile.pos0 + c0 + j) * p.I + hcol] = __float2half_rn(h);
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < tile.ntok && index_ok(tile.pos0 + c0 + j, p.draws_cap, p.error)) {
+                            const float gate = fminf(__uint_as_float(gv[j]), p.limit);
+                            const float up = fminf(fmaxf(__uint_as_float(uv[j]), -p.limit), p.limit);
+                            const float hv = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                            out[static_cast<size_t>(j) * p.I] = __float2half_rn(hv);
                         }
                     }
-                } else {
-                    const int row = rb * kTileM + quad * 32 + lane;
+                }
+            } else {
+                for (int h = 0; h < kHalves; ++h) {
+                    const int row = rb * kTileM + h * kHalfM + quad * 32 + lane;
+                    for (int c0 = 0; c0 < tile.ntok; c0 += 32) {
+                        uint32_t v[32];
+                        tc5::ld_32x32(tlane + h * kMaxN + c0, v);
+                        tc5::ld_wait();
+                        // the chunk's draw rows and routing weights: lane j reads position c0 + j once,
+                        // every lane then takes them by shuffle instead of 2 x 32 dependent loads
+                        const int my_pos = tile.pos0 + c0 + lane;
+                        const bool have = c0 + lane < tile.ntok && index_ok(my_pos, p.draws_cap, p.error);
+                        int my_draw = have ? p.draw_idx[my_pos] : -1;
+                        const float my_w = have ? p.wpos[my_pos] : 0.f;
+                        if (have && !index_ok(my_draw, p.draws_cap, p.error)) my_draw = -1;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (c0 + j < tile.ntok) {
-                            const int pos = tile.pos0 + c0 + j;
-                            p.contrib[static_cast<size_t>(p.draw_idx[pos]) * p.H + row] =
-                                p.wpos[pos] * __uint_as_float(v[j]);
+                        for (int j = 0; j < 32; ++j) {
+                            const int draw = __shfl_sync(0xFFFFFFFFu, my_draw, j);
+                            const float wj = __shfl_sync(0xFFFFFFFFu, my_w, j);
+                            if (draw >= 0) p.contrib[static_cast<size_t>(draw) * p.H + row] = wj * __uint_as_float(v[j]);
                         }
                     }
                 }
@@ -345,8 +408,9 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
 __global__ void gather_activations_kernel(const void* __restrict__ x, int64_t x_stride, int dtype,
                                           const int32_t* __restrict__ token_idx,
                                           const int32_t* __restrict__ counts, int H,
-                                          __half* __restrict__ xg) {
-    const int placed = counts[2];
+                                          __half* __restrict__ xg, int tokens, int draws_cap,
+                                          int32_t* __restrict__ error) {
+    const int placed = index_ok(counts[2], draws_cap + 1, error) ? counts[2] : 0;
     const int vec_per_row = H / 8;
     const int64_t total = static_cast<int64_t>(placed) * vec_per_row;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -354,6 +418,7 @@ __global__ void gather_activations_kernel(const void* __restrict__ x, int64_t x_
         const int pos = static_cast<int>(i / vec_per_row);
         const int v = static_cast<int>(i - static_cast<int64_t>(pos) * vec_per_row);
         const int token = token_idx[pos];
+        if (!index_ok(token, tokens, error)) continue;      // a token index outside the batch: reported, row left as it is
         const uint4 in = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + token * x_stride)[v];
         uint4 out = in;
         if (dtype == AEON_B200_BF16) {
@@ -374,13 +439,19 @@ __global__ void gather_activations_kernel(const void* __restrict__ x, int64_t x_
 // Tile list: every expert's positions in runs of at most kMaxN. One CTA; experts <= 1024.
 __global__ void build_tiles_kernel(const int32_t* __restrict__ offsets, const int32_t* __restrict__ slot_of,
                                    int experts, int skip_absent, PrefillTile* __restrict__ tiles,
-                                   int32_t* __restrict__ n_tiles, int32_t* __restrict__ error) {
+                                   int32_t* __restrict__ n_tiles, int32_t* __restrict__ error, int pool_slots,
+                                   int tiles_cap) {
     __shared__ int base[1025];
     const int e = threadIdx.x;
     int count = 0, slot = -1;
     if (e < experts) {
         count = offsets[e + 1] - offsets[e];
         slot = slot_of ? slot_of[e] : e;
+        if (pool_slots > 0 && slot >= pool_slots) {          // never an address: reported, treated as absent
+            atomicCAS(error, kErrNone, kErrIdOutOfRange);
+            slot = -1;
+            count = 0;
+        }
         if (slot < 0 && count > 0) {
             if (skip_absent) count = 0;
             else atomicCAS(error, kErrNone, kErrExpertAbsent);
@@ -403,7 +474,7 @@ __global__ void build_tiles_kernel(const int32_t* __restrict__ offsets, const in
             t.pos0 = offsets[e] + c * kMaxN;
             t.ntok = min(kMaxN, count - c * kMaxN);
             t.pad = e;
-            tiles[base[e] + c] = t;
+            if (index_ok(base[e] + c, tiles_cap, error)) tiles[base[e] + c] = t;
         }
     }
 }
@@ -412,7 +483,7 @@ __global__ void moe_accumulate_prefill_kernel(float* __restrict__ accum, int64_t
                                               const float* __restrict__ contrib,
                                               const int32_t* __restrict__ ids,
                                               const int32_t* __restrict__ slot_of, int skip_absent,
-                                              int overwrite, int experts, int tokens, int top_k, int H) {
+                                              int overwrite, int experts, int tokens, int top_k, int H, int pool_slots) {
     const int vec_per_row = H / 4;
     const int64_t total = static_cast<int64_t>(tokens) * vec_per_row;
     for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -424,7 +495,9 @@ __global__ void moe_accumulate_prefill_kernel(float* __restrict__ accum, int64_t
         for (int slot = 0; slot < top_k; ++slot) {
             const int draw = token * top_k + slot;
             const int id = ids[draw];
-            if (id >= 0 && id < experts && !(skip_absent && slot_of[id] < 0)) {
+            // absent: no slot, or a slot beyond the declared pool (reported by the work-list kernel)
+            if (id >= 0 && id < experts &&
+                !(skip_absent && (slot_of[id] < 0 || (pool_slots > 0 && slot_of[id] >= pool_slots)))) {
                 const float4 c = reinterpret_cast<const float4*>(contrib + static_cast<size_t>(draw) * H)[v];
                 a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w;
             }
@@ -453,8 +526,7 @@ void free_prefill_scratch(aeon_b200_ctx* ctx) {
     if (!s) return;
     void* bufs[] = {s->xg, s->hidden, s->contrib, s->offsets, s->token_idx, s->draw_idx, s->counts,
                     s->n_tiles, s->wpos, s->tiles, s->entries};
-    for (void* b : bufs)
-        if (b) (void)cudaFree(b);
+    for (void* b : bufs) ctx_device_free(ctx, b);
     delete s;
     ctx->prefill = nullptr;
 }
@@ -468,7 +540,8 @@ static PrefillScratch* ensure_scratch(aeon_b200_ctx* ctx, int tokens) {
     const aeon_b200_moe_config& cfg = ctx->cfg;
     const size_t draws = static_cast<size_t>(tokens) * cfg.top_k;
     auto alloc = [&](auto*& ptr, size_t count) {
-        AEON_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&ptr), count * sizeof(*ptr)));
+        using Ptr = std::remove_reference_t<decltype(ptr)>;
+        ptr = static_cast<Ptr>(ctx_device_alloc(ctx, count * sizeof(*ptr), "prefill scratch"));
         s->bytes += count * sizeof(*ptr);
     };
     // 64 spare rows so a TMA box that starts inside the last tile stays inside the allocation
@@ -510,11 +583,12 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
 
     launch_permutation(ctx, topk_ids, tokens, cfg.top_k, cfg.experts, s->offsets, s->token_idx, s->draw_idx,
                        topk_weights, s->wpos, slot_of_expert, s->entries, s->counts, skip, stream);
+    const int tiles_cap = cfg.experts + tokens * cfg.top_k / kMaxN + 1;
     build_tiles_kernel<<<1, 1024, 0, stream>>>(s->offsets, slot_of_expert, cfg.experts, skip ? 1 : 0, s->tiles,
-                                               s->n_tiles, ctx->d_error);
+                                               s->n_tiles, ctx->d_error, ctx->pool_slots, tiles_cap);
     AEON_CUDA_CHECK(cudaGetLastError());
-    gather_activations_kernel<<<4 * ctx->sm_count, 256, 0, stream>>>(x, x_stride, cfg.act_dtype, s->token_idx,
-                                                                     s->counts, cfg.hidden, s->xg);
+    gather_activations_kernel<<<4 * ctx->sm_count, 256, 0, stream>>>(
+        x, x_stride, cfg.act_dtype, s->token_idx, s->counts, cfg.hidden, s->xg, tokens, tokens * cfg.top_k, ctx->d_error);
     AEON_CUDA_CHECK(cudaGetLastError());
 
     PrefillParams p{};
@@ -534,6 +608,12 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
     p.contrib = s->contrib;
     p.limit = cfg.swiglu_limit;
     p.error = ctx->d_error;
+    p.draws_cap = tokens * cfg.top_k;
+    p.tiles_cap = tiles_cap;
+#ifdef AEON_B200_TUNING
+    static const int tune_p = getenv("AEON_B200_TUNE_P") ? atoi(getenv("AEON_B200_TUNE_P")) : 0;
+    p.tune = tune_p;
+#endif
 
     cudaEvent_t* ev = nullptr;
     if (ctx->timing_enabled) {
@@ -564,7 +644,8 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
     moe_accumulate_prefill_kernel<<<blocks, 256, 0, stream>>>(moe_accum, accum_stride, s->contrib, topk_ids,
                                                               slot_of_expert, skip ? 1 : 0,
                                                               (flags & AEON_B200_DECODE_OVERWRITE) ? 1 : 0,
-                                                              cfg.experts, tokens, cfg.top_k, cfg.hidden);
+                                                              cfg.experts, tokens, cfg.top_k, cfg.hidden,
+                                                              ctx->pool_slots);
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 6;
 }

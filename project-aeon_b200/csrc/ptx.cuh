@@ -54,6 +54,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe of a phase (mbarrier.test_wait never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait. Returns false when the iteration budget ran out, or at once when
 // `error_flag` is already set: after the first failure every later wait of the launch falls
 // through, so the kernel keeps its barrier structure (nobody is left alone at a bar.sync)
@@ -205,6 +220,63 @@ __device__ __forceinline__ void fold_group(float (&acc)[4], const float (&tlo)[4
     acc[1] = fmaf(sa24, fmaf(thi[1], 0.0625f, tlo[1]), fmaf(sa8, xs.y, acc[1]));
     acc[2] = fmaf(sb24, fmaf(thi[2], 0.0625f, tlo[2]), fmaf(sb8, xs.x, acc[2]));
     acc[3] = fmaf(sb24, fmaf(thi[3], 0.0625f, tlo[3]), fmaf(sb8, xs.y, acc[3]));
+}
+
+// ---- single-accumulator form (row-streaming kernels) -------------------------------------------
+// When the activations of the columns that meet the high-nibble plane (columns 2, 3, 6, 7 of
+// every 8: bit 1 of the column index) are stored divided by 16 -- exact in fp16 above the
+// subnormal range, within 2^-25 absolute below it -- both planes carry the factor 2^-24 and can
+// share one accumulator:
+//     sum_k (u_k - 8) x_k  =  2^24 * T  -  8 * sum_k x_k
+// which halves the accumulator registers and drops the plane-merging multiply-add.
+
+// D = A * B with a zero addend (the first MMA of a chain: no accumulator to clear beforehand).
+__device__ __forceinline__ void mma_f16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+// The two nibble planes of a word pair (rows g and g+8) as MMA A fragments.
+struct WordPlanes {
+    uint32_t lo[4], hi[4];
+};
+
+__device__ __forceinline__ WordPlanes word_planes(uint32_t wa, uint32_t wb) {
+    const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+    WordPlanes p;
+    p.lo[0] = wa & 0x000F000Fu; p.lo[1] = wb & 0x000F000Fu; p.lo[2] = wa8 & 0x000F000Fu; p.lo[3] = wb8 & 0x000F000Fu;
+    p.hi[0] = wa & 0x00F000F0u; p.hi[1] = wb & 0x00F000F0u; p.hi[2] = wa8 & 0x00F000F0u; p.hi[3] = wb8 & 0x00F000F0u;
+    return p;
+}
+
+// T (+)= planes * b: b = the token's activations for the word's 8 columns as column pairs
+// (0,1),(2,3),(4,5),(6,7), pairs (2,3) and (6,7) pre-divided by 16. kFirst starts the chain.
+template <bool kFirst>
+__device__ __forceinline__ void mma_planes(float (&T)[4], const WordPlanes& p, const uint4& b) {
+    if constexpr (kFirst) mma_f16_first(T, p.lo[0], p.lo[1], p.lo[2], p.lo[3], b.x, b.z);
+    else mma_f16(T, p.lo[0], p.lo[1], p.lo[2], p.lo[3], b.x, b.z);
+    mma_f16(T, p.hi[0], p.hi[1], p.hi[2], p.hi[3], b.y, b.w);
+}
+
+// acc += scale * (2^24 * T + xs8) with xs8 = -8 * (token, group) activation sum: rows g (sa)
+// and g+8 (sb), token columns 2t (xs8.x) and 2t+1 (xs8.y).
+__device__ __forceinline__ void fold_single(float (&acc)[4], const float (&T)[4], float sa, float sb, float2 xs8) {
+    acc[0] = fmaf(sa, fmaf(T[0], 16777216.0f, xs8.x), acc[0]);
+    acc[1] = fmaf(sa, fmaf(T[1], 16777216.0f, xs8.y), acc[1]);
+    acc[2] = fmaf(sb, fmaf(T[2], 16777216.0f, xs8.x), acc[2]);
+    acc[3] = fmaf(sb, fmaf(T[3], 16777216.0f, xs8.y), acc[3]);
+}
+
+// The two fp16 halves of a 32-bit word as fp32.
+__device__ __forceinline__ float half_lo_as_float(uint32_t bits) {
+    return __low2float(*reinterpret_cast<const __half2*>(&bits));
+}
+__device__ __forceinline__ float half_hi_as_float(uint32_t bits) {
+    return __high2float(*reinterpret_cast<const __half2*>(&bits));
 }
 
 __device__ __forceinline__ float2 lds_f2(uint32_t addr) {

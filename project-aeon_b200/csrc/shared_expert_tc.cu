@@ -368,10 +368,10 @@ void run(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2, con
         ctx->shared_tc = s;
     }
     if (s->floats < need) {
-        if (s->partial) AEON_CUDA_CHECK(cudaFree(s->partial));
+        ctx_device_free(ctx, s->partial);
         s->partial = nullptr;
         s->floats = 0;
-        AEON_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&s->partial), need * sizeof(float)));
+        s->partial = static_cast<float*>(ctx_device_alloc(ctx, need * sizeof(float), "shared expert split-K partials"));
         s->floats = need;
     }
     uint16_t* hi = reinterpret_cast<uint16_t*>(ctx->d_sh_hi);
@@ -433,7 +433,7 @@ void run(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2, con
 void free_shared_tc_scratch(aeon_b200_ctx* ctx) {
     SharedTcScratch* s = static_cast<SharedTcScratch*>(ctx->shared_tc);
     if (!s) return;
-    if (s->partial) (void)cudaFree(s->partial);
+    ctx_device_free(ctx, s->partial);
     delete s;
     ctx->shared_tc = nullptr;
 }
@@ -446,10 +446,10 @@ bool shared_expert_tc_supports(const aeon_b200_moe_config& cfg, int64_t accum_st
 void launch_shared_expert_tc(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2,
                              const void* x, int64_t x_stride, int tokens, float* moe_accum,
                              int64_t accum_stride, cudaStream_t stream) {
-    // One token tile (up to 256 tokens) per pass: the kernels index any number of token tiles,
-    // but only the single-tile shape has been checked against the oracle on a B200 so far, so
-    // larger batches are fed tile by tile (stream order keeps the passes apart; the hidden
-    // planes and the partial sums are reused).
+    // One token tile (up to 256 tokens) per pass. The split-K partial sums and the hidden planes
+    // are sized for one tile (the context's scratch holds max_tokens rows, and a tile is what
+    // the 512 TMEM columns of a CTA accumulate), so a larger batch runs tile by tile; stream
+    // order keeps the passes apart and the 88 MB of dense weights stay L2-resident between them.
     const uint16_t* xs = static_cast<const uint16_t*>(x);
     for (int t0 = 0; t0 < tokens; t0 += kMaxN) {
         const int n = std::min(kMaxN, tokens - t0);

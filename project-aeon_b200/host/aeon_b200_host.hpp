@@ -22,6 +22,14 @@
 //   V4TieredExpertExecutor      src/architecture/deepseek_v4/moe/v4_expert_executor.hpp:178-634
 //   dispatch_router             src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:124-159
 //   dispatch_expert_permutation src/platform/ops/expert_permutation.hpp:130-175
+//   select_device / DeviceScope src/platform/device.hpp:29-90
+//   DeviceStreams               src/infrastructure/device_streams.hpp:32-74
+//   DeviceContext               src/infrastructure/parallel/device_context.hpp:23-49
+//   enable_peer_access          src/infrastructure/parallel/peer_access.hpp:29-50
+//   ExpertBackendRegistry       src/infrastructure/backend_registry/expert_backend.hpp:14-79
+//   AeonModelManifest           src/infrastructure/artifact/model_manifest.hpp:102-209
+//   ParallelGroup               the communicator the reference plans as TensorParallelGroup
+//                               (plans-and-docs/execution/active/MULTI_GPU_EXECUTION_PLAN.md:189-235)
 #pragma once
 
 #include "aeon_b200.h"
@@ -32,11 +40,15 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <array>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
+#include <functional>
+#include <iostream>
 #include <list>
+#include <sstream>
 #include <stdexcept>
 #include <string>
 #include <string_view>
@@ -65,6 +77,114 @@ inline aeon_b200_moe_config moe_config_preset(const char* name) {
     aeon_b200_moe_config cfg{};
     check_status(aeon_b200_config_preset(name, &cfg));
     return cfg;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Devices and streams. The device is an index the caller supplies, never a heuristic; a device
+// that is not there is a named error (src/platform/device.hpp:24-61).
+// ---------------------------------------------------------------------------------------------
+inline int select_device(int index, bool verbose = true) {
+    const int status = aeon_b200_device_select(index);
+    if (status != AEON_B200_OK) throw std::runtime_error(aeon_b200_last_error());
+    if (verbose) {
+        char name[128] = {0};
+        int pci_bus = 0;
+        if (aeon_b200_device_describe(index, name, sizeof(name), &pci_bus, nullptr, nullptr) == AEON_B200_OK)
+            std::cout << "[Aeon Device] Using GPU [" << index << "]: " << name << " (PCI Bus 0x" << std::hex << pci_bus
+                      << std::dec << ")" << std::endl;
+    }
+    return index;
+}
+
+// Sets a device for a region and restores the previous one on exit, so a per-rank object (a
+// stream set, a pool) is built under its own device without leaking that choice.
+class DeviceScope {
+public:
+    explicit DeviceScope(int index) {
+        if (aeon_b200_device_current(&previous_) != AEON_B200_OK) previous_ = 0;
+        if (aeon_b200_device_select(index) != AEON_B200_OK)
+            throw std::runtime_error(std::string("DeviceScope: ") + aeon_b200_last_error());
+    }
+    ~DeviceScope() { (void)aeon_b200_device_select(previous_); }
+    DeviceScope(const DeviceScope&) = delete;
+    DeviceScope& operator=(const DeviceScope&) = delete;
+
+private:
+    int previous_{0};
+};
+
+// The four streams of a device, split by traffic class (compute: every kernel, and where
+// per-transfer events are awaited; sdma: warm-tier uploads; sdma_cold: cold-tier uploads;
+// demotion: eviction downloads). Non-blocking; all four or none.
+struct DeviceStreams {
+    void* compute{nullptr};
+    void* sdma{nullptr};
+    void* sdma_cold{nullptr};
+    void* demotion{nullptr};
+
+    static DeviceStreams create() {
+        DeviceStreams streams;
+        try {
+            streams.compute = create_one("compute");
+            streams.sdma = create_one("sdma");
+            streams.sdma_cold = create_one("sdma_cold");
+            streams.demotion = create_one("demotion");
+        } catch (...) {
+            streams.destroy();
+            throw;
+        }
+        return streams;
+    }
+    void destroy() noexcept {
+        for (void** stream : {&compute, &sdma, &sdma_cold, &demotion}) {
+            if (*stream != nullptr) {
+                (void)aeon_b200_stream_destroy(*stream);
+                *stream = nullptr;
+            }
+        }
+    }
+
+private:
+    static void* create_one(const char* identity) {
+        void* stream = nullptr;
+        if (aeon_b200_stream_create(&stream) != AEON_B200_OK)
+            throw std::runtime_error(std::string("DeviceStreams: stream create(") + identity + "): " +
+                                     aeon_b200_last_error());
+        return stream;
+    }
+};
+
+// A device and the four streams that belong to it, created under its own DeviceScope.
+struct DeviceContext {
+    int device{-1};
+    DeviceStreams streams;
+
+    static DeviceContext create(int device) {
+        DeviceContext context;
+        context.device = device;
+        {
+            DeviceScope scope(device);
+            context.streams = DeviceStreams::create();
+        }
+        return context;
+    }
+    void destroy() noexcept {
+        streams.destroy();
+        device = -1;
+    }
+};
+
+// Peer access for every ordered pair of `devices` where the hardware allows it, enabled from the
+// accessing device. Best effort, never a refusal: a copy between devices works without it.
+inline void enable_peer_access(const std::vector<int>& devices, bool verbose = false) {
+    for (int accessor : devices)
+        for (int peer : devices) {
+            if (accessor == peer) continue;
+            int enabled = 0;
+            (void)aeon_b200_device_enable_peer_access(accessor, peer, &enabled);
+            if (!enabled && verbose)
+                std::printf("[Peer] device %d cannot access device %d directly\n", accessor, peer);
+        }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -131,42 +251,50 @@ public:
                                     uint32_t artifact_max_tp, uint32_t num_layers) {
         const uint32_t tp = config.tensor_parallel, pp = config.pipeline_parallel;
         const uint32_t ep = config.expert_parallel;
-        if (tp == 0 || pp == 0 || ep == 0)
-            throw std::invalid_argument(
-                "parallel topology: tensor, pipeline and expert degrees must be at least 1 (tensor_parallel=" +
-                std::to_string(tp) + ", pipeline_parallel=" + std::to_string(pp) +
-                ", expert_parallel=" + std::to_string(ep) + ")");
-        if (num_layers == 0) throw std::invalid_argument("parallel topology: the model has no layers");
-        if (artifact_max_tp == 0)
-            throw std::invalid_argument("parallel topology: the artifact's max tensor-parallel degree is 0");
-        if (artifact_max_tp % tp != 0)
-            throw std::invalid_argument("parallel topology: tensor_parallel=" + std::to_string(tp) +
-                                        " does not divide the artifact's max tensor-parallel degree " +
-                                        std::to_string(artifact_max_tp));
-        if (pp > num_layers)
-            throw std::invalid_argument("parallel topology: pipeline_parallel=" + std::to_string(pp) +
-                                        " exceeds the " + std::to_string(num_layers) + " model layers");
-        if (ep > 1 && tp > 1)
-            throw std::invalid_argument(
-                "parallel topology: expert_parallel and tensor_parallel share the ranks of a stage; "
-                "set one of them to 1");
-        const size_t per_stage = static_cast<size_t>(tp) * ep;
-        const size_t rank_count = per_stage * pp;
+        const auto n = [](auto v) { return std::to_string(v); };
+        const size_t rank_count = static_cast<size_t>(tp) * ep * pp;
         std::vector<int> ids = config.device_ids;
         if (ids.empty())
             for (size_t i = 0; i < rank_count; ++i) ids.push_back(static_cast<int>(i));
-        if (ids.size() != rank_count)
-            throw std::invalid_argument("parallel topology: device_ids has " + std::to_string(ids.size()) +
-                                        " entries but tp * ep * pp = " + std::to_string(rank_count));
+        // The refusals. Their order and their texts are the contract shared with the reference
+        // (src/infrastructure/parallel/parallel_topology.hpp:114-164); the first rule that is
+        // broken is the one reported, and a later rule may rely on the earlier ones holding.
+        struct Rule {
+            std::function<bool()> broken;
+            std::function<std::string()> message;
+        };
+        const Rule rules[] = {
+            {[&] { return tp == 0 || pp == 0 || ep == 0; },
+             [&] {
+                 return "tensor, pipeline and expert degrees must be at least 1 (tensor_parallel=" + n(tp) +
+                        ", pipeline_parallel=" + n(pp) + ", expert_parallel=" + n(ep) + ")";
+             }},
+            {[&] { return num_layers == 0; }, [&] { return std::string("the model has no layers"); }},
+            {[&] { return artifact_max_tp == 0; },
+             [&] { return std::string("the artifact's max tensor-parallel degree is 0"); }},
+            {[&] { return artifact_max_tp % tp != 0; },
+             [&] {
+                 return "tensor_parallel=" + n(tp) + " does not divide the artifact's max tensor-parallel degree " +
+                        n(artifact_max_tp);
+             }},
+            {[&] { return pp > num_layers; },
+             [&] { return "pipeline_parallel=" + n(pp) + " exceeds the " + n(num_layers) + " model layers"; }},
+            {[&] { return ep > 1 && tp > 1; },
+             [&] {
+                 return std::string("expert_parallel and tensor_parallel share the ranks of a stage; set one of "
+                                    "them to 1");
+             }},
+            {[&] { return ids.size() != rank_count; },
+             [&] { return "device_ids has " + n(ids.size()) + " entries but tp * ep * pp = " + n(rank_count); }},
+        };
+        for (const Rule& rule : rules)
+            if (rule.broken()) throw std::invalid_argument("parallel topology: " + rule.message());
         for (size_t i = 0; i < ids.size(); ++i) {
             if (ids[i] < 0 || ids[i] >= visible_devices)
-                throw std::invalid_argument("parallel topology: device id " + std::to_string(ids[i]) +
-                                            " is out of range for " + std::to_string(visible_devices) +
-                                            " visible devices");
-            for (size_t j = 0; j < i; ++j)
-                if (ids[i] == ids[j])
-                    throw std::invalid_argument("parallel topology: device id " + std::to_string(ids[i]) +
-                                                " is listed more than once");
+                throw std::invalid_argument("parallel topology: device id " + n(ids[i]) + " is out of range for " +
+                                            n(visible_devices) + " visible devices");
+            if (std::find(ids.begin(), ids.begin() + i, ids[i]) != ids.begin() + i)
+                throw std::invalid_argument("parallel topology: device id " + n(ids[i]) + " is listed more than once");
         }
         ParallelTopology topo;
         topo.tp_ = tp;
@@ -232,7 +360,7 @@ private:
 // ---------------------------------------------------------------------------------------------
 // Expert payload format and pool.
 // ---------------------------------------------------------------------------------------------
-enum class ExpertFormatKind : uint32_t { OPAQUE = 0, SWIZZLED_W4A16 = 1 };
+enum class ExpertFormatKind : uint32_t { OPAQUE = 0, SWIZZLED_W4A16 = 1, UNKNOWN = 0xFFFFFFFFu };
 
 struct ExpertFormatDescriptor {
     ExpertFormatKind kind{ExpertFormatKind::SWIZZLED_W4A16};
@@ -277,6 +405,62 @@ inline ExpertFormatDescriptor make_swizzled_expert_format(const aeon_b200_moe_co
     f.shard_bytes = static_cast<size_t>(shard_bytes);
     return f;
 }
+
+// Which weight backend executes which expert format (expert_backend.hpp:14-79). One backend
+// here, the swizzled W4A16 one; its payload size follows the layer shape instead of being one
+// compile-time constant, so a descriptor is made for a configuration and validates the size an
+// artifact declares against it.
+struct ExpertBackendDescriptor {
+    std::string_view name;
+    ExpertFormatKind format_kind{ExpertFormatKind::UNKNOWN};
+    uint32_t artifact_version_min{0}, artifact_version_max{0};
+    size_t payload_bytes{0};                 // 0: any size (no configuration bound to the descriptor)
+    bool supports_fused_moe_experts{false};
+
+    void validate_format(const ExpertFormatDescriptor& format) const {
+        if (format.kind != format_kind || format.version < artifact_version_min ||
+            format.version > artifact_version_max || (payload_bytes != 0 && format.payload_bytes != payload_bytes))
+            throw std::runtime_error("Expert backend '" + std::string(name) +
+                                     "' is incompatible with the loaded expert artifact");
+    }
+};
+
+class ExpertBackendRegistry {
+public:
+    static const ExpertBackendDescriptor& resolve(std::string_view name) {
+        if (name == "swizzled_w4a16") return swizzled_w4a16();
+        throw std::invalid_argument("ExpertBackendRegistry: unsupported weight backend '" + std::string(name) + "'");
+    }
+    static const ExpertBackendDescriptor& resolve(ExpertFormatKind kind) {
+        if (kind == ExpertFormatKind::SWIZZLED_W4A16) return swizzled_w4a16();
+        throw std::invalid_argument("ExpertBackendRegistry: no backend is registered for the requested expert format");
+    }
+    static const ExpertBackendDescriptor& resolve(std::string_view name, const ExpertFormatDescriptor& format) {
+        const ExpertBackendDescriptor& backend = resolve(name);
+        backend.validate_format(format);
+        return backend;
+    }
+    static const ExpertBackendDescriptor& resolve(const ExpertFormatDescriptor& format) {
+        const ExpertBackendDescriptor& backend = resolve(format.kind);
+        backend.validate_format(format);
+        return backend;
+    }
+    // The backend bound to one layer shape: its payload size is the swizzled layout's.
+    static ExpertBackendDescriptor for_config(const aeon_b200_moe_config& cfg) {
+        ExpertBackendDescriptor d = swizzled_w4a16();
+        aeon_b200_expert_layout layout{};
+        check_status(aeon_b200_expert_layout_of(&cfg, &layout));
+        d.payload_bytes = static_cast<size_t>(layout.payload_bytes);
+        return d;
+    }
+
+private:
+    static const ExpertBackendDescriptor& swizzled_w4a16() {
+        // version 2: the reference's container; version 3: the shard-aware one
+        static const ExpertBackendDescriptor descriptor{"swizzled_w4a16", ExpertFormatKind::SWIZZLED_W4A16, 2, 3, 0, true};
+        return descriptor;
+    }
+};
 
 // One device slab of slots x payload_bytes; a slot is a byte-identical expert payload.
 class UnifiedVRAMExpertPool {
@@ -689,6 +873,11 @@ public:
     }
 
     const ExpertFormatDescriptor& format() const noexcept { return format_; }
+    void close() noexcept {
+        locations_.clear();
+        format_ = ExpertFormatDescriptor{};
+        file_.close();
+    }
     Location get_expert_location(uint32_t layer, uint32_t expert) const { return locations_.at(index_of(layer, expert)); }
     const uint8_t* get_expert_data(uint32_t layer, uint32_t expert) const {
         return file_.data() + locations_.at(index_of(layer, expert)).offset;
@@ -940,34 +1129,177 @@ public:
         return it->second;
     }
     size_t tensor_count() const noexcept { return tensors_.size(); }
+    size_t file_size() const noexcept { return file_.size(); }
+    void close() noexcept {
+        tensors_.clear();
+        file_.close();
+    }
 
 private:
     MappedFile file_;
     std::unordered_map<std::string, LoadedTensor> tensors_;
 };
 
+// What a model directory declares about itself (model_manifest.json; the reference's
+// AeonModelManifest, src/infrastructure/artifact/model_manifest.hpp:102-209): identity, the weight
+// backend, the three file names, format versions and sizes. Keys are unique in the file, so
+// each is found by name wherever it sits (the "artifact" object is flattened). Version 1 is the
+// reference's manifest; version 2 adds the shard fields of the shard-aware container.
+struct AeonArtifactSpec {
+    std::string dense_filename{"model_dense.aeon"};
+    std::string experts_filename{"model_experts_swizzled.aeon"};
+    std::string index_filename{"model_experts_swizzled.index"};
+    uint32_t expected_dense_version{1};
+    ExpertFormatKind expert_format_kind{ExpertFormatKind::SWIZZLED_W4A16};
+    uint32_t expected_expert_version{0};           // 0: version 2 or 3
+    uint32_t expert_sector_size{4096};
+    size_t expected_expert_payload_bytes{0};       // 0: any
+};
+
+struct AeonModelManifest {
+    uint32_t manifest_version{0};
+    std::string model_family, architecture, weight_backend;
+    AeonArtifactSpec artifact{};
+    size_t dense_file_bytes{0};
+    uint32_t num_layers{0}, experts_per_layer{0};
+    uint32_t max_tensor_parallel{1};
+
+    static AeonModelManifest load_from_json(const std::string& manifest_path) {
+        std::ifstream file(manifest_path);
+        if (!file.is_open()) throw std::runtime_error("AeonModelManifest: failed to open manifest: " + manifest_path);
+        std::stringstream buffer;
+        buffer << file.rdbuf();
+        const std::string text = buffer.str();
+        AeonModelManifest m;
+        m.manifest_version = static_cast<uint32_t>(number(text, "manifest_version"));
+        m.model_family = string(text, "model_family");
+        m.architecture = string(text, "architecture");
+        m.weight_backend = string(text, "weight_backend");
+        m.artifact.dense_filename = string(text, "dense_filename");
+        m.artifact.experts_filename = string(text, "experts_filename");
+        m.artifact.index_filename = string(text, "index_filename");
+        m.artifact.expected_dense_version = static_cast<uint32_t>(number(text, "dense_format_version"));
+        const std::string format = string(text, "expert_format");
+        m.artifact.expert_format_kind =
+            format == "swizzled_w4a16" ? ExpertFormatKind::SWIZZLED_W4A16 : ExpertFormatKind::UNKNOWN;
+        m.artifact.expected_expert_version = static_cast<uint32_t>(number(text, "expert_format_version"));
+        m.artifact.expert_sector_size = static_cast<uint32_t>(number(text, "expert_sector_size"));
+        m.artifact.expected_expert_payload_bytes = static_cast<size_t>(number(text, "expert_payload_bytes"));
+        m.dense_file_bytes = static_cast<size_t>(number(text, "dense_file_bytes"));
+        m.num_layers = static_cast<uint32_t>(number(text, "num_layers"));
+        m.experts_per_layer = static_cast<uint32_t>(number(text, "experts_per_layer"));
+        if (has_key(text, "max_tensor_parallel"))
+            m.max_tensor_parallel = static_cast<uint32_t>(number(text, "max_tensor_parallel"));
+        m.validate();
+        return m;
+    }
+
+    void validate() const {
+        if (manifest_version != 1 && manifest_version != 2)
+            throw std::invalid_argument("AeonModelManifest: unsupported manifest version " + std::to_string(manifest_version));
+        if (model_family.empty() || architecture.empty() || weight_backend.empty())
+            throw std::invalid_argument("AeonModelManifest: model identity is incomplete");
+        const uint32_t sector = artifact.expert_sector_size;
+        if (artifact.dense_filename.empty() || artifact.experts_filename.empty() || artifact.index_filename.empty() ||
+            artifact.expected_dense_version == 0 || artifact.expert_format_kind == ExpertFormatKind::UNKNOWN ||
+            artifact.expected_expert_version == 0 || sector == 0 || (sector & (sector - 1)) != 0 ||
+            artifact.expected_expert_payload_bytes == 0)
+            throw std::invalid_argument("AeonModelManifest: artifact identity is incomplete");
+        if (weight_backend != ExpertBackendRegistry::resolve(artifact.expert_format_kind).name)
+            throw std::invalid_argument("AeonModelManifest: weight backend does not match expert format kind");
+        if (dense_file_bytes == 0 || num_layers == 0 || experts_per_layer == 0)
+            throw std::invalid_argument("AeonModelManifest: dense size and catalog dimensions must be non-zero");
+        if (artifact.expected_expert_payload_bytes % sector != 0)
+            throw std::invalid_argument("AeonModelManifest: expert payload is not a multiple of the sector size");
+    }
+
+    void validate_loaded(const ExpertFormatDescriptor& loaded, size_t loaded_dense_file_bytes) const {
+        validate();
+        if (loaded_dense_file_bytes != dense_file_bytes)
+            throw std::runtime_error("AeonModelManifest: dense file size does not match the manifest");
+        if (loaded.kind != artifact.expert_format_kind || loaded.version != artifact.expected_expert_version ||
+            loaded.sector_size != artifact.expert_sector_size ||
+            loaded.payload_bytes != artifact.expected_expert_payload_bytes || loaded.num_layers != num_layers ||
+            loaded.experts_per_layer != experts_per_layer || loaded.shard_count != max_tensor_parallel)
+            throw std::runtime_error("AeonModelManifest: loaded artifact identity does not match the manifest");
+    }
+
+private:
+    static size_t value_start(const std::string& text, const std::string& key) {
+        const std::string quoted = "\"" + key + "\"";
+        size_t at = text.find(quoted);
+        if (at == std::string::npos) throw std::invalid_argument("AeonModelManifest: missing key '" + key + "'");
+        at = text.find(':', at + quoted.size());
+        if (at == std::string::npos) throw std::invalid_argument("AeonModelManifest: key '" + key + "' has no value");
+        ++at;
+        while (at < text.size() && (text[at] == ' ' || text[at] == '\t' || text[at] == '\n' || text[at] == '\r')) ++at;
+        return at;
+    }
+    static bool has_key(const std::string& text, const std::string& key) {
+        return text.find("\"" + key + "\"") != std::string::npos;
+    }
+    static uint64_t number(const std::string& text, const std::string& key) {
+        size_t at = value_start(text, key);
+        if (at >= text.size() || text[at] < '0' || text[at] > '9')
+            throw std::invalid_argument("AeonModelManifest: key '" + key + "' is not an unsigned number");
+        uint64_t value = 0;
+        for (; at < text.size() && text[at] >= '0' && text[at] <= '9'; ++at) value = value * 10 + (text[at] - '0');
+        return value;
+    }
+    static std::string string(const std::string& text, const std::string& key) {
+        size_t at = value_start(text, key);
+        if (at >= text.size() || text[at] != '"')
+            throw std::invalid_argument("AeonModelManifest: key '" + key + "' is not a string");
+        const size_t end = text.find('"', at + 1);
+        if (end == std::string::npos) throw std::invalid_argument("AeonModelManifest: key '" + key + "' is not a string");
+        return text.substr(at + 1, end - at - 1);
+    }
+};
+
 // The reference's loader surface for this path (src/infrastructure/artifact/aeon_loader.hpp:
 // 41-166): one model directory, dense tensors by name, experts by (layer, expert), plus the
-// planned rank_slice.
+// planned rank_slice. A directory with a manifest is opened through it: the backend the manifest
+// names is resolved and checked against the artifact first, the files after, and the loaded
+// identity against the manifest last (aeon_loader.hpp:43-78).
 class AeonModelLoader {
 public:
-    struct Artifact {
-        std::string dense_filename{"model_dense.aeon"};
-        std::string experts_filename{"model_experts_swizzled.aeon"};
-        std::string index_filename{"model_experts_swizzled.index"};
-        uint32_t expected_dense_version{1};
-        uint32_t expected_expert_version{0};    // 0: version 2 or 3
-        size_t expected_payload_bytes{0};       // 0: any
-    };
+    using Artifact = AeonArtifactSpec;
 
-    void open_model(const std::string& model_dir) { open_model(model_dir, Artifact{}); }
+    void open_model(const std::string& model_dir) {
+        const std::string manifest_path = model_dir + "/model_manifest.json";
+        std::ifstream probe(manifest_path);
+        if (probe.is_open()) {
+            probe.close();
+            open_model(model_dir, AeonModelManifest::load_from_json(manifest_path));
+            return;
+        }
+        open_model(model_dir, Artifact{});
+    }
     void open_model(const std::string& model_dir, const Artifact& artifact) {
-        if (artifact.dense_filename.empty() || artifact.experts_filename.empty() || artifact.index_filename.empty())
-            throw std::invalid_argument("AeonModelLoader: artifact file names must not be empty");
+        const uint32_t sector = artifact.expert_sector_size;
+        if (artifact.dense_filename.empty() || artifact.experts_filename.empty() || artifact.index_filename.empty() ||
+            artifact.expected_dense_version == 0 || sector == 0 || (sector & (sector - 1)) != 0)
+            throw std::invalid_argument("AeonModelLoader: artifact specification is incomplete");
         dense_.open(model_dir + "/" + artifact.dense_filename, artifact.expected_dense_version);
         experts_.open(model_dir + "/" + artifact.index_filename, model_dir + "/" + artifact.experts_filename,
-                      artifact.expected_expert_version, artifact.expected_payload_bytes);
+                      artifact.expected_expert_version, artifact.expected_expert_payload_bytes);
         model_dir_ = model_dir;
+    }
+    void open_model(const std::string& model_dir, const AeonModelManifest& manifest) {
+        manifest.validate();
+        const ExpertBackendDescriptor& backend = ExpertBackendRegistry::resolve(manifest.weight_backend);
+        if (backend.format_kind != manifest.artifact.expert_format_kind)
+            throw std::invalid_argument("AeonModelLoader: manifest backend does not match its artifact format");
+        open_model(model_dir, manifest.artifact);
+        try {
+            backend.validate_format(experts_.format());
+            manifest.validate_loaded(experts_.format(), dense_.file_size());
+        } catch (...) {
+            dense_.close();
+            experts_.close();
+            model_dir_.clear();
+            throw;
+        }
     }
 
     const std::string& model_dir() const noexcept { return model_dir_; }
@@ -1012,53 +1344,88 @@ inline void dispatch_expert_permutation(aeon_b200_ctx* ctx, const int* topk_indi
 // ---------------------------------------------------------------------------------------------
 // The executor seam and its B200 implementation.
 // ---------------------------------------------------------------------------------------------
+// 16-bit activation element (fp16 or bf16 bits, as the configuration's act_dtype says): the
+// reference's `half`. The accumulator is fp32 here where the reference's is fp16; that and
+// hipStream_t -> a stream handle are the only type differences of the seam
+// (src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:32-112).
+using act16 = uint16_t;
+
 class V4RoutedExpertExecutor {
 public:
     virtual ~V4RoutedExpertExecutor() = default;
-    virtual void on_routing_ready(uint32_t, uint32_t, const std::vector<int32_t>&, const std::vector<float>&) {}
+    virtual void on_routing_ready(uint32_t layer_id, uint32_t position, const std::vector<int32_t>& ids,
+                                  const std::vector<float>& weights) {
+        (void)layer_id; (void)position; (void)ids; (void)weights;
+    }
+    // A layer-wide dispatch; the default is the per-token sequence.
     virtual void on_routing_ready_batch(uint32_t layer_id, uint32_t first_position,
                                         const std::vector<std::vector<int32_t>>& ids,
                                         const std::vector<std::vector<float>>& weights) {
         for (size_t i = 0; i < ids.size(); ++i)
             on_routing_ready(layer_id, first_position + static_cast<uint32_t>(i), ids[i], weights[i]);
     }
-    // moe_accum (fp32 here, fp16 in the reference) holds the shared expert's output on entry.
-    virtual void accumulate_routed(uint32_t layer_id, uint32_t position, const void* expert_input,
-                                   const int* expert_ids, const float* expert_weights, float* moe_accum) = 0;
+    // moe_accum += sum_k w_k * W2_k * clamped_swiglu(W1_k x, W3_k x); it holds the shared expert's
+    // output on entry. The routed ids are the ones the matching on_routing_ready announced.
+    virtual void accumulate_routed(uint32_t layer_id, uint32_t position, const act16* expert_input,
+                                   const float* expert_weights, float* moe_accum) = 0;
+    // The chunk-wide form; the default is the per-token sequence, so token_count == 1 reproduces
+    // accumulate_routed.
     virtual void accumulate_routed_batch(uint32_t layer_id, uint32_t first_position, uint32_t token_count,
-                                         const void* batch_input, int input_stride, const int* batch_ids,
+                                         const act16* batch_input, int input_stride, const int* batch_ids,
                                          int ids_stride, const float* batch_weights, int weights_stride,
-                                         float* batch_output, int output_stride) = 0;
-    virtual void on_routed_consumed(uint32_t, uint32_t) {}
+                                         float* batch_output, int output_stride) {
+        (void)batch_ids; (void)ids_stride;
+        for (uint32_t token = 0; token < token_count; ++token)
+            accumulate_routed(layer_id, first_position + token, batch_input + static_cast<size_t>(token) * input_stride,
+                              batch_weights + static_cast<size_t>(token) * weights_stride,
+                              batch_output + static_cast<size_t>(token) * output_stride);
+    }
+    virtual void on_routed_consumed(uint32_t layer_id, uint32_t position) { (void)layer_id; (void)position; }
 };
 
-// Borrows pool, registry and (optionally) the expert container; owns its context and the
-// device copy of the layer's slot table. Misses are served by uploading the payload from the
-// container into the slot the registry hands out (HBM-first: with every expert resident each
-// request is a hot hit and nothing is copied). Decode-sized chunks go to the streaming
-// kernels, larger ones to the grouped tcgen05 path.
+// Borrows pool, registry and (optionally) the expert container; owns its context, the device
+// copies of the layer's slot table and routed ids, and the staging of the miss path. HBM-first:
+// with every expert resident each request is a hot hit and nothing is copied. Otherwise the
+// layer's misses are deduplicated, then submitted together: each payload goes from the
+// memory-mapped container through one of a ring of pinned staging buffers to its pool slot on the
+// cold-upload stream, ordered after the compute work that may still read the evicted expert,
+// and the compute stream waits on one event for the whole set -- the shape of the reference's
+// tiered supply (src/architecture/deepseek_v4/moe/v4_expert_supply.hpp:202-258,
+// src/infrastructure/expert/transport/tiered_expert_supply.hpp) without its host-RAM warm tier
+// and NVMe reader. Decode-sized chunks go to the streaming kernels, larger ones to the grouped
+// tcgen05 path.
 class V4TieredExpertExecutor final : public V4RoutedExpertExecutor, public ExpertLeaseHolder {
 public:
     static constexpr uint32_t kDecodeChunk = 128;
+    static constexpr uint32_t kStagingBuffers = 4;
 
+    // Every stream-ordered operation on one caller-supplied stream (uploads included).
     V4TieredExpertExecutor(const aeon_b200_moe_config& cfg, int device, uint32_t max_chunk,
                            UnifiedVRAMExpertPool& pool, ExpertRegistry& registry,
                            const AeonExpertContainer* container, void* compute_stream, uint32_t first_layer = 0)
         : cfg_(cfg), pool_(pool), registry_(registry), container_(container), stream_(compute_stream),
-          first_layer_(first_layer) {
-        if (registry_.vram_capacity == 0)
-            throw std::invalid_argument("V4TieredExpertExecutor: the VRAM expert pool has no slots");
-        if (registry_.experts_per_layer != static_cast<uint32_t>(cfg.experts))
-            throw std::invalid_argument("V4TieredExpertExecutor: registry and config disagree on the expert count");
-        check_status(aeon_b200_ctx_create(&cfg_, device, static_cast<int>(std::min(max_chunk, kDecodeChunk)), &ctx_));
-        device_ = device;
-        check_status(aeon_b200_pool_create(4096, 1, device, &d_slot_table_raw_));   // >= experts * 4 bytes
-        if (static_cast<size_t>(cfg.experts) * sizeof(int32_t) > 4096)
-            throw std::invalid_argument("V4TieredExpertExecutor: more than 1024 experts per layer");
+          upload_stream_(nullptr), first_layer_(first_layer) {
+        init(device, max_chunk);
+    }
+    // Kernels on streams.compute, miss uploads on streams.sdma_cold (asynchronous supply).
+    V4TieredExpertExecutor(const aeon_b200_moe_config& cfg, int device, uint32_t max_chunk,
+                           UnifiedVRAMExpertPool& pool, ExpertRegistry& registry,
+                           const AeonExpertContainer* container, const DeviceStreams& streams,
+                           uint32_t first_layer = 0)
+        : cfg_(cfg), pool_(pool), registry_(registry), container_(container), stream_(streams.compute),
+          upload_stream_(streams.sdma_cold), first_layer_(first_layer) {
+        init(device, max_chunk);
     }
     ~V4TieredExpertExecutor() override {
         if (ctx_) (void)aeon_b200_ctx_destroy(ctx_);
-        if (d_slot_table_raw_) (void)aeon_b200_pool_destroy(d_slot_table_raw_, device_);
+        if (d_slot_table_) (void)aeon_b200_device_free(d_slot_table_);
+        if (d_ids_) (void)aeon_b200_device_free(d_ids_);
+        for (Staging& st : staging_) {
+            if (st.pinned) (void)aeon_b200_host_free_pinned(st.pinned);
+            if (st.done) (void)aeon_b200_event_destroy(st.done);
+        }
+        if (compute_mark_) (void)aeon_b200_event_destroy(compute_mark_);
+        if (uploads_done_) (void)aeon_b200_event_destroy(uploads_done_);
     }
 
     void on_routing_ready(uint32_t layer_id, uint32_t position, const std::vector<int32_t>& ids,
@@ -1069,7 +1436,9 @@ public:
                                         " routed experts, got " + std::to_string(ids.size()));
         begin_dispatch(layer_id, position, 1);
         for (int32_t id : ids) request(layer_id, id);
+        submit_transfers();
         publish_slot_table(layer_id);
+        publish_ids(ids.data(), ids.size());
         batch_draws_ += ids.size();
     }
 
@@ -1079,45 +1448,61 @@ public:
         (void)weights;
         if (ids.empty())
             throw std::invalid_argument("V4TieredExpertExecutor: a layer-wide dispatch needs at least one token");
+        if (ids.size() > max_chunk_)
+            throw std::invalid_argument("V4TieredExpertExecutor: the dispatch exceeds the executor's chunk size");
         begin_dispatch(layer_id, first_position, static_cast<uint32_t>(ids.size()));
         std::vector<uint8_t> seen(registry_.experts_per_layer, 0);
-        for (const auto& row : ids)
+        flat_ids_.clear();
+        for (const auto& row : ids) {
+            if (row.size() != static_cast<size_t>(cfg_.top_k))
+                throw std::invalid_argument("V4TieredExpertExecutor: every token needs top_k routed experts");
             for (int32_t id : row) {
                 if (id < 0 || static_cast<uint32_t>(id) >= registry_.experts_per_layer)
                     throw std::out_of_range("V4TieredExpertExecutor: routed expert id out of range");
                 if (!seen[id]) { seen[id] = 1; request(layer_id, id); }   // the layer's union, once
+                flat_ids_.push_back(id);
                 ++batch_draws_;
             }
+        }
+        submit_transfers();
         publish_slot_table(layer_id);
+        publish_ids(flat_ids_.data(), flat_ids_.size());
     }
 
-    void accumulate_routed(uint32_t layer_id, uint32_t position, const void* expert_input, const int* expert_ids,
+    void accumulate_routed(uint32_t layer_id, uint32_t position, const act16* expert_input,
                            const float* expert_weights, float* moe_accum) override {
-        if (!dispatched_ || current_layer_ != layer_id)
-            throw std::logic_error("V4TieredExpertExecutor: accumulate_routed without a matching on_routing_ready");
-        if (position < first_position_ || position - first_position_ >= token_count_)
-            throw std::out_of_range("V4TieredExpertExecutor: token index past the batch's token count");
-        check_status(aeon_b200_moe_decode(ctx_, pool_.d_experts, slot_table(), expert_input, cfg_.hidden, expert_ids,
-                                          expert_weights, 1, moe_accum, cfg_.hidden, 0, stream_));
+        accumulate_routed(layer_id, position, expert_input,
+                          d_ids_ + static_cast<size_t>(checked_row(layer_id, position)) * cfg_.top_k, expert_weights,
+                          moe_accum);
+    }
+    // The same with the token's routed ids already on the device (no host round trip of the routing).
+    void accumulate_routed(uint32_t layer_id, uint32_t position, const act16* expert_input, const int* expert_ids_device,
+                           const float* expert_weights, float* moe_accum) {
+        (void)checked_row(layer_id, position);
+        check_status(aeon_b200_moe_decode(ctx_, pool_.d_experts, d_slot_table_, expert_input, cfg_.hidden,
+                                          expert_ids_device, expert_weights, 1, moe_accum, cfg_.hidden, 0, stream_));
     }
 
+    // batch_ids: the chunk's ids on the device, [token, top_k]; nullptr uses the ids the matching
+    // on_routing_ready_batch announced.
     void accumulate_routed_batch(uint32_t layer_id, uint32_t first_position, uint32_t token_count,
-                                 const void* batch_input, int input_stride, const int* batch_ids, int ids_stride,
+                                 const act16* batch_input, int input_stride, const int* batch_ids, int ids_stride,
                                  const float* batch_weights, int weights_stride, float* batch_output,
                                  int output_stride) override {
         if (token_count == 0) return;
         if (!dispatched_ || current_layer_ != layer_id || first_position != first_position_ ||
             token_count != token_count_)
             throw std::logic_error("V4TieredExpertExecutor: accumulate_routed_batch without a matching batch dispatch");
-        if (batch_ids == nullptr || ids_stride != cfg_.top_k || weights_stride != cfg_.top_k)
+        if ((batch_ids != nullptr && ids_stride != cfg_.top_k) || weights_stride != cfg_.top_k)
             throw std::invalid_argument("V4TieredExpertExecutor: batch ids and weights must be [token, top_k]");
+        const int* ids = batch_ids != nullptr ? batch_ids : d_ids_;
         if (token_count <= kDecodeChunk) {
-            check_status(aeon_b200_moe_decode(ctx_, pool_.d_experts, slot_table(), batch_input, input_stride,
-                                              batch_ids, batch_weights, static_cast<int>(token_count), batch_output,
+            check_status(aeon_b200_moe_decode(ctx_, pool_.d_experts, d_slot_table_, batch_input, input_stride, ids,
+                                              batch_weights, static_cast<int>(token_count), batch_output,
                                               output_stride, 0, stream_));
         } else {
-            check_status(aeon_b200_moe_prefill(ctx_, pool_.d_experts, slot_table(), batch_input, input_stride,
-                                               batch_ids, batch_weights, static_cast<int>(token_count), batch_output,
+            check_status(aeon_b200_moe_prefill(ctx_, pool_.d_experts, d_slot_table_, batch_input, input_stride, ids,
+                                               batch_weights, static_cast<int>(token_count), batch_output,
                                                output_stride, 0, stream_));
         }
     }
@@ -1129,11 +1514,46 @@ public:
     size_t outstanding_leases() const noexcept override { return leases_.size(); }
     uint64_t batch_draws() const noexcept { return batch_draws_; }
     uint64_t batch_distinct() const noexcept { return batch_distinct_; }
+    uint64_t uploads() const noexcept { return uploads_; }
     uint32_t last_dispatch_tokens() const noexcept { return token_count_; }
     aeon_b200_ctx* context() const noexcept { return ctx_; }
     void check_device() { check_status(aeon_b200_ctx_check(ctx_, stream_)); }
 
 private:
+    struct Staging {
+        void* pinned{nullptr};
+        void* done{nullptr};      // recorded after the buffer's last upload
+        bool in_flight{false};
+    };
+    struct Miss {
+        uint32_t slot, local_layer, expert;
+        uint64_t operation_id;
+    };
+
+    void init(int device, uint32_t max_chunk) {
+        if (registry_.vram_capacity == 0)
+            throw std::invalid_argument("V4TieredExpertExecutor: the VRAM expert pool has no slots");
+        if (registry_.experts_per_layer != static_cast<uint32_t>(cfg_.experts))
+            throw std::invalid_argument("V4TieredExpertExecutor: registry and config disagree on the expert count");
+        if (max_chunk == 0) throw std::invalid_argument("V4TieredExpertExecutor: the chunk size must be positive");
+        device_ = device;
+        max_chunk_ = max_chunk;
+        check_status(aeon_b200_ctx_create(&cfg_, device, static_cast<int>(std::min(max_chunk, kDecodeChunk)), &ctx_));
+        void* raw = nullptr;
+        check_status(aeon_b200_device_alloc(static_cast<uint64_t>(cfg_.experts) * sizeof(int32_t), device, &raw));
+        d_slot_table_ = static_cast<int32_t*>(raw);
+        check_status(aeon_b200_device_alloc(static_cast<uint64_t>(max_chunk) * cfg_.top_k * sizeof(int32_t), device, &raw));
+        d_ids_ = static_cast<int32_t*>(raw);
+        if (upload_stream_ != nullptr) {
+            DeviceScope scope(device);
+            for (Staging& st : staging_) {
+                check_status(aeon_b200_host_alloc_pinned(pool_.format().payload_bytes, &st.pinned));
+                check_status(aeon_b200_event_create(&st.done));
+            }
+            check_status(aeon_b200_event_create(&compute_mark_));
+            check_status(aeon_b200_event_create(&uploads_done_));
+        }
+    }
     void begin_dispatch(uint32_t layer_id, uint32_t first_position, uint32_t tokens) {
         if (layer_id < first_layer_ || layer_id - first_layer_ >= registry_.num_layers)
             throw std::out_of_range("V4TieredExpertExecutor: layer outside this stage");
@@ -1141,6 +1561,14 @@ private:
         first_position_ = first_position;
         token_count_ = tokens;
         dispatched_ = true;
+        misses_.clear();
+    }
+    uint32_t checked_row(uint32_t layer_id, uint32_t position) const {
+        if (!dispatched_ || current_layer_ != layer_id)
+            throw std::logic_error("V4TieredExpertExecutor: accumulate_routed without a matching on_routing_ready");
+        if (position < first_position_ || position - first_position_ >= token_count_)
+            throw std::out_of_range("V4TieredExpertExecutor: token index past the batch's token count");
+        return position - first_position_;
     }
     void request(uint32_t layer_id, int32_t expert) {
         if (expert < 0 || static_cast<uint32_t>(expert) >= registry_.experts_per_layer)
@@ -1155,37 +1583,128 @@ private:
                 leases_.pop_back();
                 throw std::logic_error("V4TieredExpertExecutor: a routed expert is not resident and no container was given");
             }
-            pool_.upload_from_host_expert(static_cast<uint32_t>(r.vram_slot),
-                                          container_->get_expert_data(local, static_cast<uint32_t>(expert)), stream_);
-            registry_.complete_request(r.operation_id);
+            misses_.push_back(Miss{static_cast<uint32_t>(r.vram_slot), local, static_cast<uint32_t>(expert), r.operation_id});
         }
+    }
+    // The dispatch's misses, together. Without an upload stream: stream-ordered copies on the compute
+    // stream. With one: pinned staging ring -> pool slot on the upload stream, which first waits for
+    // the compute work enqueued so far (it may still read an expert this dispatch evicts); the
+    // compute stream then waits for the whole set.
+    void submit_transfers() {
+        if (misses_.empty()) return;
+        const size_t bytes = pool_.format().payload_bytes;
+        if (upload_stream_ == nullptr) {
+            for (const Miss& m : misses_) {
+                pool_.upload_from_host_expert(m.slot, container_->get_expert_data(m.local_layer, m.expert), stream_);
+                registry_.complete_request(m.operation_id);
+            }
+        } else {
+            check_status(aeon_b200_event_record(compute_mark_, stream_));
+            check_status(aeon_b200_stream_wait_event(upload_stream_, compute_mark_));
+            for (const Miss& m : misses_) {
+                Staging& st = staging_[next_staging_];
+                next_staging_ = (next_staging_ + 1) % kStagingBuffers;
+                if (st.in_flight) check_status(aeon_b200_event_synchronize(st.done));   // its last upload has left
+                std::memcpy(st.pinned, container_->get_expert_data(m.local_layer, m.expert), bytes);
+                check_status(aeon_b200_copy_to_device_async(pool_.get_slot_base(m.slot), st.pinned, bytes, upload_stream_));
+                check_status(aeon_b200_event_record(st.done, upload_stream_));
+                st.in_flight = true;
+            }
+            check_status(aeon_b200_event_record(uploads_done_, upload_stream_));
+            check_status(aeon_b200_stream_wait_event(stream_, uploads_done_));
+            for (const Miss& m : misses_) registry_.complete_request(m.operation_id);
+        }
+        uploads_ += misses_.size();
+        misses_.clear();
     }
     void publish_slot_table(uint32_t layer_id) {
         host_table_ = registry_.layer_slot_table(layer_id - first_layer_);
-        // stream-ordered copy: the kernels that follow on the same stream read the new table
-        check_status(aeon_b200_pool_upload(d_slot_table_raw_, 4096, 0, padded_table(), stream_));
+        // stream-ordered copy from pageable memory (staged before the call returns): the kernels
+        // that follow on the same stream read the new table
+        check_status(aeon_b200_copy_to_device_async(d_slot_table_, host_table_.data(),
+                                                    host_table_.size() * sizeof(int32_t), stream_));
     }
-    const void* padded_table() {
-        staging_.assign(1024, -1);
-        std::copy(host_table_.begin(), host_table_.end(), staging_.begin());
-        return staging_.data();
+    void publish_ids(const int32_t* ids, size_t count) {
+        check_status(aeon_b200_copy_to_device_async(d_ids_, ids, count * sizeof(int32_t), stream_));
     }
-    const int32_t* slot_table() const { return static_cast<const int32_t*>(d_slot_table_raw_); }
 
     aeon_b200_moe_config cfg_;
     UnifiedVRAMExpertPool& pool_;
     ExpertRegistry& registry_;
     const AeonExpertContainer* container_;
     void* stream_;
+    void* upload_stream_;
     uint32_t first_layer_;
     aeon_b200_ctx* ctx_{nullptr};
-    void* d_slot_table_raw_{nullptr};
+    int32_t* d_slot_table_{nullptr};
+    int32_t* d_ids_{nullptr};
     int device_{0};
-    std::vector<int32_t> host_table_, staging_;
+    uint32_t max_chunk_{0};
+    Staging staging_[kStagingBuffers];
+    uint32_t next_staging_{0};
+    void* compute_mark_{nullptr};
+    void* uploads_done_{nullptr};
+    std::vector<Miss> misses_;
+    std::vector<int32_t> host_table_, flat_ids_;
     std::vector<uint32_t> leases_;
     uint32_t current_layer_{0}, first_position_{0}, token_count_{0};
     bool dispatched_{false};
-    uint64_t batch_draws_{0}, batch_distinct_{0};
+    uint64_t batch_draws_{0}, batch_distinct_{0}, uploads_{0};
+};
+
+// ---------------------------------------------------------------------------------------------
+// One rank's membership of a multi-GPU group: the communicator the reference plans as
+// TensorParallelGroup (MULTI_GPU_EXECUTION_PLAN.md:189-235), over the library's NCCL entry points.
+// One rank calls unique_id(), the bytes travel by any host channel, every rank constructs its
+// member with them (a collective call).
+// ---------------------------------------------------------------------------------------------
+class ParallelGroup {
+public:
+    using UniqueId = std::array<uint8_t, AEON_B200_GROUP_ID_BYTES>;
+
+    static UniqueId unique_id() {
+        UniqueId id{};
+        check_status(aeon_b200_group_unique_id(id.data()));
+        return id;
+    }
+    ParallelGroup(const UniqueId& id, int rank, int world, int device) {
+        check_status(aeon_b200_group_create(id.data(), rank, world, device, &group_));
+    }
+    ~ParallelGroup() {
+        if (group_) (void)aeon_b200_group_destroy(group_);
+    }
+    ParallelGroup(const ParallelGroup&) = delete;
+    ParallelGroup& operator=(const ParallelGroup&) = delete;
+
+    int rank() const noexcept { return aeon_b200_group_rank(group_); }
+    int world() const noexcept { return aeon_b200_group_world(group_); }
+
+    // expert parallel: every rank's activation rows to every rank, rank order
+    void dispatch(const act16* x_local, int tokens_local, int hidden, act16* x_all, void* stream) {
+        check_status(aeon_b200_ep_dispatch(group_, x_local, tokens_local, static_cast<int64_t>(hidden) * 2, x_all, stream));
+    }
+    // expert parallel: partial rows to the ranks that own the tokens, then add in rank order
+    void exchange(const float* partial, int tokens_local, int hidden, float* recv, void* stream) {
+        check_status(aeon_b200_ep_exchange(group_, partial, tokens_local, hidden, recv, stream));
+    }
+    void combine(float* out, int64_t out_stride, const float* recv, int tokens_local, int hidden, void* stream) {
+        check_status(aeon_b200_ep_combine(out, out_stride, recv, world(), tokens_local, hidden, stream));
+    }
+    // tensor parallel: sum of the partial outputs, each rank keeps its tokens' rows
+    void reduce(const float* partial, int tokens_local, int hidden, float* out_local, void* stream) {
+        check_status(aeon_b200_tp_reduce(group_, partial, tokens_local, hidden, out_local, stream));
+    }
+    // pipeline: the stage hand-off
+    void send(const void* rows, uint64_t bytes, int peer, void* stream) {
+        check_status(aeon_b200_pp_send(group_, rows, bytes, peer, stream));
+    }
+    void recv(void* rows, uint64_t bytes, int peer, void* stream) {
+        check_status(aeon_b200_pp_recv(group_, rows, bytes, peer, stream));
+    }
+    aeon_b200_group* handle() const noexcept { return group_; }
+
+private:
+    aeon_b200_group* group_{nullptr};
 };
 
 }  // namespace aeon::core

@@ -2,7 +2,12 @@
 // than the catalog (8 slots for 32 experts, so misses, uploads and evictions all happen) must
 // give results bit-identical to the direct C-ABI call on a fully resident pool — the shape of
 // the reference's tests/test_v4_expert_executor.cpp:12-75 (tiered executor vs direct-payload
-// executor, 8-slot pool to force the drain path, wrong-expert probe must differ).
+// executor, 8-slot pool to force the drain path, wrong-expert probe must differ). The token
+// loop is the reference layer body's own sequence (src/architecture/deepseek_v4/layer/
+// v4_layer_body_moe.hpp:160-192,285-312): router ids read back to the host, on_routing_ready,
+// shared expert (here: a cleared accumulator), accumulate_routed(layer, pos, x, weights, accum),
+// on_routed_consumed. The same is then run with the miss uploads on their own stream
+// (DeviceContext / DeviceStreams) and must still be bit-identical.
 #include "aeon_b200_host.hpp"
 
 #include <cuda_runtime.h>
@@ -62,6 +67,14 @@ int main(int argc, char** argv) {
     AeonExpertContainer container;
     container.open(idx, exp, 2, format.payload_bytes);
 
+    select_device(0, false);
+    check("a device index that is not there is a named error",
+          throws<std::runtime_error>([&] { select_device(4096, false); }));
+    enable_peer_access({0}, false);                   // one device: nothing to enable, nothing to refuse
+    DeviceContext device_context = DeviceContext::create(0);
+    check("a device context carries four distinct streams",
+          device_context.streams.compute && device_context.streams.sdma && device_context.streams.sdma_cold &&
+              device_context.streams.demotion && device_context.streams.compute != device_context.streams.sdma_cold);
     cudaStream_t stream;
     CUDA_OK(cudaStreamCreate(&stream));
     UnifiedVRAMExpertPool small_pool(8, cfg, format), full_pool(E, cfg, format);
@@ -107,7 +120,7 @@ int main(int argc, char** argv) {
         std::vector<float> wrow(w.begin() + t * K, w.begin() + (t + 1) * K);
         exec.on_routing_ready(0, t, row, wrow);
         CUDA_OK(cudaMemsetAsync(d_a + t * H, 0, H * 4, stream));
-        exec.accumulate_routed(0, t, d_x + t * H, d_ids + t * K, d_w + t * K, d_a + t * H);
+        exec.accumulate_routed(0, t, d_x + t * H, d_w + t * K, d_a + t * H);     // ids: the announced ones
         exec.on_routed_consumed(0, t);
         exec.check_device();
         exec.release_leases();       // token boundary
@@ -126,6 +139,34 @@ int main(int argc, char** argv) {
     check("the small pool really evicted", registry.evictions >= 4 && registry.cold_misses >= 12 && registry.hot_hits >= 2);
     check("leases are back to zero at the token boundary", exec.outstanding_leases() == 0);
 
+    // the same tokens with the miss uploads on their own stream, through pinned staging
+    {
+        ExpertRegistry async_registry(1, E, 8);
+        UnifiedVRAMExpertPool async_pool(8, cfg, format);
+        V4TieredExpertExecutor async_exec(cfg, 0, 8, async_pool, async_registry, &container, device_context.streams);
+        cudaStream_t cs = static_cast<cudaStream_t>(device_context.streams.compute);
+        CUDA_OK(cudaStreamSynchronize(stream));
+        bool ok = true;
+        for (int round = 0; round < 2; ++round)           // second round: slots evicted in the first come back
+            for (int t = 0; t < T; ++t) {
+                std::vector<int32_t> row(ids.begin() + t * K, ids.begin() + (t + 1) * K);
+                std::vector<float> wrow(w.begin() + t * K, w.begin() + (t + 1) * K);
+                async_exec.on_routing_ready(0, t, row, wrow);
+                CUDA_OK(cudaMemsetAsync(d_a + t * H, 0, H * 4, cs));
+                async_exec.accumulate_routed(0, t, d_x + t * H, d_w + t * K, d_a + t * H);
+                async_exec.on_routed_consumed(0, t);
+                async_exec.release_leases();
+                ok &= async_registry.invariants_hold();
+            }
+        async_exec.check_device();
+        CUDA_OK(cudaStreamSynchronize(cs));
+        CUDA_OK(cudaMemcpy(a.data(), d_a, a.size() * 4, cudaMemcpyDeviceToHost));
+        check("asynchronous supply (upload stream + pinned staging) == direct call, bit for bit",
+              ok && std::memcmp(a.data(), b.data(), a.size() * 4) == 0);
+        check("it uploaded through the staging ring more often than the ring is long",
+              async_exec.uploads() > V4TieredExpertExecutor::kStagingBuffers && async_registry.evictions >= 4);
+    }
+
     // chunk-wide dispatch: the layer's union is requested once
     registry.init(1, E, 16);
     UnifiedVRAMExpertPool mid_pool(16, cfg, format);
@@ -142,6 +183,32 @@ int main(int argc, char** argv) {
     batch_exec.check_device();
     fetch(d_a, a);
     check("chunk-wide dispatch == direct call, bit for bit", std::memcmp(a.data(), b.data(), a.size() * 4) == 0);
+    CUDA_OK(cudaMemsetAsync(d_a, 0, T * H * 4, stream));
+    batch_exec.accumulate_routed_batch(0, 10, T, d_x, H, nullptr, 0, d_w, K, d_a, H);   // the announced ids
+    batch_exec.check_device();
+    fetch(d_a, a);
+    check("chunk-wide consume with the announced ids == direct call, bit for bit",
+          std::memcmp(a.data(), b.data(), a.size() * 4) == 0);
+    {
+        // the seam's default bodies: an executor that only implements the per-token form
+        struct PerToken final : V4RoutedExpertExecutor {
+            V4TieredExpertExecutor& inner;
+            int calls{0};
+            explicit PerToken(V4TieredExpertExecutor& e) : inner(e) {}
+            void accumulate_routed(uint32_t layer, uint32_t pos, const act16* x, const float* weights,
+                                   float* accum) override {
+                ++calls;
+                inner.accumulate_routed(layer, pos, x, weights, accum);
+            }
+        } per_token(batch_exec);
+        CUDA_OK(cudaMemsetAsync(d_a, 0, T * H * 4, stream));
+        V4RoutedExpertExecutor& seam = per_token;
+        seam.accumulate_routed_batch(0, 10, T, d_x, H, nullptr, 0, d_w, K, d_a, H);
+        batch_exec.check_device();
+        fetch(d_a, a);
+        check("the default chunk body is the per-token sequence", per_token.calls == T &&
+                                                                      std::memcmp(a.data(), b.data(), a.size() * 4) == 0);
+    }
     check("the chunk issued one deduplicated set (18 draws -> 12 distinct experts)",
           batch_exec.batch_draws() == 18 && batch_exec.batch_distinct() == 12 && batch_exec.last_dispatch_tokens() == 3);
     check("a mismatched batch consume is a protocol error",
@@ -158,6 +225,7 @@ int main(int argc, char** argv) {
     check("wrong-expert probe goes red", std::memcmp(a.data(), b.data(), H * 4) != 0 &&
                                              std::memcmp(a.data() + H, b.data() + H, 2 * H * 4) == 0);
 
+    device_context.destroy();
     aeon_b200_ctx_destroy(direct);
     std::remove(idx.c_str()); std::remove(exp.c_str());
     std::printf("[executor on GPU] %s (%d failures)\n", g_fail == 0 ? "ALL PASS" : "FAILED", g_fail);

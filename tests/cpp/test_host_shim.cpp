@@ -7,6 +7,8 @@
 // version 3 of it with rank slices, and the dense container behind AeonModelLoader.
 #include "aeon_b200_host.hpp"
 
+#include <sstream>
+
 #include <cstdio>
 #include <cstdlib>
 #include <functional>
@@ -397,6 +399,69 @@ int main(int argc, char** argv) {
         const LoadedTensor& g = loader.get_tensor("layers.0.ffn.gate.weight");
         check("python-written artifact: gate tensor bytes", fnv(g.data, static_cast<size_t>(g.byte_size)) == gate_hash);
         check("python-written artifact: rank slice (tp 2, rank 1) offset", loader.rank_slice(0, 3, 2, 1).offset == slice_offset);
+
+        // the directory carries a manifest: the loader went through it (backend resolved and
+        // checked against the artifact first, loaded identity against the manifest last)
+        const std::string manifest_path = model_dir + "/model_manifest.json";
+        const AeonModelManifest manifest = AeonModelManifest::load_from_json(manifest_path);
+        check("manifest: identity, backend, catalog and shard degree",
+              manifest.weight_backend == "swizzled_w4a16" && !manifest.model_family.empty() &&
+                  !manifest.architecture.empty() && manifest.num_layers == 1 && manifest.experts_per_layer == 32 &&
+                  manifest.max_tensor_parallel == shard_count &&
+                  manifest.artifact.expected_expert_payload_bytes == payload_bytes &&
+                  manifest.dense_file_bytes == loader.dense().file_size());
+        std::ifstream in(manifest_path);
+        std::stringstream whole;
+        whole << in.rdbuf();
+        const std::string good = whole.str();
+        auto with = [&](const std::string& from, const std::string& to) {
+            std::string text = good;
+            const size_t at = text.find(from);
+            if (at == std::string::npos) return false;
+            text.replace(at, from.size(), to);
+            std::ofstream(manifest_path, std::ios::trunc) << text;
+            return true;
+        };
+        AeonModelLoader refused;
+        check("manifest: an unknown weight backend is refused before any file is opened",
+              with("\"weight_backend\": \"swizzled_w4a16\"", "\"weight_backend\": \"dense_fp8\"") &&
+                  throws<std::invalid_argument>([&] { refused.open_model(model_dir); }, "weight backend"));
+        check("manifest: a payload size the artifact does not have is refused",
+              with("\"expert_payload_bytes\": " + std::to_string(payload_bytes),
+                   "\"expert_payload_bytes\": " + std::to_string(payload_bytes + 4096)) &&
+                  throws<std::runtime_error>([&] { refused.open_model(model_dir); }));
+        check("manifest: a dense size that is not the file's is refused",
+              with("\"dense_file_bytes\": " + std::to_string(manifest.dense_file_bytes),
+                   "\"dense_file_bytes\": " + std::to_string(manifest.dense_file_bytes + 1)) &&
+                  throws<std::runtime_error>([&] { refused.open_model(model_dir); }, "dense file size"));
+        check("manifest: a missing key is refused",
+              with("\"model_family\"", "\"model_clan\"") &&
+                  throws<std::invalid_argument>([&] { refused.open_model(model_dir); }, "model_family"));
+        std::ofstream(manifest_path, std::ios::trunc) << good;
+        refused.open_model(model_dir);
+        check("manifest: restored, the directory opens again", refused.max_tensor_parallel() == shard_count);
+    }
+    // ---- backend registry ----
+    {
+        const aeon_b200_moe_config ref = moe_config_preset("ref_dsv4");
+        const ExpertFormatDescriptor f = make_swizzled_expert_format(ref, 43);
+        const ExpertBackendDescriptor& by_name = ExpertBackendRegistry::resolve("swizzled_w4a16");
+        check("backend registry: by name, by kind, with a format",
+              by_name.supports_fused_moe_experts && &ExpertBackendRegistry::resolve(ExpertFormatKind::SWIZZLED_W4A16) == &by_name &&
+                  &ExpertBackendRegistry::resolve("swizzled_w4a16", f) == &by_name && &ExpertBackendRegistry::resolve(f) == &by_name);
+        check("backend registry: unknown name refused",
+              throws<std::invalid_argument>([] { ExpertBackendRegistry::resolve("gguf_q4"); }, "unsupported weight backend"));
+        check("backend registry: unknown format kind refused",
+              throws<std::invalid_argument>([] { ExpertBackendRegistry::resolve(ExpertFormatKind::OPAQUE); }, "no backend"));
+        const ExpertBackendDescriptor bound = ExpertBackendRegistry::for_config(ref);
+        ExpertFormatDescriptor other = f;
+        other.payload_bytes += 4096;
+        check("backend bound to a layer shape refuses an artifact of another payload size",
+              bound.payload_bytes == 14155776u && throws<std::runtime_error>([&] { bound.validate_format(other); }, "incompatible"));
+        ExpertFormatDescriptor old_version = f;
+        old_version.version = 1;
+        check("backend refuses a format version it does not read",
+              throws<std::runtime_error>([&] { by_name.validate_format(old_version); }, "incompatible"));
     }
     // ---- format / presets through the C ABI ----
     {

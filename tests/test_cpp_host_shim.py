@@ -57,6 +57,11 @@ def test_host_shim(tmp_path):
     assert "ALL PASS" in r.stdout and "FAIL " not in r.stdout
 
 
+def test_integration_example_compiles_with_override(tmp_path):
+    """The executor of INTEGRATION.md overrides the seam's members as written (compile and link only)."""
+    build(os.path.join(ROOT, "tests", "cpp", "integration_example.cpp"), str(tmp_path / "integration_example"))
+
+
 import pytest
 
 

@@ -38,7 +38,9 @@ class TinyMoe:
     def shared(self, x, out):
         out.copy_(x @ self.sw.T)
 
-    def routed(self, x, ids, weights, out, skip_absent):
+    def routed(self, x, ids, weights, out, skip_absent, overwrite=False):
+        if overwrite:
+            out.zero_()
         for t in range(x.shape[0]):
             for s in range(K):
                 e = int(ids[t, s])
@@ -92,7 +94,9 @@ class TinyShardMoe(TinyMoe):
         super().__init__(range(E))
         self.lo, self.hi = lo, hi
 
-    def routed(self, x, ids, weights, out, skip_absent):
+    def routed(self, x, ids, weights, out, skip_absent, overwrite=False):
+        if overwrite:
+            out.zero_()
         lo, hi = self.lo, self.hi
         for t in range(x.shape[0]):
             for s in range(K):

@@ -172,3 +172,37 @@ def test_argument_validation():
     assert e.value.status == 1
     with pytest.raises(aeon_b200.AeonError):           # null pool
         ctx.moe_decode(0, layer.slot_of, x[:1], ids[:1], w[:1], out[:1])
+
+
+def test_group_128_at_hidden_4096_matches_oracle(oracle):
+    """The group-128 kernels at the reference model's hidden width (their second instance)."""
+    cfg = aeon_b200.preset("baseline").copy(hidden=4096)
+    resident = [3, 4, 5, 6, 9, 10, 11, 12, 13]
+    layer = gs.SyntheticLayer(cfg, resident, seed=2, layer=1, with_shared=False)
+    rng = np.random.default_rng(77)
+    tokens = 11                                        # one expert gets more than one work entry
+    ids, w = random_routing(rng, tokens, cfg.top_k, resident)
+    x_bits = gs.activations(cfg, tokens, seed=6)
+    got, _ = run_decode(cfg, layer, x_bits, ids, w)
+    want = gs.oracle_routed(oracle, layer, x_bits, ids, w.astype(np.float64), [0, 5, tokens - 1])
+    for t in (0, 5, tokens - 1):
+        gs.assert_close(oracle, want[t], got[t], f"hidden 4096 token {t}")
+
+
+def test_misaligned_accumulator_is_refused_on_the_host():
+    """A float4-misaligned accumulator or row stride is an argument error, never a device fault."""
+    import torch
+    cfg = aeon_b200.preset("baseline")
+    layer = gs.SyntheticLayer(cfg, [0, 1, 2, 3, 4, 5, 6, 7], seed=0, layer=0, with_shared=False)
+    ctx = aeon_b200.Context(cfg, max_tokens=2)
+    x = gs.torch_bits(gs.activations(cfg, 2, seed=0), cfg.act_dtype)
+    ids = torch.arange(8, dtype=torch.int32, device="cuda").repeat(2, 1).contiguous()
+    w = torch.full((2, 8), 0.125, dtype=torch.float32, device="cuda")
+    flat = torch.zeros(2 * (cfg.hidden + 2) + 1, dtype=torch.float32, device="cuda")
+    shifted = flat[1:1 + 2 * cfg.hidden].view(2, cfg.hidden)                    # 4 bytes off a 16-byte boundary
+    odd_stride = flat[:2 * (cfg.hidden + 2)].view(2, cfg.hidden + 2)[:, :cfg.hidden]   # stride not a multiple of 4
+    for bad in (shifted, odd_stride):
+        with pytest.raises(aeon_b200.AeonError) as e:
+            ctx.moe_decode(layer.pool.base, layer.slot_of, x, ids, w, bad)
+        assert e.value.status == 1
+    ctx.check()

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 LAYERS, TOKENS = 2, 32
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, peer_combine=False):
     import torch
     import torch.distributed as dist
     from aeon_b200 import stack, synth
@@ -30,7 +30,8 @@ def _worker(rank, world, port, results):
         tl = TOKENS // world
         x_local = x_all[:, rank * tl:(rank + 1) * tl].contiguous()
 
-        ep = stack.MoeStack(cfg, LAYERS, TOKENS, seed=3, device=rank, rank=rank, world=world, dist=dist)
+        ep = stack.MoeStack(cfg, LAYERS, TOKENS, seed=3, device=rank, rank=rank, world=world, dist=dist,
+                            peer_combine=peer_combine)
         out_ep = torch.empty(LAYERS, tl, cfg.hidden, dtype=torch.float32, device="cuda")
         routing_ep = [ep.forward_layer(l, x_local[l], out_ep[l], return_routing=True) for l in range(LAYERS)]
         ep.ctx.check()
@@ -38,6 +39,7 @@ def _worker(rank, world, port, results):
         ep.forward(x_local, again)
         torch.cuda.synchronize()
         reproducible = torch.equal(out_ep, again)
+        ep.close()
         del ep
         torch.cuda.empty_cache()
 
@@ -64,14 +66,17 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("peer_combine", [False, True], ids=["nccl-combine", "peer-combine"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_expert_parallel_matches_single_gpu(world):
+def test_expert_parallel_matches_single_gpu(world, peer_combine):
+    """peer_combine: the combine fused with the accumulate over CUDA-IPC mapped receive buffers
+    (plain peer stores + one flag per rank) instead of the all-to-all collective."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     results = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), results, peer_combine), nprocs=world, join=True)
     for rank in range(world):
         ids_equal, max_abs, rel_l2, reproducible = results[rank]
         assert ids_equal, "routing must be bit-identical on every rank"
