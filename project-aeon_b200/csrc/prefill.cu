@@ -19,7 +19,7 @@
 // warps changed nothing.) The fp32 accumulators live in tensor memory: two buffers of two
 // 128-column halves, so the epilogue of one tile overlaps the main loop of the next.
 //
-// Warp roles of a CTA (448 threads):
+// Warp roles of a CTA (480 threads):
 //   warps 0-3   epilogue: tcgen05.ld their TMEM lane quadrant of both halves, finish (SwiGLU /
 //               routing weight), store;
 //   warps 4-11  dequantise: one thread per weight row of the 256-row tile. Per k-block a thread
@@ -34,7 +34,8 @@
 //               (leaving out the stores, the conversion arithmetic, the activation loads or
 //               even the MMAs each changed the time by less than 15 %);
 //   warp 12     one thread issues the tiled TMA loads of the activation operand (no multicast);
-//   warp 13     one thread issues the MMAs and the commits; the warp owns the TMEM allocation.
+//   warps 13-14 one thread each issues the MMAs and the commits of one 128-row half; warp 13
+//               owns the TMEM allocation.
 // A 4-stage ring of (weight tile, activation tile) pairs connects them through mbarriers.
 // Every wait is bounded; a wait that runs out sets the context's error flag, after which all
 // waits fall through and the kernel ends (TMEM is always freed).
@@ -70,7 +71,9 @@ constexpr int kStages = 4;
 constexpr int kEpilogueWarps = 4;
 constexpr int kDequantWarps = kTileM / 32;            // one thread per weight row of the tile
 constexpr int kPrefetch = 4;         // k-blocks of packed weights a dequantising thread keeps in flight
-constexpr int kThreads = (kEpilogueWarps + kDequantWarps + 2) * 32;
+constexpr int kTmaWarp = kEpilogueWarps + kDequantWarps;
+constexpr int kMmaWarp0 = kTmaWarp + 1;       // one MMA-issuing warp per 128-row half
+constexpr int kThreads = (kMmaWarp0 + kHalves) * 32;
 constexpr int kHalfA = kHalfM * kTileK * 2;           // 16 KB: one half's operand tile
 constexpr int kStageA = kHalves * kHalfA;             // 32 KB
 constexpr int kStageB = kMaxN * kTileK * 2;           // 16 KB
@@ -98,7 +101,6 @@ struct PrefillParams {
     float* contrib;       // [draws, H] fp32
     float limit;
     int32_t* error;
-    int tune;             // development builds: how the dequantising warps wait for a free stage
     // extents for the bounds-checked build
     int draws_cap;        // rows of hidden / contrib, entries of draw_idx / wpos
     int tiles_cap;        // tiles
@@ -153,15 +155,15 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             ptx::mbar_init(full_bar + 8 * s, kDequantWarps + 1);
-            ptx::mbar_init(empty_bar + 8 * s, 1);
+            ptx::mbar_init(empty_bar + 8 * s, kHalves);      // one commit per MMA-issuing thread
         }
         for (int b = 0; b < 2; ++b) {
-            ptx::mbar_init(acc_full + 8 * b, 1);
+            ptx::mbar_init(acc_full + 8 * b, kHalves);
             ptx::mbar_init(acc_empty + 8 * b, kEpilogueWarps);
         }
         ptx::fence_barrier_init();
     }
-    if (warp == kEpilogueWarps + kDequantWarps + 1) {
+    if (warp == kMmaWarp0) {
         tc5::tmem_alloc(tmem_slot, kTmemCols);
         tc5::tmem_relinquish();
     }
@@ -176,28 +178,43 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     const int n_tiles = index_ok(*p.n_tiles, p.tiles_cap + 1, p.error) ? *p.n_tiles : 0;
     const int total_items = n_tiles * row_blocks;
 
-    if (warp == kEpilogueWarps + kDequantWarps) {
+    if (warp == kTmaWarp) {
         // ------------------------------ TMA: activation operand ------------------------------
         if (lane == 0) {
-            uint32_t n = 0;
+            const int rounds = kblocks / kStages;
+            uint32_t phase = 0;
             for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
                 const PrefillTile tile = p.tiles[item / row_blocks];
-                const int boxes = (tile.ntok + 63) / 64;
-                for (int kb = 0; kb < kblocks; ++kb, ++n) {
-                    const int s = n % kStages;
-                    const uint32_t parity = (n / kStages) & 1;
-                    if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
-                    ptx::mbar_arrive_expect_tx(full_bar + 8 * s, boxes * 64 * kTileK * 2);
-                    for (int b = 0; b < boxes; ++b)
-                        tc5::tma_load_2d(b_smem + s * kStageB + b * (64 * kTileK * 2), &act_map,
-                                         kb * kTileK, tile.pos0 + b * 64, full_bar + 8 * s);
+                const bool two_boxes = tile.ntok > 64;                  // a box is 64 token rows
+                const uint32_t bytes = (two_boxes ? 2 : 1) * 64 * kTileK * 2;
+                for (int j = 0; j < rounds; ++j) {
+#pragma unroll
+                    for (int i = 0; i < kStages; ++i) {
+                        const int k0 = (j * kStages + i) * kTileK;
+                        if (!ptx::mbar_wait(empty_bar + 8 * i, phase ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
+                        ptx::mbar_arrive_expect_tx(full_bar + 8 * i, bytes);
+                        tc5::tma_load_2d(b_smem + i * kStageB, &act_map, k0, tile.pos0, full_bar + 8 * i);
+                        if (two_boxes)
+                            tc5::tma_load_2d(b_smem + i * kStageB + 64 * kTileK * 2, &act_map, k0, tile.pos0 + 64,
+                                             full_bar + 8 * i);
+                    }
+                    phase ^= 1;
                 }
             }
         }
-    } else if (warp == kEpilogueWarps + kDequantWarps + 1) {
+    } else if (warp >= kMmaWarp0) {
         // ------------------------------ MMA issue ---------------------------------------------
+        // One thread per 128-row half, each with its own accumulator columns. A single thread
+        // issuing both halves was the kernel's limit: per k-block it ran eight MMAs plus sixteen
+        // descriptor constructions and the ring arithmetic as one serial instruction stream,
+        // about 1,100 cycles against 320 of tensor time. Here the round over the ring is unrolled,
+        // so a descriptor is the base descriptor plus a constant, and each thread issues four MMAs.
+        const int h = warp - kMmaWarp0;
         if (lane == 0) {
-            uint32_t n = 0, it = 0;
+            const uint64_t a_desc0 = tc5::smem_desc_sw128(a_smem + h * kHalfA);
+            const uint64_t b_desc0 = tc5::smem_desc_sw128(b_smem);
+            const int rounds = kblocks / kStages;
+            uint32_t phase = 0, it = 0;
             for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
                 const PrefillTile tile = p.tiles[item / row_blocks];
                 const uint32_t n_mma = static_cast<uint32_t>((tile.ntok + 15) & ~15);
@@ -206,25 +223,24 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
                 if (!ptx::mbar_wait(acc_empty + 8 * buf, ((it >> 1) & 1) ^ 1, p.error))
                     flag_error(p.error, kErrWaitTimeout);
                 tc5::fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * (kHalves * kMaxN);
-                for (int kb = 0; kb < kblocks; ++kb, ++n) {
-                    const int s = n % kStages;
-                    const uint32_t parity = (n / kStages) & 1;
-                    if (!ptx::mbar_wait(full_bar + 8 * s, parity, p.error)) flag_error(p.error, kErrWaitTimeout);
-                    tc5::fence_after_sync();
-                    const uint32_t a_addr = a_smem + s * kStageA;
-                    const uint32_t b_addr = b_smem + s * kStageB;
+                const uint32_t d_tmem = tmem_base + buf * (kHalves * kMaxN) + h * kMaxN;
+                for (int j = 0; j < rounds; ++j) {
 #pragma unroll
-                    for (int h = 0; h < kHalves; ++h)
+                    for (int i = 0; i < kStages; ++i) {
+                        if (!ptx::mbar_wait(full_bar + 8 * i, phase, p.error)) flag_error(p.error, kErrWaitTimeout);
+                        tc5::fence_after_sync();
 #pragma unroll
                         for (int kk = 0; kk < kTileK / 16; ++kk) {
-                            tc5::mma_f16_ss(d_tmem + h * kMaxN, tc5::smem_desc_sw128(a_addr + h * kHalfA + kk * 32),
-                                            tc5::smem_desc_sw128(b_addr + kk * 32), idesc,
-                                            (kb > 0 || kk > 0) ? 1u : 0u);
+                            // the start-address field counts 16-byte units: adding a byte offset >> 4 moves the tile
+                            tc5::mma_f16_ss(d_tmem, a_desc0 + ((i * kStageA + kk * 32) >> 4),
+                                            b_desc0 + ((i * kStageB + kk * 32) >> 4), idesc,
+                                            (i == 0 && kk == 0) ? (j != 0 ? 1u : 0u) : 1u);
                         }
-                    tc5::commit(empty_bar + 8 * s);      // stage free when these MMAs are done
+                        tc5::commit(empty_bar + 8 * i);      // this half is done with the stage
+                    }
+                    phase ^= 1;
                 }
-                tc5::commit(acc_full + 8 * buf);         // accumulator complete
+                tc5::commit(acc_full + 8 * buf);             // this half's accumulator is complete
             }
         }
     } else if (warp >= kEpilogueWarps) {
@@ -300,22 +316,6 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
                     } else {
                         s2a = s2b = sraw * 0x10001u;
                     }
-#ifdef AEON_B200_TUNING
-                    if (p.tune == 1 || p.tune == 3) {          // one lane waits, the warp follows
-                        if (lane == 0) {
-                            if (p.tune == 3) {
-                                uint32_t spins = 0;
-                                while (!ptx::mbar_test_wait(empty_bar + 8 * i, phase ^ 1) && ++spins < (1u << 24)) {}
-                            } else if (!ptx::mbar_wait(empty_bar + 8 * i, phase ^ 1, p.error)) {
-                                flag_error(p.error, kErrWaitTimeout);
-                            }
-                        }
-                        __syncwarp();
-                    } else if (p.tune == 2) {                  // every lane probes without suspending
-                        uint32_t spins = 0;
-                        while (!ptx::mbar_test_wait(empty_bar + 8 * i, phase ^ 1) && ++spins < (1u << 24)) {}
-                    } else
-#endif
                     if (!ptx::mbar_wait(empty_bar + 8 * i, phase ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
                     uint8_t* dst = row_dst + i * kStageA;
                     *reinterpret_cast<uint4*>(dst + ((0u << 4) ^ swz)) = dequant_word(q0.x, s2a);
@@ -398,7 +398,7 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
 
     tc5::fence_before_sync();
     __syncthreads();
-    if (warp == kEpilogueWarps + kDequantWarps + 1) {
+    if (warp == kMmaWarp0) {
         tc5::fence_after_sync();
         tc5::tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -610,10 +610,7 @@ void launch_moe_prefill(aeon_b200_ctx* ctx, const void* pool_base, const int32_t
     p.error = ctx->d_error;
     p.draws_cap = tokens * cfg.top_k;
     p.tiles_cap = tiles_cap;
-#ifdef AEON_B200_TUNING
-    static const int tune_p = getenv("AEON_B200_TUNE_P") ? atoi(getenv("AEON_B200_TUNE_P")) : 0;
-    p.tune = tune_p;
-#endif
+
 
     cudaEvent_t* ev = nullptr;
     if (ctx->timing_enabled) {

@@ -54,21 +54,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Non-blocking probe of a phase (mbarrier.test_wait never suspends the thread).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
 // Bounded wait. Returns false when the iteration budget ran out, or at once when
 // `error_flag` is already set: after the first failure every later wait of the launch falls
 // through, so the kernel keeps its barrier structure (nobody is left alone at a bar.sync)
