@@ -42,9 +42,9 @@ def ep_layer_forward_peer(ops, dist, world, x_local, out_local, x_all, group=Non
     token; `ops.combine_peer` waits for every rank's rows and adds them in rank order. One
     collective per layer instead of two, no local partial, no exchange kernel."""
     scope = {} if group is None else {"group": group}
+    ops.shared(x_local, out_local)        # needs the rank's own rows only: may run beside all that follows
     dist.all_gather_into_tensor(x_all, x_local, **scope)
     weights, ids = ops.router(x_all)
-    ops.shared(x_local, out_local)
     ops.routed_push(x_all, ids, weights, out_local, x_local.shape[0])
     ops.combine_peer(out_local)
     return weights, ids
@@ -59,9 +59,9 @@ def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv,
     collectives are `dist`'s (NCCL on GPUs; gloo in the CPU tests of the protocol).
     Returns the (replicated) routing of the whole batch."""
     scope = {} if group is None else {"group": group}          # the ranks of one pipeline stage
+    ops.shared(x_local, out_local)        # needs the rank's own rows only: may run beside all that follows
     dist.all_gather_into_tensor(x_all, x_local, **scope)        # dispatch
     weights, ids = ops.router(x_all)                            # replicated, identical inputs
-    ops.shared(x_local, out_local)
     ops.routed(x_all, ids, weights, partial, skip_absent=True, overwrite=True)   # writes, needs no zero fill
     if not recv.is_contiguous():
         raise ValueError("the receive buffer must be a dense [world, tokens_local, hidden] block")
@@ -184,20 +184,38 @@ def layer_body_moe(ctx, w, hc, res_mid, prefill: bool = False):
 class _DeviceOps:
     """The library's kernels behind the four calls ep_layer_forward needs."""
 
-    def __init__(self, ctx, w):
+    def __init__(self, ctx, w, side=None):
         self.ctx, self.w = ctx, w
+        # side = (stream, fork event, join event): the shared expert then runs on that stream,
+        # and the combine, the first reader of what it wrote, waits for it
+        self.side = side
 
     def router(self, x):
         return self.ctx.router_topk(x, self.w.gate)
 
     def shared(self, x, out):
-        self.ctx.shared_expert(self.w.shared[0], self.w.shared[1], self.w.shared[2], x, out)
+        if self.side is None:
+            self.ctx.shared_expert(self.w.shared[0], self.w.shared[1], self.w.shared[2], x, out)
+            return
+        import torch
+        stream, fork, join = self.side
+        fork.record(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            stream.wait_event(fork)
+            self.ctx.shared_expert(self.w.shared[0], self.w.shared[1], self.w.shared[2], x, out)
+            join.record(stream)
+
+    def _join_shared(self):
+        if self.side is not None:
+            import torch
+            torch.cuda.current_stream().wait_event(self.side[2])
 
     def routed(self, x, ids, weights, out, skip_absent, overwrite=False):
         self.ctx.moe_decode(self.w.pool.base, self.w.slot_of, x, ids, weights, out,
                             skip_absent=skip_absent, overwrite=overwrite)
 
     def combine(self, out, recv):
+        self._join_shared()
         aeon_b200.ep_combine(out, recv)
 
     # -- the peer-memory form of the combine -------------------------------------------------------
@@ -209,6 +227,7 @@ class _DeviceOps:
         self.peer.push(self.ctx, self.w.slot_of, ids, tokens_local)
 
     def combine_peer(self, out):
+        self._join_shared()
         self.peer.combine(self.ctx, out)
 
 
@@ -400,7 +419,8 @@ class MoeStack:
     def forward_layer(self, l: int, x, out, collect_stats: bool = False, return_routing: bool = False):
         w = self.weights[l]
         ctx = self.ctx
-        ops = _DeviceOps(ctx, w)
+        ops = _DeviceOps(ctx, w, (self._side, self._fork, self._join)
+                         if self.world > 1 and self.overlap_shared else None)
         if self.world == 1 and not self.overlap_shared:
             ops.shared(x, out)
             weights, ids = ops.router(x)

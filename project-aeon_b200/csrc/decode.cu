@@ -42,7 +42,6 @@
 #include "ptx.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 
 namespace aeon_b200 {
 
@@ -1424,43 +1423,6 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     p.entries_cap = cfg.experts + p.draws_cap / 8 + 1;
 
     // Kernel instances: K-warps x chunks-per-warp x 128 columns = hidden.
-#ifdef AEON_B200_TUNING
-    // Development builds only: kernel geometries selectable at run time for A/B timing sweeps.
-    static const int tune_a = getenv("AEON_B200_TUNE_A") ? atoi(getenv("AEON_B200_TUNE_A")) : 0;
-    static const int tune_b = getenv("AEON_B200_TUNE_B") ? atoi(getenv("AEON_B200_TUNE_B")) : 0;
-    if (cfg.group_size == 128 && cfg.hidden == 7168 && cfg.intermediate == 2048 && (tune_a || tune_b)) {
-        auto ka = moe_w13_rows_kernel<8, 4, 28>;
-        int ta = GeomRowsA<8, 4, 28>::kThreads, sa = GeomRowsA<8, 4, 28>::kSmem;
-        auto kb = moe_w2_rows_kernel<16, 2, 2, 16>;
-        int tb = GeomRowsB<16, 2, 2, 16>::kThreads, sb = GeomRowsB<16, 2, 2, 16>::kSmem;
-#define PICK_A(K, ...) { ka = K; using GG = __VA_ARGS__; ta = GG::kThreads; sa = GG::kSmem; }
-#define PICK_B(K, ...) { kb = K; using GG = __VA_ARGS__; tb = GG::kThreads; sb = GG::kSmem; }
-        switch (tune_a) {
-            case 0: break;
-            case 5: PICK_A((moe_w13_rows_kernel<16, 2, 28>), GeomRowsA<16, 2, 28>); break;
-            case 6: PICK_A((moe_w13_rows_kernel<12, 2, 28>), GeomRowsA<12, 2, 28>); break;
-            case 7: PICK_A((moe_w13_rows_kernel<8, 4, 28>), GeomRowsA<8, 4, 28>); break;
-            case 8: PICK_A((moe_w13_rows_kernel<8, 2, 28>), GeomRowsA<8, 2, 28>); break;
-            case 9: PICK_A((moe_w13_rows_kernel<16, 1, 28>), GeomRowsA<16, 1, 28>); break;
-            default: throw StatusError(AEON_B200_ERR_UNSUPPORTED, "unknown tuning selection A");
-        }
-        switch (tune_b) {
-            case 0: break;
-            case 1: PICK_B((moe_w2_rows_kernel<16, 1, 4, 16>), GeomRowsB<16, 1, 4, 16>); break;
-            case 2: PICK_B((moe_w2_rows_kernel<12, 2, 2, 16>), GeomRowsB<12, 2, 2, 16>); break;
-            case 3: PICK_B((moe_w2_rows_kernel<12, 2, 4, 16>), GeomRowsB<12, 2, 4, 16>); break;
-            case 4: PICK_B((moe_w2_rows_kernel<12, 1, 4, 16>), GeomRowsB<12, 1, 4, 16>); break;
-            case 5: PICK_B((moe_w2_rows_kernel<16, 1, 2, 16>), GeomRowsB<16, 1, 2, 16>); break;
-            case 6: PICK_B((moe_w2_rows_kernel<8, 2, 4, 16>), GeomRowsB<8, 2, 4, 16>); break;
-            case 7: PICK_B((moe_w2_rows_kernel<8, 2, 8, 16>), GeomRowsB<8, 2, 8, 16>); break;
-            default: throw StatusError(AEON_B200_ERR_UNSUPPORTED, "unknown tuning selection B");
-        }
-#undef PICK_A
-#undef PICK_B
-        launch_pair(ctx, p, ka, ta, sa, kb, tb, sb, 1, stream);
-        return;
-    }
-#endif
     // Group 128: the row-streaming kernels. Kernel A: eight warps (two per scheduler, no register
     // cap in the way) with a four-step ring, 128 KB of weights in flight per SM; kernel B: sixteen
     // warps of two tiles each with a two-chunk ring. Both chosen by timing the alternatives on

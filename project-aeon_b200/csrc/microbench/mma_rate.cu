@@ -5,7 +5,8 @@
 // rewritten (their contents are whatever shared memory holds: only the timing matters). Two forms:
 //   issue    all MMAs back to back, one commit at the end;
 //   commit   one commit per k-block, as in the pipelined kernel (nobody waits on them but the end).
-// Prints cycles per MMA and the fraction of the nominal rate (4096 MACs per cycle per SM).
+// and the A operand either in shared memory (a descriptor) or in tensor memory (128 lanes x 8
+// packed columns per MMA). Prints cycles per MMA and the fraction of the nominal rate (4096 MACs per cycle per SM).
 //   make -C project-aeon_b200/csrc microbench && project-aeon_b200/build/mma_rate
 #include <cuda_runtime.h>
 
@@ -22,7 +23,7 @@ constexpr int kStageA = 128 * 64 * 2;     // 16 KB
 constexpr int kStageB = 256 * 64 * 2;     // 32 KB
 
 __global__ void __launch_bounds__(128, 1)
-mma_rate_kernel(int n, int iters, int commit_each, int halves, long long* cycles, int* error) {
+mma_rate_kernel(int n, int iters, int commit_each, int halves, int a_in_tmem, long long* cycles, int* error) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem0 = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem0 - ptx::smem_u32(smem_raw));
@@ -57,10 +58,19 @@ mma_rate_kernel(int n, int iters, int commit_each, int halves, long long* cycles
 #pragma unroll
             for (int s = 0; s < kStages; ++s) {
                 for (int h = 0; h < halves; ++h) {
+                    if (a_in_tmem) {
+                        // A operand: 128 lanes x 8 columns per MMA (16 fp16 = 8 packed columns), kept in
+                        // the columns above the accumulator (N <= 128 in this mode)
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        tc5::mma_f16_ss(tmem + h * 256, a0 + ((s * kStageA + kk * 32) >> 4),
-                                        b0 + ((s * kStageB + kk * 32) >> 4), idesc, 1u);
+                        for (int kk = 0; kk < 4; ++kk)
+                            tc5::mma_f16_ts(tmem + h * 128, tmem + 256 + (s * 4 + kk) * 8,
+                                            b0 + ((s * kStageB + kk * 32) >> 4), idesc, 1u);
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk)
+                            tc5::mma_f16_ss(tmem + h * 256, a0 + ((s * kStageA + kk * 32) >> 4),
+                                            b0 + ((s * kStageB + kk * 32) >> 4), idesc, 1u);
+                    }
                 }
                 if (commit_each) tc5::commit(bar);
             }
@@ -99,13 +109,14 @@ int main() {
     const int smem = 1024 + kStages * (kStageA + kStageB) + 256;
     CHECK(cudaFuncSetAttribute(mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int iters = 2000;                    // x 4 k-blocks x 4 MMAs
+    for (int a_in_tmem = 0; a_in_tmem <= 1; ++a_in_tmem)
     for (int halves = 1; halves <= 2; ++halves)
         for (int commit_each = 0; commit_each <= 1; ++commit_each)
             for (int n : {32, 64, 96, 128, 192, 256}) {
-                if (halves == 2 && n > 256) continue;
+                if (a_in_tmem && n > 128) continue;      // the A columns sit above a 2 x 128-column accumulator
                 long long cycles = 0;
                 for (int rep = 0; rep < 2; ++rep) {
-                    mma_rate_kernel<<<sms, 128, smem>>>(n, iters, commit_each, halves, d_cycles, d_error);
+                    mma_rate_kernel<<<sms, 128, smem>>>(n, iters, commit_each, halves, a_in_tmem, d_cycles, d_error);
                     CHECK(cudaGetLastError());
                     CHECK(cudaDeviceSynchronize());
                 }
@@ -113,8 +124,8 @@ int main() {
                 const double mmas = static_cast<double>(iters) * kStages * 4 * halves;
                 const double per_mma = cycles / mmas;
                 const double ideal = 128.0 * n * 16 / 4096.0;
-                std::printf("%s  accumulators=%d  N=%3d : %7.1f cycles per MMA  (nominal %5.1f, %.2f of nominal rate)\n",
-                            commit_each ? "commit per k-block" : "issue only        ", halves, n, per_mma, ideal,
+                std::printf("A in %s  %s  accumulators=%d  N=%3d : %7.1f cycles per MMA  (nominal %5.1f, %.2f of nominal rate)\n",
+                            a_in_tmem ? "tensor memory" : "shared memory", commit_each ? "commit per k-block" : "issue only        ", halves, n, per_mma, ideal,
                             ideal / per_mma);
             }
     int flag = 0;

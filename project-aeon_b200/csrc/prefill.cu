@@ -55,7 +55,6 @@
 #include "tensor_map.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 #include <type_traits>
 
 namespace aeon_b200 {
@@ -342,6 +341,20 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             const int ti = item / row_blocks;
             const int rb = item - ti * row_blocks;
             const PrefillTile tile = p.tiles[ti];
+            // GEMM 2: the tile's draw rows and routing weights do not depend on the accumulators, so they
+            // are fetched before the wait: lane j holds position 32 c + j of chunk c
+            int my_draw[kMaxN / 32];
+            float my_w[kMaxN / 32];
+            if constexpr (!kGateUp) {
+#pragma unroll
+                for (int c = 0; c < kMaxN / 32; ++c) {
+                    const int my_pos = tile.pos0 + c * 32 + lane;
+                    const bool have = c * 32 + lane < tile.ntok && index_ok(my_pos, p.draws_cap, p.error);
+                    my_draw[c] = have ? p.draw_idx[my_pos] : -1;
+                    my_w[c] = have ? p.wpos[my_pos] : 0.f;
+                    if (have && !index_ok(my_draw[c], p.draws_cap, p.error)) my_draw[c] = -1;
+                }
+            }
             const uint32_t buf = it & 1;
             if (!ptx::mbar_wait(acc_full + 8 * buf, (it >> 1) & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
             tc5::fence_after_sync();
@@ -370,21 +383,17 @@ moe_grouped_gemm_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             } else {
                 for (int h = 0; h < kHalves; ++h) {
                     const int row = rb * kTileM + h * kHalfM + quad * 32 + lane;
-                    for (int c0 = 0; c0 < tile.ntok; c0 += 32) {
+#pragma unroll
+                    for (int c = 0; c < kMaxN / 32; ++c) {
+                        if (c * 32 >= tile.ntok) break;
                         uint32_t v[32];
-                        tc5::ld_32x32(tlane + h * kMaxN + c0, v);
+                        tc5::ld_32x32(tlane + h * kMaxN + c * 32, v);
                         tc5::ld_wait();
-                        // the chunk's draw rows and routing weights: lane j reads position c0 + j once,
-                        // every lane then takes them by shuffle instead of 2 x 32 dependent loads
-                        const int my_pos = tile.pos0 + c0 + lane;
-                        const bool have = c0 + lane < tile.ntok && index_ok(my_pos, p.draws_cap, p.error);
-                        int my_draw = have ? p.draw_idx[my_pos] : -1;
-                        const float my_w = have ? p.wpos[my_pos] : 0.f;
-                        if (have && !index_ok(my_draw, p.draws_cap, p.error)) my_draw = -1;
+                        // every lane takes the chunk's draws and weights by shuffle instead of 2 x 32 dependent loads
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            const int draw = __shfl_sync(0xFFFFFFFFu, my_draw, j);
-                            const float wj = __shfl_sync(0xFFFFFFFFu, my_w, j);
+                            const int draw = __shfl_sync(0xFFFFFFFFu, my_draw[c], j);
+                            const float wj = __shfl_sync(0xFFFFFFFFu, my_w[c], j);
                             if (draw >= 0) p.contrib[static_cast<size_t>(draw) * p.H + row] = wj * __uint_as_float(v[j]);
                         }
                     }

@@ -78,6 +78,20 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
         : "memory");
 }
 
+// The same with the A operand in tensor memory (lane = row of A, K elements packed two 16-bit
+// values per 32-bit column), B in shared memory.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // The mbarrier gets one arrival when every MMA issued so far by this thread has finished
 // (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void commit(uint32_t mbar) {
