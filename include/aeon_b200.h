@@ -376,6 +376,16 @@ int aeon_b200_group_world(const aeon_b200_group* group);
  * (an all-gather; at decode sizes a padded all-to-all would move the same bytes). */
 int aeon_b200_ep_dispatch(aeon_b200_group* group, const void* x_local, int tokens_local,
                           int64_t row_bytes, void* x_all, void* stream);
+/* The dispatch for ranks that route their own tokens: besides the activation rows, every rank
+ * contributes the routing of its tokens_local tokens (ids_local / weights_local [tokens_local,
+ * top_k], from aeon_b200_router_topk on x_local) and receives the whole batch's routing in rank
+ * order. The router is a per-token function, so the gathered routing equals, bit for bit, what a
+ * router run on x_all returns; each rank computes 1 / world of it instead of all of it. The three
+ * gathers are one grouped NCCL call. */
+int aeon_b200_ep_dispatch_routed(aeon_b200_group* group, const void* x_local, int tokens_local,
+                                 int64_t row_bytes, void* x_all, const int32_t* ids_local,
+                                 const float* weights_local, int top_k, int32_t* ids_all,
+                                 float* weights_all, void* stream);
 /* Expert-parallel exchange: partial[world * tokens_local, hidden] holds this rank's partial
  * output rows for every token of the batch; rows [r * tokens_local, (r+1) * tokens_local) go to
  * rank r, whose recv[s, :, :] receives the slice computed by rank s (an equal-split all-to-all).
@@ -405,13 +415,24 @@ int aeon_b200_pp_recv(aeon_b200_group* group, void* rows, uint64_t bytes, int pe
  * slices to out[tokens_local, :] in rank order. A flag that does not arrive within the budget
  * (default 2 s) is reported by aeon_b200_ctx_check as TIMEOUT; the peer object is then out of
  * step and must be destroyed. Calls must alternate push / combine, once each per layer on every
- * rank, with the layer's dispatch (aeon_b200_ep_dispatch) between one layer's combine and the
- * next layer's push: that collective is what keeps a fast rank from overwriting rows a slow
- * owner still reads. No counterpart in the reference (no expert parallelism there); the
+ * rank, with the layer's dispatch (aeon_b200_ep_dispatch, aeon_b200_ep_dispatch_routed or
+ * aeon_b200_ep_peer_dispatch) between one layer's combine and the next layer's push: waiting for
+ * every rank's dispatch is what keeps a fast rank from overwriting rows a slow owner still reads. No counterpart in the reference (no expert parallelism there); the
  * summation order follows src/platform/ops/moe_accumulate.hpp:73-92. */
 typedef struct aeon_b200_ep_peer aeon_b200_ep_peer;
 int aeon_b200_ep_peer_create(aeon_b200_group* group, int device, int tokens_local_max, int hidden,
                              aeon_b200_ep_peer** out_host);
+/* The dispatch in the same form: stores this rank's tokens_local activation rows (16-bit
+ * elements, dense, 16-byte aligned) and the routing it computed for them (ids_local /
+ * weights_local [tokens_local, top_k]) into every rank's gather buffers, raises one flag per
+ * rank, and waits (bounded, as the combine does) for all ranks' rows. Returns this rank's gather
+ * buffers, valid once the call's work on `stream` is done: x_all[world * tokens_local, hidden],
+ * ids_all / weights_all[world * tokens_local, top_k], in rank order -- what
+ * aeon_b200_ep_dispatch_routed delivers, without a collective. The buffers belong to the peer
+ * object and are overwritten by the next dispatch. */
+int aeon_b200_ep_peer_dispatch(aeon_b200_ctx* ctx, aeon_b200_ep_peer* peer, const void* x_local,
+                               int tokens_local, const int32_t* ids_local, const float* weights_local,
+                               void** x_all, int32_t** ids_all, float** weights_all, void* stream);
 int aeon_b200_ep_peer_destroy(aeon_b200_ep_peer* peer);
 int aeon_b200_ep_peer_set_wait_budget(aeon_b200_ep_peer* peer, double milliseconds);
 int aeon_b200_moe_accumulate_push(aeon_b200_ctx* ctx, aeon_b200_ep_peer* peer, const int32_t* slot_of_expert,

@@ -40,7 +40,8 @@ EXPORTED_SYMBOLS = [
     "aeon_b200_expert_rank_slice", "aeon_b200_merge_expert_shards",
     "aeon_b200_hc_params_default", "aeon_b200_hc_ffn_front", "aeon_b200_hc_post",
     "aeon_b200_group_unique_id", "aeon_b200_group_create", "aeon_b200_group_destroy",
-    "aeon_b200_group_rank", "aeon_b200_group_world", "aeon_b200_ep_dispatch", "aeon_b200_ep_exchange",
+    "aeon_b200_group_rank", "aeon_b200_group_world", "aeon_b200_ep_dispatch", "aeon_b200_ep_dispatch_routed", "aeon_b200_ep_exchange",
+    "aeon_b200_ep_peer_dispatch",
     "aeon_b200_tp_reduce", "aeon_b200_pp_send", "aeon_b200_pp_recv",
     "aeon_b200_device_count", "aeon_b200_device_current", "aeon_b200_device_select",
     "aeon_b200_device_describe", "aeon_b200_device_enable_peer_access", "aeon_b200_device_alloc",
@@ -160,12 +161,16 @@ def lib() -> ctypes.CDLL:
     L.aeon_b200_ep_peer_set_wait_budget.argtypes = [c_void_p, ctypes.c_double]
     L.aeon_b200_moe_accumulate_push.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     L.aeon_b200_ep_peer_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]
+    L.aeon_b200_ep_peer_dispatch.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                             POINTER(c_void_p), POINTER(c_void_p), POINTER(c_void_p), c_void_p]
     L.aeon_b200_group_unique_id.argtypes = [c_void_p]
     L.aeon_b200_group_create.argtypes = [c_void_p, c_int, c_int, c_int, POINTER(c_void_p)]
     L.aeon_b200_group_destroy.argtypes = [c_void_p]
     L.aeon_b200_group_rank.argtypes = [c_void_p]
     L.aeon_b200_group_world.argtypes = [c_void_p]
     L.aeon_b200_ep_dispatch.argtypes = [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]
+    L.aeon_b200_ep_dispatch_routed.argtypes = [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p,
+                                               c_int, c_void_p, c_void_p, c_void_p]
     L.aeon_b200_ep_exchange.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     L.aeon_b200_tp_reduce.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     L.aeon_b200_pp_send.argtypes = [c_void_p, c_void_p, c_uint64, c_int, c_void_p]
@@ -555,6 +560,15 @@ class Group:
         check(lib().aeon_b200_ep_dispatch(self._h, _dense(x_local, "x_local"), x_local.shape[0], row_bytes,
                                           _dense(x_all, "x_all"), _stream()))
 
+    def ep_dispatch_routed(self, x_local, x_all, ids_local, weights_local, ids_all, weights_all) -> None:
+        """The dispatch plus the all-gather of the routing each rank computed for its own tokens."""
+        row_bytes = x_local.shape[1] * x_local.element_size()
+        check(lib().aeon_b200_ep_dispatch_routed(self._h, _dense(x_local, "x_local"), x_local.shape[0], row_bytes,
+                                                 _dense(x_all, "x_all"), _dense(ids_local, "ids_local"),
+                                                 _dense(weights_local, "weights_local"), ids_local.shape[1],
+                                                 _dense(ids_all, "ids_all"), _dense(weights_all, "weights_all"),
+                                                 _stream()))
+
     def ep_exchange(self, partial, recv) -> None:
         tl = partial.shape[0] // self.world
         check(lib().aeon_b200_ep_exchange(self._h, _dense(partial, "partial"), tl, partial.shape[1],
@@ -583,6 +597,19 @@ class Group:
                                       src, _stream()))
 
 
+class _DevicePointer:
+    """A device buffer owned by the library, seen through the CUDA array interface."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 2, "strides": None}
+
+
+def _device_view(ptr: int, shape, typestr: str, device):
+    import torch
+    return torch.as_tensor(_DevicePointer(ptr, shape, typestr), device=device)
+
+
 class PeerCombine:
     """Receive buffers of an expert-parallel group mapped between the ranks of one box (CUDA IPC),
     for the combine that is fused with the slot-order accumulate: push() is the second half of a
@@ -607,6 +634,26 @@ class PeerCombine:
 
     def set_wait_budget(self, milliseconds: float) -> None:
         check(lib().aeon_b200_ep_peer_set_wait_budget(self._h, float(milliseconds)))
+
+    def dispatch(self, ctx: Context, x_local, ids_local, weights_local):
+        """Peer-memory dispatch: returns (x_all, ids_all, weights_all), views of this rank's gather
+        buffers (overwritten by the next dispatch), filled once the stream reaches this point."""
+        import torch
+        tl, hidden = x_local.shape
+        k = ids_local.shape[1]
+        px, pi, pw = c_void_p(), c_void_p(), c_void_p()
+        check(lib().aeon_b200_ep_peer_dispatch(ctx._h, self._h, _dense(x_local, "x_local"), tl,
+                                               _dense(ids_local, "ids_local"), _dense(weights_local, "weights_local"),
+                                               ctypes.byref(px), ctypes.byref(pi), ctypes.byref(pw), _stream()))
+        key = (tl, hidden, k, x_local.dtype)
+        if getattr(self, "_views_key", None) != key:
+            tokens = tl * self.group.world
+            dev = x_local.device
+            x_all = _device_view(px.value, (tokens, hidden), "<i2", dev).view(x_local.dtype)
+            ids_all = _device_view(pi.value, (tokens, k), "<i4", dev)
+            weights_all = _device_view(pw.value, (tokens, k), "<f4", dev)
+            self._views, self._views_key = (x_all, ids_all, weights_all), key
+        return self._views
 
     def push(self, ctx: Context, slot_of_expert, ids, tokens_local: int) -> None:
         check(lib().aeon_b200_moe_accumulate_push(ctx._h, self._h, _dense(slot_of_expert, "slot_of_expert"),

@@ -35,22 +35,49 @@ def _torch_bits(bits: np.ndarray, dtype: int, device):
     return t.view(torch.bfloat16 if dtype == aeon_b200.BF16 else torch.float16)
 
 
-def ep_layer_forward_peer(ops, dist, world, x_local, out_local, x_all, group=None):
+def ep_dispatch_and_route(ops, dist, x_local, x_all, routing_all=None, group=None):
+    """Dispatch and routing of one expert-parallel layer. Without `routing_all` every rank gathers
+    the batch and runs the router on all of it (replicated, identical inputs). With routing_all =
+    (ids_all, weights_all) every rank routes its own tokens and the routing is gathered with the
+    rows: the router is a per-token function, so the result is the same bit for bit, and each
+    rank does 1 / world of the router's work. `dist.ep_dispatch_routed` (the library's group) does
+    the three gathers as one call; a plain torch.distributed module does them one by one."""
+    scope = {} if group is None else {"group": group}
+    if routing_all is None:
+        dist.all_gather_into_tensor(x_all, x_local, **scope)
+        return ops.router(x_all)
+    ids_all, weights_all = routing_all
+    weights_local, ids_local = ops.router(x_local)
+    fused = getattr(dist, "ep_dispatch_routed", None)
+    if fused is not None:
+        fused(x_local, x_all, ids_local, weights_local, ids_all, weights_all)
+    else:
+        dist.all_gather_into_tensor(x_all, x_local, **scope)
+        dist.all_gather_into_tensor(ids_all, ids_local.contiguous(), **scope)
+        dist.all_gather_into_tensor(weights_all, weights_local.contiguous(), **scope)
+    return weights_all, ids_all
+
+
+def ep_layer_forward_peer(ops, dist, world, x_local, out_local, x_all, group=None, routing_all=None):
     """The same layer with the combine fused into the accumulate over peer memory: after the
-    dispatch gather and the replicated router, `ops.routed_push` runs the resident experts and
+    dispatch and the routing, `ops.routed_push` runs the resident experts and
     stores each finished partial row straight into the receive buffer of the rank that owns the
     token; `ops.combine_peer` waits for every rank's rows and adds them in rank order. One
     collective per layer instead of two, no local partial, no exchange kernel."""
-    scope = {} if group is None else {"group": group}
     ops.shared(x_local, out_local)        # needs the rank's own rows only: may run beside all that follows
-    dist.all_gather_into_tensor(x_all, x_local, **scope)
-    weights, ids = ops.router(x_all)
+    if getattr(ops, "peer_dispatch", False):
+        # the dispatch over peer memory too: route the rank's own tokens, store rows and routing into
+        # every rank's gather buffers, wait for the others' (no collective in the layer)
+        weights_local, ids_local = ops.router(x_local)
+        x_all, ids, weights = ops.dispatch_peer(x_local, ids_local, weights_local)
+    else:
+        weights, ids = ep_dispatch_and_route(ops, dist, x_local, x_all, routing_all, group)
     ops.routed_push(x_all, ids, weights, out_local, x_local.shape[0])
     ops.combine_peer(out_local)
     return weights, ids
 
 
-def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv, group=None):
+def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv, group=None, routing_all=None):
     """One expert-parallel MoE layer on this rank (the protocol of the module docstring).
 
     `ops` supplies the compute: router(x) -> (weights, ids); shared(x, out) writes the shared
@@ -60,8 +87,7 @@ def ep_layer_forward(ops, dist, world, x_local, out_local, x_all, partial, recv,
     Returns the (replicated) routing of the whole batch."""
     scope = {} if group is None else {"group": group}          # the ranks of one pipeline stage
     ops.shared(x_local, out_local)        # needs the rank's own rows only: may run beside all that follows
-    dist.all_gather_into_tensor(x_all, x_local, **scope)        # dispatch
-    weights, ids = ops.router(x_all)                            # replicated, identical inputs
+    weights, ids = ep_dispatch_and_route(ops, dist, x_local, x_all, routing_all, group)
     ops.routed(x_all, ids, weights, partial, skip_absent=True, overwrite=True)   # writes, needs no zero fill
     if not recv.is_contiguous():
         raise ValueError("the receive buffer must be a dense [world, tokens_local, hidden] block")
@@ -218,8 +244,12 @@ class _DeviceOps:
         self._join_shared()
         aeon_b200.ep_combine(out, recv)
 
-    # -- the peer-memory form of the combine -------------------------------------------------------
+    # -- the peer-memory form of the combine (and of the dispatch) -----------------------------------
     peer = None
+    peer_dispatch = False
+
+    def dispatch_peer(self, x_local, ids_local, weights_local):
+        return self.peer.dispatch(self.ctx, x_local, ids_local, weights_local)
 
     def routed_push(self, x, ids, weights, scratch_out, tokens_local):
         self.ctx.moe_decode(self.w.pool.base, self.w.slot_of, x, ids, weights, scratch_out,
@@ -335,6 +365,8 @@ class MoeStack:
         self._stats = [dict(distinct=0, draws=0, tokens=0) for _ in range(layers)]
         self.group = None
         self.peer = None
+        # with peer_combine: the dispatch over peer memory as well (False: the grouped NCCL gather)
+        self.peer_dispatch = True
         if world > 1:
             H = cfg.hidden
             # the data-path collectives run on the library's own communicator (C ABI); `dist` only
@@ -342,6 +374,9 @@ class MoeStack:
             self.group = aeon_b200.Group.from_process_group(dist, device)
             self.x_all = torch.empty(max_tokens, H, dtype=self.weights[0].gate.dtype, device=dev)
             self.partial = torch.empty(max_tokens, H, dtype=torch.float32, device=dev)
+            # every rank routes its own tokens; the routing of the batch is gathered with the rows
+            self.ids_all = torch.empty(max_tokens, cfg.top_k, dtype=torch.int32, device=dev)
+            self.weights_all = torch.empty(max_tokens, cfg.top_k, dtype=torch.float32, device=dev)
             self.recv = torch.empty(world, max_tokens // world, H, dtype=torch.float32, device=dev)
             # peer_combine: the combine fused with the accumulate over CUDA-IPC mapped buffers
             self.peer = aeon_b200.PeerCombine(self.group, device, max_tokens // world, H) if peer_combine else None
@@ -446,9 +481,12 @@ class MoeStack:
         else:
             tl = x.shape[0]
             tokens_seen = tl * self.world
+            routing_all = (self.ids_all[:tokens_seen], self.weights_all[:tokens_seen])
             if self.peer is not None:
                 ops.peer = self.peer
-                weights, ids = ep_layer_forward_peer(ops, self.group, self.world, x, out, self.x_all[:tokens_seen])
+                ops.peer_dispatch = self.peer_dispatch
+                weights, ids = ep_layer_forward_peer(ops, self.group, self.world, x, out, self.x_all[:tokens_seen],
+                                                     routing_all=routing_all)
                 self._extra_launches += 1
                 if collect_stats:
                     distinct, _ = ctx.last_stats()
@@ -456,11 +494,11 @@ class MoeStack:
                     local = ((flat >= self.first_expert) &
                              (flat < self.first_expert + self.cfg.experts // self.world)).sum().item()
                     self._stats[l] = dict(distinct=distinct, draws=int(local), tokens=tokens_seen)
-                return (weights, ids) if return_routing else None
+                return (weights.clone(), ids.clone()) if return_routing else None    # the gather buffers are reused
             weights, ids = ep_layer_forward(ops, self.group, self.world, x, out,
                                             self.x_all[:tokens_seen], self.partial[:tokens_seen],
                                             self.recv.view(-1)[:tokens_seen * x.shape[1]]
-                                            .view(self.world, tl, x.shape[1]))
+                                            .view(self.world, tl, x.shape[1]), routing_all=routing_all)
             self._extra_launches += 2
         if collect_stats:
             distinct, _ = ctx.last_stats()
@@ -469,7 +507,7 @@ class MoeStack:
                      (flat < self.first_expert + self.cfg.experts // self.world)).sum().item()
             self._stats[l] = dict(distinct=distinct, draws=int(local), tokens=tokens_seen)
         if return_routing:
-            return weights, ids
+            return (weights.clone(), ids.clone()) if self.world > 1 else (weights, ids)
 
     # -- configuration-1 sweep: one layer at batch 1/8/32/128, rotating over the layers so
     #    consecutive iterations stream different weights (a batch-1 step touches ~180 MB,

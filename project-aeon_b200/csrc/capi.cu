@@ -195,6 +195,11 @@ void free_ctx_buffers(aeon_b200_ctx* c) {
     }
     delete c->guards;
     c->guards = nullptr;
+    if (c->aux_fork) (void)cudaEventDestroy(c->aux_fork);
+    if (c->aux_join) (void)cudaEventDestroy(c->aux_join);
+    if (c->aux_stream) (void)cudaStreamDestroy(c->aux_stream);
+    c->aux_fork = c->aux_join = nullptr;
+    c->aux_stream = nullptr;
 }
 
 }  // namespace
@@ -320,6 +325,9 @@ int aeon_b200_ctx_create(const aeon_b200_moe_config* cfg, int device, int max_to
             c->d_sh_lo = device_alloc<__half>(c, T * cfg->intermediate, total, "sh_lo");
             AEON_CUDA_CHECK(cudaMemset(c->d_error, 0, sizeof(int32_t)));
             AEON_CUDA_CHECK(cudaMemset(c->d_counts, 0, 4 * sizeof(int32_t)));
+            AEON_CUDA_CHECK(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
+            AEON_CUDA_CHECK(cudaEventCreateWithFlags(&c->aux_fork, cudaEventDisableTiming));
+            AEON_CUDA_CHECK(cudaEventCreateWithFlags(&c->aux_join, cudaEventDisableTiming));
             c->scratch_bytes = total;
         } catch (...) {
             free_ctx_buffers(c);

@@ -166,6 +166,10 @@ struct aeon_b200_ctx {
     __half* d_sh_mid;
     __half* d_sh_lo;
     void* shared_tc;        // split-K partial sums of the tensor-core form, allocated on first use
+
+    // the permutation of a decode call runs beside the activation staging on this stream
+    cudaStream_t aux_stream;
+    cudaEvent_t aux_fork, aux_join;
 };
 
 namespace aeon_b200 {

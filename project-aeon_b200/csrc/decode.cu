@@ -1367,7 +1367,18 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
             "aeon_b200_moe_decode: moe_accum must be 16-byte aligned and accum_stride a multiple of 4 "
             "(the accumulate uses 128-bit accesses)");
 
-    // 1. activations -> fp16 in kernel column order
+    // 1. draws sorted by expert + work list, on the context's own stream: it needs the routing only
+    //    and runs beside the staging of the activations (two short, latency-bound kernels). Under
+    //    stream capture the two events become graph edges.
+    AEON_CUDA_CHECK(cudaEventRecord(ctx->aux_fork, stream));
+    AEON_CUDA_CHECK(cudaStreamWaitEvent(ctx->aux_stream, ctx->aux_fork, 0));
+    launch_permutation(ctx, topk_ids, tokens, cfg.top_k, cfg.experts, ctx->d_offsets,
+                       ctx->d_token_idx, ctx->d_draw_idx, topk_weights, ctx->d_wpos,
+                       slot_of_expert, ctx->d_entries, ctx->d_counts,
+                       (flags & AEON_B200_DECODE_SKIP_ABSENT) != 0, ctx->aux_stream);
+    AEON_CUDA_CHECK(cudaEventRecord(ctx->aux_join, ctx->aux_stream));
+
+    // 2. activations -> fp16 in kernel column order
     const int64_t total = static_cast<int64_t>(tokens) * cfg.hidden;
     const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 4 * ctx->sm_count));
     if (cfg.group_size == 128) {
@@ -1382,11 +1393,7 @@ void launch_moe_decode(aeon_b200_ctx* ctx, const void* pool_base, const int32_t*
     AEON_CUDA_CHECK(cudaGetLastError());
     ctx->launches += 1;
 
-    // 2. draws sorted by expert + work list
-    launch_permutation(ctx, topk_ids, tokens, cfg.top_k, cfg.experts, ctx->d_offsets,
-                       ctx->d_token_idx, ctx->d_draw_idx, topk_weights, ctx->d_wpos,
-                       slot_of_expert, ctx->d_entries, ctx->d_counts,
-                       (flags & AEON_B200_DECODE_SKIP_ABSENT) != 0, stream);
+    AEON_CUDA_CHECK(cudaStreamWaitEvent(stream, ctx->aux_join, 0));
 
     // 3. the two streaming kernels
     DecodeParams p{};

@@ -167,6 +167,29 @@ int aeon_b200_ep_dispatch(aeon_b200_group* group, const void* x_local, int token
     });
 }
 
+int aeon_b200_ep_dispatch_routed(aeon_b200_group* group, const void* x_local, int tokens_local,
+                                 int64_t row_bytes, void* x_all, const int32_t* ids_local,
+                                 const float* weights_local, int top_k, int32_t* ids_all,
+                                 float* weights_all, void* stream) {
+    return guarded([&] {
+        require(group && x_local && x_all && ids_local && weights_local && ids_all && weights_all,
+                "aeon_b200_ep_dispatch_routed: null pointer");
+        require(tokens_local > 0 && row_bytes > 0 && top_k > 0, "aeon_b200_ep_dispatch_routed: empty rows");
+        DeviceScope scope(group->device);
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        const size_t draws = static_cast<size_t>(tokens_local) * top_k;
+        // one grouped call: the three gathers go out as a single launch
+        nccl_check(nccl().GroupStart(), "ncclGroupStart");
+        nccl_check(nccl().AllGather(x_local, x_all, static_cast<size_t>(tokens_local) * row_bytes, kNcclUint8,
+                                    group->comm, s), "ncclAllGather");
+        nccl_check(nccl().AllGather(ids_local, ids_all, draws * sizeof(int32_t), kNcclUint8, group->comm, s),
+                   "ncclAllGather");
+        nccl_check(nccl().AllGather(weights_local, weights_all, draws * sizeof(float), kNcclUint8, group->comm, s),
+                   "ncclAllGather");
+        nccl_check(nccl().GroupEnd(), "ncclGroupEnd");
+    });
+}
+
 int aeon_b200_ep_exchange(aeon_b200_group* group, const float* partial, int tokens_local, int hidden,
                           float* recv, void* stream) {
     return guarded([&] {

@@ -64,7 +64,7 @@ def single_rank(x):
     return out, ids
 
 
-def worker(rank, world, port, results):
+def worker(rank, world, port, results, sharded_routing=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -78,7 +78,11 @@ def worker(rank, world, port, results):
         x_all = torch.empty(T, H, dtype=torch.float64)
         partial = torch.empty(T, H, dtype=torch.float64)
         recv = torch.empty(world, tl, H, dtype=torch.float64)
-        w, ids = stack.ep_layer_forward(moe, dist, world, x_local, out_local, x_all, partial, recv)
+        # sharded_routing: every rank routes its own tokens and the routing is gathered with the rows
+        routing_all = (torch.empty(T, K, dtype=torch.int32), torch.empty(T, K, dtype=torch.float64)) \
+            if sharded_routing else None
+        w, ids = stack.ep_layer_forward(moe, dist, world, x_local, out_local, x_all, partial, recv,
+                                        routing_all=routing_all)
         want, want_ids = single_rank(x)
         ok_ids = torch.equal(ids, want_ids)
         err = (out_local - want[rank * tl:(rank + 1) * tl]).abs().max().item()
@@ -140,11 +144,12 @@ def free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("sharded_routing", [False, True])
 @pytest.mark.parametrize("world", [2, 4])
-def test_ep_protocol_matches_single_rank(world):
+def test_ep_protocol_matches_single_rank(world, sharded_routing):
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(worker, args=(world, free_port(), results), nprocs=world, join=True)
+    mp.spawn(worker, args=(world, free_port(), results, sharded_routing), nprocs=world, join=True)
     assert len(results) == world
     for rank in range(world):
         ok_ids, err, gathered = results[rank]

@@ -49,6 +49,18 @@ def _worker(rank, world, unique_id, results):
         want_sum = want_recv.double().sum(dim=0)
         ok["reduce"] = (out_local.double() - want_sum).abs().max().item() <= 1e-3
 
+        # dispatch with the routing each rank made for its own tokens (one grouped call)
+        ids_local = torch.full((TL, 8), rank, dtype=torch.int32, device="cuda")
+        w_local = torch.full((TL, 8), rank + 0.5, dtype=torch.float32, device="cuda")
+        ids_all = torch.zeros(world * TL, 8, dtype=torch.int32, device="cuda")
+        w_all = torch.zeros(world * TL, 8, dtype=torch.float32, device="cuda")
+        x_all.zero_()
+        g.ep_dispatch_routed(x_local, x_all, ids_local, w_local, ids_all, w_all)
+        torch.cuda.synchronize()
+        owner = torch.arange(world).repeat_interleave(TL).reshape(-1, 1).expand(-1, 8)
+        ok["dispatch_routed"] = (torch.equal(x_all.cpu(), want_all) and torch.equal(ids_all.cpu(), owner.int())
+                                 and torch.equal(w_all.cpu(), owner.float() + 0.5))
+
         # pipeline hand-off: a ring of byte copies, rank r -> r + 1
         carry = torch.full((TL, H), float(rank), dtype=torch.bfloat16, device="cuda")
         got = torch.zeros_like(carry)
