@@ -1683,6 +1683,12 @@ public:
     void dispatch(const act16* x_local, int tokens_local, int hidden, act16* x_all, void* stream) {
         check_status(aeon_b200_ep_dispatch(group_, x_local, tokens_local, static_cast<int64_t>(hidden) * 2, x_all, stream));
     }
+    // the same with the routing every rank computed for its own tokens (one grouped call)
+    void dispatch_routed(const act16* x_local, int tokens_local, int hidden, act16* x_all, const int32_t* ids_local,
+                         const float* weights_local, int top_k, int32_t* ids_all, float* weights_all, void* stream) {
+        check_status(aeon_b200_ep_dispatch_routed(group_, x_local, tokens_local, static_cast<int64_t>(hidden) * 2, x_all,
+                                                  ids_local, weights_local, top_k, ids_all, weights_all, stream));
+    }
     // expert parallel: partial rows to the ranks that own the tokens, then add in rank order
     void exchange(const float* partial, int tokens_local, int hidden, float* recv, void* stream) {
         check_status(aeon_b200_ep_exchange(group_, partial, tokens_local, hidden, recv, stream));

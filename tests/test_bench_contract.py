@@ -1,8 +1,8 @@
 """The benchmark's output contract: one JSON line with the keys the driver reads. Checked on a
-line recorded from a B200 run of `python bench.py --steps 10 --warmup 3`
-(tests/golden/bench_line_b200_sample.json; recorded when the kernel windows of the roofline
-object were still taken inside the overlapped step, hence its kernel-A fraction of 0.64 rather
-than the 0.69 of the kernel alone) and, live, on the CPU reference arm."""
+line recorded from a B200 run of `python bench.py --steps 20 --warmup 5`
+(tests/golden/bench_line_b200_sample.json) and, live, on the CPU reference arm. The shape
+literals the reference arm uses instead of the product library are checked against the
+library's own preset."""
 import json
 import os
 import subprocess
@@ -38,6 +38,14 @@ def test_recorded_b200_line_has_the_contract_keys():
     assert abs(roof["frac"] - roof["achieved"] / roof["peak"]) < 1e-9
     # ncu traffic within 2 % of the algorithmic bytes: every weight byte is read once
     assert 0.98 < roof["traffic"] / roof["algorithmic_bytes_per_launch"] < 1.02
+    assert roof["kernel"] == "moe_w13_rows_kernel" and roof["second_kernel"]["kernel"] == "moe_w2_rows_kernel"
+    assert 0.5 < roof["frac"] < 1.05 and 0.5 < roof["whole_step"]["frac"] < 1.0
+    # the run checks itself on the box that timed it: identical routing, layer output within tolerance
+    parity = line["parity"]
+    assert parity["ok"] and parity["ids_equal"] and parity["ids_match_oracle"]
+    assert parity["max_abs"] <= parity["tolerance"]["max_abs"] == 2e-2
+    assert parity["rel_l2"] <= parity["tolerance"]["rel_l2"] == 1e-3
+    assert line["launch_mode"] in ("cuda graph replay", "eager launches")
     cpu = line["cpu_baseline"]
     for key in ("value", "unit", "cores", "kind", "sample"):
         assert key in cpu, key
@@ -59,3 +67,15 @@ def test_reference_arm_prints_one_contract_line():
     assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0,
                            "d2h_bytes_per_step": 0}
     assert line["cpu_baseline"]["value"] == line["value"] and line["cpu_baseline"]["kind"] == "port"
+
+
+def test_reference_arm_shape_literals_match_the_library_preset():
+    """bench.py's reference arm must not load the product library, so it carries the benchmark's
+    shapes as literals; they have to be the library's `baseline` preset."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "project-aeon_b200"))
+    import bench
+    import aeon_b200
+    cfg = aeon_b200.preset("baseline")
+    for key, value in bench.BASELINE_SHAPE.items():
+        assert getattr(cfg, key) == value, key
