@@ -491,11 +491,23 @@ def main():
         end.record()
         barrier()
         ms = start.elapsed_time(end)
-        clocks = sampler.stop() if sampler else None
         if dist is not None:
             t = torch.tensor([ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
+        clocks = None
+        if sampler:
+            # nvidia-smi delivers a sample every 100 ms: a timed region shorter than half a second
+            # (the multi-GPU steps) is followed by the same steps, untimed, until 0.6 s of load have
+            # been sampled. The count comes from the reduced time, so every rank runs the same number.
+            extra = 0
+            if ms < 500.0:
+                extra = min(4000, int(600.0 / max(ms / steps, 1e-3)))
+                for _ in range(extra):
+                    fn()
+                barrier()
+            clocks = sampler.stop()
+            clocks["window"] = "timed region" if extra == 0 else f"timed region + {extra} untimed steps of the same load"
         return ms, clocks
 
     warmup = max(args.warmup, 3) if args.case == "full" else args.warmup
