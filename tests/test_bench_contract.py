@@ -51,7 +51,10 @@ def test_recorded_b200_line_has_the_contract_keys():
         assert key in cpu, key
     assert cpu["kind"] in ("reference", "port") and cpu["cores"] >= 1
     clocks = line["clocks"]
-    assert clocks["sm_mhz"] > 0.9 * clocks["sm_max_mhz"]
+    # at the clock limit, or below it with the power cap as the stated reason (1 kW part under a
+    # memory-bound load); never below it for no reason (a leftover clock lock)
+    assert clocks["sm_mhz"] > 0.9 * clocks["sm_max_mhz"] or "sw_power_cap" in clocks["reasons"]
+    assert clocks["sm_mhz"] > 0.8 * clocks["sm_max_mhz"]
     assert not set(clocks["reasons"]) & {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
 
 
