@@ -17,6 +17,7 @@
 // depend on the device's exp/log rounding. Stored weights are the unbiased scores of the
 // selected experts, divided by their sum when renormalising, then scaled.
 #include "common.cuh"
+#include "ptx.cuh"
 
 #include <mutex>
 
@@ -105,27 +106,43 @@ router_logits_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
     }
 }
 
-// The same logits for batches of 16 tokens and more, register-tiled: a warp owns kTileExperts
-// experts x kTileTokens tokens, so a gate vector is loaded once per eight tokens and an activation
-// vector once per four experts (the per-expert kernel above re-reads 1.25 rows per logit, this one
-// 0.19: at batch 128 that is 590 MB against 90 MB through L2, and the kernel was bound by exactly
-// that traffic). The four warps of a CTA share the token rows through L1. Every logit is still the
-// defined sum: lane l adds its vectors l, l + 32, ... in ascending order, element by element, one
-// fused multiply-add each, then the butterfly -- the results are bit-identical to the kernel above.
+// The same logits for batches of 32 tokens and more, tiled: a CTA of four warps owns 16 experts x
+// 8 tokens, a warp 4 experts x 8 tokens, so a gate vector is used for eight tokens and an
+// activation vector for sixteen experts (the per-expert kernel above re-reads 1.25 rows per
+// logit, this one 0.19: at batch 128 that is 590 MB against 90 MB through L2, and that kernel
+// was bound by exactly that traffic). The operands of a step (one 16-byte vector per lane and
+// row: 24 rows, 12 KB) come through a four-stage shared-memory ring filled with cp.async three
+// steps ahead, so no warp waits on a global load: with the loads straight into registers, one
+// step ahead, the kernel spent 1 us per step on the L2 round trip against 0.25 us of arithmetic.
+// Every logit is still the defined sum: lane l adds its vectors l, l + 32, ... in ascending
+// order, element by element, one fused multiply-add each, then the butterfly -- the results are
+// bit-identical to the kernel above.
 constexpr int kTileExperts = 4;     // per warp
 constexpr int kTileTokens = 8;      // per CTA (and per warp)
 constexpr int kTileWarps = 4;
+constexpr int kTileStages = 4;
+constexpr int kTileRows = kTileWarps * kTileExperts + kTileTokens;   // operand rows per step
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kTileWarps * 32)
 router_logits_tile_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
                           const uint16_t* __restrict__ gate, int tokens, int experts, int hidden,
                           float* __restrict__ logits) {
+    // [stage][row][lane]: rows 0..15 the CTA's gate rows (4 per warp), rows 16..23 its token rows
+    __shared__ uint4 ring[kTileStages][kTileRows][32];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int e0 = (blockIdx.x * kTileWarps + warp) * kTileExperts;
     const int t0 = blockIdx.y * kTileTokens;
-    if (e0 >= experts) return;
 
     float acc[kTileExperts][kTileTokens];
 #pragma unroll
@@ -133,47 +150,49 @@ router_logits_tile_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
 #pragma unroll
         for (int j = 0; j < kTileTokens; ++j) acc[a][j] = 0.f;
 
-    // rows past the end are clamped to the last one and their results dropped
-    const uint4* grow[kTileExperts];
+    // The rows this thread copies every step: its warp's four gate rows and two of the eight token
+    // rows. Rows past the end are clamped to the last one and their results dropped.
+    const uint4* src[kTileExperts + 2];
 #pragma unroll
     for (int a = 0; a < kTileExperts; ++a)
-        grow[a] = reinterpret_cast<const uint4*>(gate + static_cast<size_t>(min(e0 + a, experts - 1)) * hidden);
-    const uint4* xrow[kTileTokens];
+        src[a] = reinterpret_cast<const uint4*>(gate + static_cast<size_t>(min(e0 + a, experts - 1)) * hidden) + lane;
 #pragma unroll
-    for (int j = 0; j < kTileTokens; ++j)
-        xrow[j] = reinterpret_cast<const uint4*>(x + static_cast<size_t>(min(t0 + j, tokens - 1)) * x_stride);
+    for (int q = 0; q < 2; ++q)
+        src[kTileExperts + q] = reinterpret_cast<const uint4*>(
+                                    x + static_cast<size_t>(min(t0 + 2 * warp + q, tokens - 1)) * x_stride) + lane;
+    auto issue = [&](int step) {
+        uint4(*st)[32] = ring[step % kTileStages];
+#pragma unroll
+        for (int a = 0; a < kTileExperts; ++a) cp_async16(&st[warp * kTileExperts + a][lane], src[a] + step * 32);
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+            cp_async16(&st[kTileWarps * kTileExperts + 2 * warp + q][lane], src[kTileExperts + q] + step * 32);
+    };
 
-    // The next step's twelve vectors are requested before this step's 256 multiply-adds, so the
-    // loads' latency hides behind the arithmetic (a CTA has few warps and cannot hide it by switching).
-    const int vectors = hidden / 8;
-    uint4 gq[kTileExperts], xq[kTileTokens];
+    const int steps = hidden / 256;       // 32 lanes x 8 elements per step; hidden is a multiple of 256 here
 #pragma unroll
-    for (int a = 0; a < kTileExperts; ++a) gq[a] = __ldg(grow[a] + lane);
-#pragma unroll
-    for (int j = 0; j < kTileTokens; ++j) xq[j] = __ldg(xrow[j] + lane);
-    for (int v = lane; v < vectors; v += 32) {
-        uint4 gn[kTileExperts], xn[kTileTokens];
-        const int vn = v + 32 < vectors ? v + 32 : v;       // the last step re-requests its own (cached) vectors
-#pragma unroll
-        for (int a = 0; a < kTileExperts; ++a) gn[a] = __ldg(grow[a] + vn);
-#pragma unroll
-        for (int j = 0; j < kTileTokens; ++j) xn[j] = __ldg(xrow[j] + vn);
+    for (int s = 0; s < kTileStages - 1; ++s) {
+        if (s < steps) issue(s);
+        cp_async_commit();
+    }
+    for (int step = 0; step < steps; ++step) {
+        cp_async_wait<kTileStages - 2>();     // this thread's copies of `step` have landed
+        __syncthreads();                      // ... and everyone's; everyone is also done with step - 1
+        if (step + kTileStages - 1 < steps) issue(step + kTileStages - 1);      // into the stage step - 1 used
+        cp_async_commit();
+        const uint4(*st)[32] = ring[step % kTileStages];
         float gv[kTileExperts][8];
 #pragma unroll
-        for (int a = 0; a < kTileExperts; ++a) widen8<kBf16>(gq[a], gv[a]);
+        for (int a = 0; a < kTileExperts; ++a) widen8<kBf16>(st[warp * kTileExperts + a][lane], gv[a]);
 #pragma unroll
         for (int j = 0; j < kTileTokens; ++j) {
             float xv[8];
-            widen8<kBf16>(xq[j], xv);
+            widen8<kBf16>(st[kTileWarps * kTileExperts + j][lane], xv);
 #pragma unroll
             for (int a = 0; a < kTileExperts; ++a)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[a][j] = fmaf(gv[a][i], xv[i], acc[a][j]);
         }
-#pragma unroll
-        for (int a = 0; a < kTileExperts; ++a) gq[a] = gn[a];
-#pragma unroll
-        for (int j = 0; j < kTileTokens; ++j) xq[j] = xn[j];
     }
 #pragma unroll
     for (int a = 0; a < kTileExperts; ++a)
@@ -273,7 +292,7 @@ void launch_logits_dtype(const aeon_b200_moe_config& cfg, const void* x, int64_t
     const int expert_ctas = (cfg.experts + kLogitWarps - 1) / kLogitWarps;
     const uint16_t* xs = static_cast<const uint16_t*>(x);
     const uint16_t* gs = static_cast<const uint16_t*>(gate);
-    if (tokens >= 4 * kTileTokens) {
+    if (tokens >= 4 * kTileTokens && cfg.hidden % 256 == 0) {
         const dim3 grid((cfg.experts + kTileWarps * kTileExperts - 1) / (kTileWarps * kTileExperts),
                         (tokens + kTileTokens - 1) / kTileTokens);
         router_logits_tile_kernel<kBf16><<<grid, kTileWarps * 32, 0, stream>>>(xs, x_stride, gs, tokens, cfg.experts,
