@@ -387,7 +387,7 @@ class MoeStack:
         self._side = torch.cuda.Stream(device=dev)
         self._fork = torch.cuda.Event()
         self._join = torch.cuda.Event()
-        self._graph = None
+        self._graphs = {}          # (x pointer, out pointer) -> (graph, launches per replay)
         torch.cuda.synchronize(device)
 
     # -- bookkeeping ----------------------------------------------------------------------
@@ -408,10 +408,10 @@ class MoeStack:
     # -- the step -------------------------------------------------------------------------
     def forward(self, x, out, collect_stats: bool = False):
         """x[layers, tokens_local, H] 16-bit -> out[layers, tokens_local, H] fp32."""
-        if self._graph is not None and not collect_stats and x.data_ptr() == self._graph_x and \
-                out.data_ptr() == self._graph_out:
-            self._graph.replay()
-            self._extra_launches += self._graph_launches
+        captured = None if collect_stats else self._graphs.get((x.data_ptr(), out.data_ptr()))
+        if captured is not None:
+            captured[0].replay()
+            self._extra_launches += captured[1]
             return
         for l in range(self.layers):
             self.forward_layer(l, x[l], out[l], collect_stats)
@@ -419,7 +419,8 @@ class MoeStack:
     def capture(self, x, out):
         """Records one step over the fixed buffers x / out as a CUDA graph; later forward(x, out)
         calls with the same buffers replay it (one launch for the whole stack, no per-kernel
-        launch gaps). The step must have run once already (lazy allocations happen there)."""
+        launch gaps). The step must have run once already (lazy allocations happen there).
+        Several buffer pairs may be captured (double-buffered callers replay them in turn)."""
         import torch
         before = self.launches
         graph = torch.cuda.CUDAGraph()
@@ -427,8 +428,7 @@ class MoeStack:
         with torch.cuda.graph(graph):
             for l in range(self.layers):
                 self.forward_layer(l, x[l], out[l])
-        self._graph_launches = self.launches - before
-        self._graph, self._graph_x, self._graph_out = graph, x.data_ptr(), out.data_ptr()
+        self._graphs[(x.data_ptr(), out.data_ptr())] = (graph, self.launches - before)
 
     def close(self):
         """Releases the captured step and leaves the multi-GPU group (a collective call)."""
@@ -444,11 +444,12 @@ class MoeStack:
         """Drops the captured step. A graph that holds NCCL nodes keeps references into the
         communicator (NCCL frees a captured plan only when its graph is destroyed), so the
         process group must not be torn down while the graph is alive."""
-        if self._graph is not None:
+        if self._graphs:
             import torch
             torch.cuda.synchronize()
-            self._graph.reset()
-            self._graph = None
+            for graph, _ in self._graphs.values():
+                graph.reset()
+            self._graphs = {}
             torch.cuda.synchronize()
 
     def forward_layer(self, l: int, x, out, collect_stats: bool = False, return_routing: bool = False):
