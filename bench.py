@@ -737,7 +737,7 @@ def parity_check(args, model, cfg, dist, rank, world, x_dev, out_dev, x_bits_all
         ok = ids_equal and result["ids_match_oracle"] and cmp["max_abs"] <= tol_abs and cmp["rel_l2"] <= tol_l2
     else:
         ok = ids_equal
-    if dist is not None:   # every rank leaves with the same verdict
+    if dist is not None:   # every rank leaves with the same outcome
         t = torch.tensor([1 if ok else 0], dtype=torch.int64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         ok = bool(t.item())
