@@ -9,11 +9,12 @@
 // dimension (16..256), K in blocks of 64, fp32 accumulators in tensor memory.
 //
 //   warps 0-3   epilogue: tcgen05.ld, store the tile's fp32 partial sums;
-//   warps 4-11  feed the weight operand: two threads per tile row copy the row's 64 16-bit values
-//               of the k-block (four 128-bit loads, four k-blocks ahead) into the 128-byte-swizzled
-//               K-major tile in shared memory;
-//   warp 12     tiled TMA loads of the activation operand (no multicast);
-//   warp 13     MMA issue and commits; owns the tensor-memory allocation.
+//   warp 4      one thread issues the tiled TMA loads of both operands (no multicast): the dense
+//               16-bit weights are MMA-ready as they lie in memory, so a 128-row x 64-column box
+//               lands in the 128-byte-swizzled K-major tile without passing through registers
+//               (a first version copied them with eight warps of 128-bit loads and stores and was
+//               bound by those warps, 58 us for the two projections against 14 us of HBM time);
+//   warp 5      MMA issue and commits; owns the tensor-memory allocation.
 //
 // The projections are small in M x N (32 and 56 row blocks for one token tile), so K is split
 // over up to four CTAs per tile to occupy the SMs; every split writes its partial tile to a
@@ -38,9 +39,10 @@ constexpr int kTileM = 128;
 constexpr int kTileK = 64;
 constexpr int kMaxN = 256;
 constexpr int kStages = 4;
-constexpr int kEpilogueWarps = 4, kFeedWarps = 8;
-constexpr int kPrefetch = 4;         // k-blocks a feeding thread keeps in flight
-constexpr int kThreads = (kEpilogueWarps + kFeedWarps + 2) * 32;
+constexpr int kEpilogueWarps = 4;
+constexpr int kTmaWarp = kEpilogueWarps, kMmaWarp = kEpilogueWarps + 1;
+constexpr int kPrefetch = 4;         // K-splits are whole multiples of this many k-blocks
+constexpr int kThreads = (kEpilogueWarps + 2) * 32;
 constexpr int kStageA = kTileM * kTileK * 2;          // 16 KB
 constexpr int kStageB = kMaxN * kTileK * 2;           // 32 KB
 constexpr int kSmemBytes = 1024 /*align*/ + kStages * (kStageA + kStageB) + 256 /*barriers*/;
@@ -61,11 +63,6 @@ struct DenseParams {
 
 __device__ __forceinline__ void flag_error(int32_t* error, int code) { atomicCAS(error, kErrNone, code); }
 
-__device__ __forceinline__ uint4 ldg128(const uint16_t* p) {
-    uint4 v;
-    asm("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 
 // item -> (token tile, row block, split); the split runs fastest
 struct Item {
@@ -80,12 +77,14 @@ __device__ __forceinline__ Item decode_item(int item, int row_blocks, int splits
     return it;
 }
 
-// kGateUp: tile row r is row (rb*64 + (r/32)*16 + r%16) of W1 when (r/16) is even and of W3 when
-// odd (the interleave of the grouped GEMM); else tile row r is row rb*128 + r of W2.
+// kGateUp: row block rb < I / 128 is rows rb*128 .. of W1 (wmap_a), the others rows of W3 (wmap_b),
+// so the partial buffer's columns are [gate I | up I]; else row block rb is rows rb*128 .. of W2.
+// map0..2: the activation planes.
 template <bool kGateUp, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMap map0,
-                         const __grid_constant__ CUtensorMap map1, const __grid_constant__ CUtensorMap map2) {
+                         const __grid_constant__ CUtensorMap map1, const __grid_constant__ CUtensorMap map2,
+                         const __grid_constant__ CUtensorMap wmap_a, const __grid_constant__ CUtensorMap wmap_b) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem0 = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem0 - ptx::smem_u32(smem_raw));
@@ -106,7 +105,7 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            ptx::mbar_init(full_bar + 8 * s, kFeedWarps + 1);
+            ptx::mbar_init(full_bar + 8 * s, 1);             // the TMA thread's arrive with the byte count
             ptx::mbar_init(empty_bar + 8 * s, 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -115,7 +114,7 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
         }
         ptx::fence_barrier_init();
     }
-    if (warp == kEpilogueWarps + kFeedWarps + 1) {
+    if (warp == kMmaWarp) {
         tc5::tmem_alloc(tmem_slot, kTmemCols);
         tc5::tmem_relinquish();
     }
@@ -130,8 +129,8 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
     const int kb_split = p.planes * kb_plane / p.splits;     // k-blocks of one item
     const int total_items = token_tiles * row_blocks * p.splits;
 
-    if (warp == kEpilogueWarps + kFeedWarps) {
-        // ------------------------------ TMA: activation operand ------------------------------
+    if (warp == kTmaWarp) {
+        // ------------------------------ TMA: both operands ---------------------------------------
         if (lane == 0) {
             uint32_t n = 0;
             for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
@@ -139,6 +138,14 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
                 const int tok0 = it.tt * kMaxN;
                 const int ntok = min(kMaxN, p.tokens - tok0);
                 const int boxes = (ntok + 63) / 64;
+                const CUtensorMap* wmap = &wmap_a;
+                int wrow = it.rb * kTileM;
+                if constexpr (kGateUp) {
+                    if (wrow >= p.half_rows) {
+                        wmap = &wmap_b;
+                        wrow -= p.half_rows;
+                    }
+                }
                 for (int k = 0; k < kb_split; ++k, ++n) {
                     const int kg = it.sp * kb_split + k;
                     const int plane = kg / kb_plane;
@@ -147,14 +154,15 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
                     const int s = n % kStages;
                     const uint32_t parity = (n / kStages) & 1;
                     if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error)) flag_error(p.error, kErrWaitTimeout);
-                    ptx::mbar_arrive_expect_tx(full_bar + 8 * s, boxes * 64 * kTileK * 2);
+                    ptx::mbar_arrive_expect_tx(full_bar + 8 * s, boxes * 64 * kTileK * 2 + kStageA);
+                    tc5::tma_load_2d(a_smem + s * kStageA, wmap, kb * kTileK, wrow, full_bar + 8 * s);
                     for (int b = 0; b < boxes; ++b)
                         tc5::tma_load_2d(b_smem + s * kStageB + b * (64 * kTileK * 2), map, kb * kTileK,
                                          tok0 + b * 64, full_bar + 8 * s);
                 }
             }
         }
-    } else if (warp == kEpilogueWarps + kFeedWarps + 1) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issue ---------------------------------------------
         if (lane == 0) {
             uint32_t n = 0, count = 0;
@@ -186,58 +194,6 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
                 tc5::commit(acc_full + 8 * buf);         // accumulator complete
             }
         }
-    } else if (warp >= kEpilogueWarps) {
-        // ------------------------------ feed the weight operand --------------------------------
-        const int d = tid - kEpilogueWarps * 32;
-        const int r = d >> 1;                             // tile row, 0..127
-        const int half = d & 1;                           // which 32 columns of the k-block
-        const uint32_t row_smem = (r >> 3) * 1024 + (r & 7) * 128;
-        uint32_t dst_off[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) dst_off[c] = row_smem + (((half * 4 + c) ^ (r & 7)) << 4);
-        uint32_t n = 0;
-        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-            const Item it = decode_item(item, row_blocks, p.splits);
-            const uint16_t* src_row;
-            if constexpr (kGateUp) {
-                const int row = it.rb * 64 + (r >> 5) * 16 + (r & 15);
-                src_row = (((r >> 4) & 1) ? p.wb : p.wa) + static_cast<size_t>(row) * p.K;
-            } else {
-                src_row = p.wa + static_cast<size_t>(it.rb * kTileM + r) * p.K;
-            }
-            src_row += half * 32;
-            // k-block k of the item covers weight columns ((sp * kb_split + k) mod kb_plane) * 64 ..
-            auto fetch = [&](int k, uint4 (&q)[4]) {
-                const int kg = it.sp * kb_split + k;
-                const int kb = kg % kb_plane;
-                const uint16_t* src = src_row + kb * kTileK;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) q[c] = ldg128(src + c * 8);
-            };
-            uint4 qbuf[kPrefetch][4];
-#pragma unroll
-            for (int i = 0; i < kPrefetch; ++i) fetch(i, qbuf[i]);
-            for (int k0 = 0; k0 < kb_split; k0 += kPrefetch) {
-                const bool more = k0 + kPrefetch < kb_split;
-#pragma unroll
-                for (int i = 0; i < kPrefetch; ++i) {
-                    const int s = n % kStages;
-                    const uint32_t parity = (n / kStages) & 1;
-                    ++n;
-                    if (!ptx::mbar_wait(empty_bar + 8 * s, parity ^ 1, p.error))
-                        flag_error(p.error, kErrWaitTimeout);
-                    uint8_t* dst = smem_gen + s * kStageA;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(dst + dst_off[c]) = qbuf[i][c];
-                    // generic-proxy writes must be visible to the tensor core (async proxy)
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(full_bar + 8 * s);
-                    // the slot is free again: next round's k-block for it goes in flight
-                    if (more) fetch(k0 + kPrefetch + i, qbuf[i]);
-                }
-            }
-        }
     } else {
         // ------------------------------ epilogue: fp32 partial tile ------------------------------
         const int quad = warp;                              // TMEM lanes 32*quad .. +31
@@ -247,9 +203,7 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
             const Item it = decode_item(item, row_blocks, p.splits);
             const int tok0 = it.tt * kMaxN;
             const int ntok = min(kMaxN, p.tokens - tok0);
-            int col;
-            if constexpr (kGateUp) col = ((r >> 4) & 1) * p.half_rows + it.rb * 64 + (r >> 5) * 16 + (r & 15);
-            else col = it.rb * kTileM + r;
+            const int col = it.rb * kTileM + r;
             float* out = p.partial + (static_cast<size_t>(it.sp) * p.tokens + tok0) * p.rows + col;
             const uint32_t buf = count & 1;
             if (!ptx::mbar_wait(acc_full + 8 * buf, (count >> 1) & 1, p.error)) flag_error(p.error, kErrWaitTimeout);
@@ -271,7 +225,7 @@ shared_dense_gemm_kernel(const DenseParams p, const __grid_constant__ CUtensorMa
 
     tc5::fence_before_sync();
     __syncthreads();
-    if (warp == kEpilogueWarps + kFeedWarps + 1) {
+    if (warp == kMmaWarp) {
         tc5::fence_after_sync();
         tc5::tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -382,6 +336,10 @@ void run(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2, con
     const CUtensorMap hi_map = make_rowmajor16_map(hi, tokens, I, I);
     const CUtensorMap mid_map = make_rowmajor16_map(mid, tokens, I, I);
     const CUtensorMap lo_map = make_rowmajor16_map(lo, tokens, I, I);
+    // the dense weights, one 128-row box per k-block
+    const CUtensorMap w1_map = make_rowmajor16_map(w1, I, H, H, kTileM);
+    const CUtensorMap w3_map = make_rowmajor16_map(w3, I, H, H, kTileM);
+    const CUtensorMap w2_map = make_rowmajor16_map(w2, H, I, I, kTileM);
 
     auto gemm1 = shared_dense_gemm_kernel<true, kBf16>;
     auto gemm2 = shared_dense_gemm_kernel<false, kBf16>;
@@ -400,7 +358,7 @@ void run(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2, con
     p.partial = s->partial;
     p.error = ctx->d_error;
     const int items1 = token_tiles * (2 * I / kTileM) * splits1;
-    gemm1<<<std::min(items1, ctx->sm_count), kThreads, kSmemBytes, stream>>>(p, x_map, x_map, x_map);
+    gemm1<<<std::min(items1, ctx->sm_count), kThreads, kSmemBytes, stream>>>(p, x_map, x_map, x_map, w1_map, w3_map);
     AEON_CUDA_CHECK(cudaGetLastError());
     {
         const int64_t total = static_cast<int64_t>(tokens) * I;
@@ -417,7 +375,7 @@ void run(aeon_b200_ctx* ctx, const void* w1, const void* w3, const void* w2, con
     p.planes = 3;
     p.splits = splits2;
     const int items2 = token_tiles * (H / kTileM) * splits2;
-    gemm2<<<std::min(items2, ctx->sm_count), kThreads, kSmemBytes, stream>>>(p, hi_map, mid_map, lo_map);
+    gemm2<<<std::min(items2, ctx->sm_count), kThreads, kSmemBytes, stream>>>(p, hi_map, mid_map, lo_map, w2_map, w2_map);
     AEON_CUDA_CHECK(cudaGetLastError());
     {
         const int64_t total = static_cast<int64_t>(tokens) * H / 4;

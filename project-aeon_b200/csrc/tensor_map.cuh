@@ -29,13 +29,14 @@ inline EncodeTiledFn encode_tiled() {
 }
 
 // Row-major 16-bit matrix [rows, cols] whose rows are `row_stride` elements apart (a multiple
-// of 8, i.e. 16 bytes); box = 64 columns (128 B) x 64 rows, 128-byte swizzle; rows past the
-// end read as zero.
-inline CUtensorMap make_rowmajor16_map(const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride) {
+// of 8, i.e. 16 bytes); box = 64 columns (128 B) x `box_rows` rows (a multiple of 8, at most 256:
+// a box is whole 1024-byte swizzle atoms), 128-byte swizzle; rows past the end read as zero.
+inline CUtensorMap make_rowmajor16_map(const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                                       uint32_t box_rows = 64) {
     CUtensorMap map;
     const cuuint64_t gdim[2] = {cols, rows};
     const cuuint64_t gstride[1] = {row_stride * 2};
-    const cuuint32_t box[2] = {64, 64};
+    const cuuint32_t box[2] = {64, box_rows};
     const cuuint32_t estride[2] = {1, 1};
     const CUresult rc = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim,
                                        gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
