@@ -10,16 +10,21 @@ experts. Weights are synthetic (see synth.py); a real model uploads payloads int
 
 Expert parallelism (world > 1). Expert e lives on rank e // (E / world); gate and shared
 expert are replicated; every rank owns tokens_local = tokens / world tokens.
-  dispatch  all-gather of the activation rows, so every rank holds the whole batch. At decode
-            batch sizes a padded equal-split all-to-all moves exactly the same bytes, and
-            the gather needs no count exchange and no host synchronisation. The router then
-            runs replicated on identical inputs, so routing is bit-identical on every rank
-            and needs no exchange either.
-  compute   each rank runs only its resident experts (absent experts are skipped) into a
-            zeroed fp32 partial [tokens, H].
-  combine   equal-split all-to-all of the partial rows to their owners, then the owners add
-            the `world` partial slices in rank order to their shared-expert rows: a fixed
-            summation order, independent of arrival order.
+  shared    the shared expert of the rank's own tokens runs on a side stream beside everything
+            up to the combine, whose initial value it produces.
+  routing   every rank routes its own tokens. The router is a per-token function, so the
+            gathered routing is bit-identical to a router run on the whole batch.
+  dispatch  rows and routing of every rank to every rank: a grouped all-gather
+            (Group.ep_dispatch_routed) or, with peer_combine, plain stores into every rank's
+            gather buffers and a bounded wait for the others' (PeerCombine.dispatch). At decode
+            batch sizes a padded equal-split all-to-all would move exactly the same bytes.
+  compute   each rank runs only its resident experts over the whole batch (absent experts are
+            skipped).
+  combine   collective form: the partial rows are written (no zero fill), an equal-split
+            all-to-all moves them to their owners, the owners add the `world` slices in rank
+            order. Peer form: the accumulate stores each finished row straight into its owner's
+            receive buffer and the owner waits for `world` flags, then adds in rank order. Either
+            way the summation order is fixed, independent of arrival.
 """
 from __future__ import annotations
 
