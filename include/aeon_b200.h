@@ -217,7 +217,7 @@ int aeon_b200_expert_permutation(aeon_b200_ctx* ctx, const int32_t* topk_ids, in
  * run_layer_body_moe_shared_expert[_batch]
  * (src/architecture/deepseek_v4/layer/v4_layer_body_moe.hpp:216-256,
  *  src/architecture/deepseek_v4/layer/v4_layer_body_batch.hpp:863-917).
- * w1, w3: [I, H]; w2: [H, I]; row-major, act_dtype. Up to 64 tokens the weights
+ * w1, w3: [I, H]; w2: [H, I]; row-major, act_dtype. Up to 16 tokens the weights
  * are streamed through warp MMAs; above, the two projections run as split-K
  * tcgen05 GEMMs, whose partial-sum scratch is allocated by the first such call
  * on a context (make that call outside any stream capture). */

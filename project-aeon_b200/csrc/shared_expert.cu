@@ -25,10 +25,11 @@ namespace aeon_b200 {
 namespace {
 
 // Above this many tokens the tensor-core form (shared_expert_tc.cu) takes over. Its time is
-// nearly flat in the token count (it is bound by feeding the weight operand), while the kernels
-// here stream the weights once per group of 32 tokens; measured on B200 the two meet between two
-// and three groups (batch 32: 983 vs 1057 us per layer; batch 128: 1741 vs 1706 us).
-constexpr int kTensorCoreFrom = 64;
+// nearly flat in the token count (both operands arrive by TMA; it is bound by streaming the 88 MB
+// of weights), while the kernels here stream the weights once per group of up to 32 tokens.
+// Measured on B200, microseconds per call: these kernels 31 / 38 / 67 / 76 / 94 at 8 / 16 / 17 /
+// 32 / 64 tokens, the tensor-core form 49 / 52 / 54 at 65 / 96 / 128.
+constexpr int kTensorCoreFrom = 16;
 
 // Instances <warps, N tiles>: <16, 1> up to 8 tokens, <16, 2> up to 16, <8, 4> beyond
 // (32 tokens per CTA pass). The reduction buffer stays within 32 KB of static shared memory.

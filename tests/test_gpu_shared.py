@@ -8,8 +8,9 @@ import gpu_support as gs
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("preset,tokens", [("baseline", 1), ("baseline", 12), ("baseline", 19), ("ref_dsv4", 5), ("ref_dsv4", 45),
-                                           # above 64 tokens: the tensor-core form
+@pytest.mark.parametrize("preset,tokens", [("baseline", 1), ("baseline", 12), ("baseline", 16), ("ref_dsv4", 5),
+                                           # above 16 tokens: the tensor-core form
+                                           ("baseline", 17), ("baseline", 19), ("ref_dsv4", 45), ("baseline", 64),
                                            ("baseline", 100), ("ref_dsv4", 77),
                                            # more than one 256-token pass
                                            ("baseline", 300)])
