@@ -106,7 +106,7 @@ router_logits_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
     }
 }
 
-// The same logits for batches of 32 tokens and more, tiled: a CTA of four warps owns 16 experts x
+// The same logits for batches of 16 tokens and more, tiled: a CTA of four warps owns 16 experts x
 // 8 tokens, a warp 4 experts x 8 tokens, so a gate vector is used for eight tokens and an
 // activation vector for sixteen experts (the per-expert kernel above re-reads 1.25 rows per
 // logit, this one 0.19: at batch 128 that is 590 MB against 90 MB through L2, and that kernel
@@ -118,10 +118,9 @@ router_logits_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
 // order, element by element, one fused multiply-add each, then the butterfly -- the results are
 // bit-identical to the kernel above.
 constexpr int kTileExperts = 4;     // per warp
-constexpr int kTileTokens = 8;      // per CTA (and per warp)
+constexpr int kTileTokens = 8;      // per CTA (and per warp); 4 for batches that would leave SMs idle
 constexpr int kTileWarps = 4;
 constexpr int kTileStages = 4;
-constexpr int kTileRows = kTileWarps * kTileExperts + kTileTokens;   // operand rows per step
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(smem_dst)), "l"(src) : "memory");
@@ -132,12 +131,15 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
-template <bool kBf16>
+template <bool kBf16, int kTileTokens>
 __global__ void __launch_bounds__(kTileWarps * 32)
 router_logits_tile_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
                           const uint16_t* __restrict__ gate, int tokens, int experts, int hidden,
                           float* __restrict__ logits) {
-    // [stage][row][lane]: rows 0..15 the CTA's gate rows (4 per warp), rows 16..23 its token rows
+    static_assert(kTileTokens % kTileWarps == 0, "every warp copies the same number of token rows");
+    constexpr int kTileRows = kTileWarps * kTileExperts + kTileTokens;   // operand rows per step
+    constexpr int kCopyTokens = kTileTokens / kTileWarps;                // token rows a warp copies
+    // [stage][row][lane]: rows 0..15 the CTA's gate rows (4 per warp), then its token rows
     __shared__ uint4 ring[kTileStages][kTileRows][32];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -150,23 +152,23 @@ router_logits_tile_kernel(const uint16_t* __restrict__ x, int64_t x_stride,
 #pragma unroll
         for (int j = 0; j < kTileTokens; ++j) acc[a][j] = 0.f;
 
-    // The rows this thread copies every step: its warp's four gate rows and two of the eight token
+    // The rows this thread copies every step: its warp's four gate rows and its share of the token
     // rows. Rows past the end are clamped to the last one and their results dropped.
-    const uint4* src[kTileExperts + 2];
+    const uint4* src[kTileExperts + kCopyTokens];
 #pragma unroll
     for (int a = 0; a < kTileExperts; ++a)
         src[a] = reinterpret_cast<const uint4*>(gate + static_cast<size_t>(min(e0 + a, experts - 1)) * hidden) + lane;
 #pragma unroll
-    for (int q = 0; q < 2; ++q)
+    for (int q = 0; q < kCopyTokens; ++q)
         src[kTileExperts + q] = reinterpret_cast<const uint4*>(
-                                    x + static_cast<size_t>(min(t0 + 2 * warp + q, tokens - 1)) * x_stride) + lane;
+                                    x + static_cast<size_t>(min(t0 + kCopyTokens * warp + q, tokens - 1)) * x_stride) + lane;
     auto issue = [&](int step) {
         uint4(*st)[32] = ring[step % kTileStages];
 #pragma unroll
         for (int a = 0; a < kTileExperts; ++a) cp_async16(&st[warp * kTileExperts + a][lane], src[a] + step * 32);
 #pragma unroll
-        for (int q = 0; q < 2; ++q)
-            cp_async16(&st[kTileWarps * kTileExperts + 2 * warp + q][lane], src[kTileExperts + q] + step * 32);
+        for (int q = 0; q < kCopyTokens; ++q)
+            cp_async16(&st[kTileWarps * kTileExperts + kCopyTokens * warp + q][lane], src[kTileExperts + q] + step * 32);
     };
 
     const int steps = hidden / 256;       // 32 lanes x 8 elements per step; hidden is a multiple of 256 here
@@ -292,11 +294,19 @@ void launch_logits_dtype(const aeon_b200_moe_config& cfg, const void* x, int64_t
     const int expert_ctas = (cfg.experts + kLogitWarps - 1) / kLogitWarps;
     const uint16_t* xs = static_cast<const uint16_t*>(x);
     const uint16_t* gs = static_cast<const uint16_t*>(gate);
-    if (tokens >= 4 * kTileTokens && cfg.hidden % 256 == 0) {
-        const dim3 grid((cfg.experts + kTileWarps * kTileExperts - 1) / (kTileWarps * kTileExperts),
-                        (tokens + kTileTokens - 1) / kTileTokens);
-        router_logits_tile_kernel<kBf16><<<grid, kTileWarps * 32, 0, stream>>>(xs, x_stride, gs, tokens, cfg.experts,
-                                                                             cfg.hidden, logits);
+    if (tokens >= 2 * kTileTokens && cfg.hidden % 256 == 0) {
+        const int expert_groups = (cfg.experts + kTileWarps * kTileExperts - 1) / (kTileWarps * kTileExperts);
+        // a CTA's time is the length of its K loop whatever the batch: when 8-token tiles would leave
+        // more than half of the SMs without a CTA, 4-token tiles halve each CTA's work instead
+        if (expert_groups * ((tokens + kTileTokens - 1) / kTileTokens) * 2 <= 148) {
+            const dim3 grid(expert_groups, (tokens + 3) / 4);
+            router_logits_tile_kernel<kBf16, 4><<<grid, kTileWarps * 32, 0, stream>>>(xs, x_stride, gs, tokens,
+                                                                                   cfg.experts, cfg.hidden, logits);
+        } else {
+            const dim3 grid(expert_groups, (tokens + kTileTokens - 1) / kTileTokens);
+            router_logits_tile_kernel<kBf16, kTileTokens><<<grid, kTileWarps * 32, 0, stream>>>(
+                xs, x_stride, gs, tokens, cfg.experts, cfg.hidden, logits);
+        }
     } else if (tokens < kLogitTokens) {
         // one token per CTA pass: no clamped duplicates at the smallest batches
         router_logits_kernel<kBf16, 1><<<dim3(expert_ctas, tokens), kLogitWarps * 32, 0, stream>>>(

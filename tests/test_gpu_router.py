@@ -24,7 +24,7 @@ def run_router(cfg, x_bits, gate_bits, bias=None, hash_table=None, token_ids=Non
     return w.cpu().numpy(), ids.cpu().numpy(), logits.cpu().numpy()
 
 
-@pytest.mark.parametrize("tokens", [1, 8, 37, 128])
+@pytest.mark.parametrize("tokens", [1, 8, 16, 21, 32, 37, 128])
 def test_baseline_router_matches_oracle(oracle, tokens):
     cfg = aeon_b200.preset("baseline")
     rng = np.random.default_rng(0)
